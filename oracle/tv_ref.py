@@ -1,0 +1,585 @@
+"""CPU restatement of the reference's unrolled FISTA TV-inpainting layer (forward + hand-derived backward).
+
+TEST INFRASTRUCTURE ONLY.  This module is the checker for the CUDA path and the timed CPU baseline of the
+benchmark.  Nothing in the shipped package imports it; the product path has no CPU fallback.
+
+Parity status: PARITY UNPINNED by the reference's own tests -- the reference ships no tests, golden vectors or
+fixtures, and its CUDA sources cannot be built without the un-vendored ImageUtilities library.  What pins this
+restatement instead:
+  * the reverse-sweep math is checked against ``torch.autograd`` of the forward restatement (``exact=True`` mode),
+  * the forward is checked against an independent per-pixel loop restatement (``forward_iteration_loops``),
+  * the reference-only approximations ("quirks") are small, separately switchable deltas on top of that.
+
+Every function cites the lines of ``cudaTV/cudaCode/TVInpaintFista.cu`` it follows.  All tensors are torch CPU
+tensors; ``dtype=torch.float64`` is the parity oracle, ``dtype=torch.float32`` is the timed CPU baseline.
+
+Layout: ``b``, ``init``, gradients w.r.t. them: ``[N, C, H, W]``;  ``wx``, ``wy``, ``c`` and their gradients:
+``[N, 1, H, W]``.  The reference handles N == 1 only; a batch is N independent problems.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import numpy as np
+import torch
+
+# ---------------------------------------------------------------------------------------------------------------
+# constants (TVInpaintFista.cu:30-90); the reference writes them as fp32 literals, so the fp64 oracle uses the
+# fp32-rounded values too.
+# ---------------------------------------------------------------------------------------------------------------
+HUBER_DELTA = float(np.float32(0.1))        # __HDelta1__            :44
+CLIP_LOCAL_GRAD = 10000.0                   # clipLocalGrad          :52
+LOCAL_GC_MULT = float(np.float32(0.1))      # localGCMult            :63
+LOCAL_GX_MULT = float(np.float32(0.1))      # localGXMult            :65
+LOCAL_GB_MULT = 1.0                         # localGBMult            :67
+GLOBAL_G_MULT = float(np.float32(0.1))      # globalGMult            :69
+KILL_T = 50.0                               # _kill_T_               :84
+SCALE_T = 10.0                              # _scale_T_              :88
+MEMORY_T = 0.975                            # _memory_T_             :90
+LIPSCHITZ_INV = 1.0 / 8.0                   # L                      :1478, :1587
+MAX_TOLERANCE = 10000000.0                  # check_gradUpdate       :160
+NUM_IDS = 10                                # __uniqueIds__  TVInpaintFista.h:5
+
+
+def checkpoint_schedule(its: int) -> List[int]:
+    """Iteration indices at which the reference checkpoints (y, x) (TVInpaintFista.cu:1499-1504)."""
+    n = int(math.floor(math.sqrt(its)))
+    return [int(math.floor(i * math.sqrt(its) * 0.5) * 2) for i in range(n)]
+
+
+def step_sizes(its: int) -> List[float]:
+    """FISTA momentum table, stored by the reference as fp32 (TVInpaintFista.cu:1525-1532)."""
+    out = []
+    t = 1.0
+    for _ in range(its):
+        t_ = t
+        t = (1.0 + math.sqrt(1.0 + 4.0 * t * t)) / 2.0
+        out.append(float(np.float32(max(0.0, (t_ - 1.0) / t))))
+    return out
+
+
+def effective_iterations(its: int) -> int:
+    """The forward loop runs its/2 pairs (TVInpaintFista.cu:1539)."""
+    return 2 * (its // 2)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# shifted views.  The reference stages a zero-padded tile (TVInpaintFista.cu:1229-1237), so every neighbour
+# outside the image reads 0.
+# ---------------------------------------------------------------------------------------------------------------
+def _up(a):      # a[h-1][w]
+    z = torch.zeros_like(a)
+    z[..., 1:, :] = a[..., :-1, :]
+    return z
+
+
+def _dn(a):      # a[h+1][w]
+    z = torch.zeros_like(a)
+    z[..., :-1, :] = a[..., 1:, :]
+    return z
+
+
+def _lf(a):      # a[h][w-1]
+    z = torch.zeros_like(a)
+    z[..., :, 1:] = a[..., :, :-1]
+    return z
+
+
+def _rt(a):      # a[h][w+1]
+    z = torch.zeros_like(a)
+    z[..., :, :-1] = a[..., :, 1:]
+    return z
+
+
+@dataclass
+class _Weights:
+    """The six texture reads of the kernels (TVInpaintFista.cu:1204-1211), already multiplied by L."""
+    wx_0: torch.Tensor   # wx[h][w-1]            (w > 0)
+    wx_1: torch.Tensor   # wx[h][w]              (w < W-1)
+    wy_0: torch.Tensor   # wy[h-1][w]            (h > 0)
+    wy_1: torch.Tensor   # wy[h][w]              (h < H-1)
+    wx_2: torch.Tensor   # wx[h-1][w]            (h > 0 and w < W-1)
+    wy_2: torch.Tensor   # wy[h][w-1]            (w > 0 and h < H-1)
+    mask_x: torch.Tensor  # w < W-1
+    mask_y: torch.Tensor  # h < H-1
+
+
+def _prepare_weights(wx: torch.Tensor, wy: torch.Tensor, dtype) -> _Weights:
+    # The reference scales private copies of wx, wy by L = 1/8 (:1483-1489, :1588-1593); inputs are not modified.
+    wxs = (wx.to(dtype) * LIPSCHITZ_INV).clone()
+    wys = (wy.to(dtype) * LIPSCHITZ_INV).clone()
+    mask_x = torch.ones_like(wxs, dtype=torch.bool)
+    mask_x[..., :, -1] = False
+    mask_y = torch.ones_like(wys, dtype=torch.bool)
+    mask_y[..., -1, :] = False
+    wx_1 = torch.where(mask_x, wxs, torch.zeros_like(wxs))
+    wy_1 = torch.where(mask_y, wys, torch.zeros_like(wys))
+    return _Weights(wx_0=_lf(wx_1), wx_1=wx_1, wy_0=_up(wy_1), wy_1=wy_1, wx_2=_up(wx_1), wy_2=_lf(wy_1),
+                    mask_x=mask_x, mask_y=mask_y)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# forward
+# ---------------------------------------------------------------------------------------------------------------
+def gradient_step(y: torch.Tensor, wts: _Weights) -> torch.Tensor:
+    """x^{k+1/2} = y - (Huber-weighted graph Laplacian)(y)   (TVInpaintFista.cu:1247-1274)."""
+    d = HUBER_DELTA
+    yc = y
+    y_up, y_dn, y_lf, y_rt = _up(y), _dn(y), _lf(y), _rt(y)
+    y_up_rt = _up(_rt(y))
+    y_dn_lf = _dn(_lf(y))
+    one = torch.ones((), dtype=y.dtype)
+    x05 = yc.clone()
+    # triangle anchored at (h-1, w)   :1250-1259
+    hub = torch.sqrt((yc - y_up) * (yc - y_up) * wts.wy_0 + (y_up - y_up_rt) * (y_up - y_up_rt) * wts.wx_2)
+    x05 = x05 - (yc - y_up) * (wts.wy_0 / torch.maximum(one, hub / d))
+    # triangle anchored at (h, w-1)   :1260-1266
+    hub = torch.sqrt((yc - y_lf) * (yc - y_lf) * wts.wx_0 + (y_lf - y_dn_lf) * (y_lf - y_dn_lf) * wts.wy_2)
+    x05 = x05 - (yc - y_lf) * (wts.wx_0 / torch.maximum(one, hub / d))
+    # triangle anchored at (h, w)     :1268-1274
+    hub = torch.sqrt((yc - y_dn) * (yc - y_dn) * wts.wy_1 + (yc - y_rt) * (yc - y_rt) * wts.wx_1)
+    x05 = x05 - (yc - y_dn) * (wts.wy_1 / torch.maximum(one, hub / d))
+    x05 = x05 - (yc - y_rt) * (wts.wx_1 / torch.maximum(one, hub / d))
+    return x05
+
+
+def prox_huber(x05: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
+    """Huber data-term prox (TVInpaintFista.cu:1288-1292)."""
+    x = (c * b + x05) / (1.0 + c)
+    lo = x05 - c
+    hi = x05 + c
+    x = torch.where(lo > 1.0 + b, lo, x)
+    x = torch.where(hi < b - 1.0, hi, x)
+    return x
+
+
+def forward_iteration(y, x_prev, b, c, wts: _Weights, t: float):
+    """One launch of the forward kernel (TVInpaintFista.cu:1194-1319 / :1321-1455).
+
+    Returns (y_next, x_next, x05) where x05 is the pre-prox iterate the *_writexk05 variant stores (:1414)."""
+    x05 = gradient_step(y, wts)
+    x = prox_huber(x05, b, c)
+    y_next = x + t * (x - x_prev)        # :1315
+    return y_next, x, x05
+
+
+def tv_forward_raw(wx, wy, c, b, init, its: int, dtype=torch.float64):
+    """Host loop of TVInpaintFista::forward (TVInpaintFista.cu:1463-1559) without the id bookkeeping.
+
+    Returns (solution, checkpoints) where checkpoints[i] = (y, x) at iteration checkpoint_schedule(its)[i]."""
+    b = b.to(dtype)
+    c = c.to(dtype)
+    wts = _prepare_weights(wx, wy, dtype)
+    x = init.to(dtype).clone()       # d_dout  :1495
+    y = init.to(dtype).clone()       # y0_temp :1496
+    sched = checkpoint_schedule(its)
+    steps = step_sizes(its)
+    ckpts = []
+    nxt = 0
+    for g in range(effective_iterations(its)):
+        if g % 2 == 0 and nxt < len(sched) and sched[nxt] == g:     # :1541-1546
+            ckpts.append((y.clone(), x.clone()))
+            nxt += 1
+        y, x, _ = forward_iteration(y, x, b, c, wts, steps[g])
+    return x, ckpts
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# reverse sweep
+# ---------------------------------------------------------------------------------------------------------------
+def rederive_y(x05_it, x05_itm1, b, c, t: float):
+    """y^{k+1} rebuilt from two stored pre-prox iterates (TVInpaintFista.cu:1130-1189, Huber branch).
+
+    When iterate `it` sits in the quadratic zone BOTH iterates go through the quadratic formula; otherwise both
+    go through an L1 soft-threshold -- neither is the forward Huber prox for the other iterate in general."""
+    diff = b - x05_it
+    sign = torch.where(diff < 0, -torch.ones_like(diff), torch.ones_like(diff))
+    quad = (1.0 + c) >= sign * diff
+    # quadratic zone :1154-1159
+    xk_q = (c * b + x05_it) / (1.0 + c)
+    xkm_q = (c * b + x05_itm1) / (1.0 + c)
+    y_q = xk_q + t * (xk_q - xkm_q)
+    # L1 zone :1160-1165
+    xk_l = torch.where(c <= sign * diff, b - diff + sign * c, b)
+    diff2 = b - x05_itm1
+    sign2 = torch.where(diff2 < 0, -torch.ones_like(diff2), torch.ones_like(diff2))
+    xkm_l = torch.where(c <= sign2 * diff2, b - diff2 + sign2 * c, b)
+    y_l = xk_l + t * (xk_l - xkm_l)
+    return torch.where(quad, y_q, y_l)
+
+
+def _prox_reverse(df_dxk, x05, b, c):
+    """Prox Jacobian applied to the gradient w.r.t. x^{k+1} (TVInpaintFista.cu:806-828 == :240-255).
+
+    Returns (g_half_out, dgc_contrib [N,1,H,W], dgb_contrib [N,C,H,W]); the contributions carry the reference's
+    localGCMult / localGBMult scalings."""
+    diff = b - x05
+    sign = torch.where(diff < 0, -torch.ones_like(diff), torch.ones_like(diff))
+    quad = (1.0 + c) >= sign * diff
+    opc = 1.0 + c
+    gc_q = df_dxk * (b / opc - (c * b + x05) / (opc * opc)) * LOCAL_GC_MULT
+    gh_q = df_dxk / opc
+    gb_q = df_dxk * c / opc * LOCAL_GB_MULT
+    # linear zone; the nested `conf >= sign*diff` test (:818) can never hold once 1+conf < sign*diff
+    gh_l = df_dxk
+    gc_l = sign * df_dxk * LOCAL_GC_MULT
+    zero = torch.zeros_like(df_dxk)
+    g_half = torch.where(quad, gh_q, gh_l)
+    dgc = torch.where(quad, gc_q, gc_l).sum(dim=1, keepdim=True)
+    dgb = torch.where(quad, gb_q, zero)
+    return g_half, dgc, dgb
+
+
+def laplacian_transpose(y, g, wts: _Weights):
+    """(d x^{k+1/2} / d y)^T g and the per-edge weight gradients, evaluated at y (TVInpaintFista.cu:651-771).
+
+    Returns (df_dy_t [N,C,H,W], dgwx [N,1,H,W], dgwy [N,1,H,W]); dgw* carry -localGXMult and are summed over
+    channels exactly like the reference's in-place accumulation."""
+    d = HUBER_DELTA
+    yk = y
+    y_up, y_dn, y_lf, y_rt = _up(y), _dn(y), _lf(y), _rt(y)
+    y_up_rt = _up(_rt(y))
+    y_dn_lf = _dn(_lf(y))
+    g_up, g_dn, g_lf, g_rt = _up(g), _dn(g), _lf(g), _rt(g)
+    g_up_rt = _up(_rt(g))
+    g_dn_lf = _dn(_lf(g))
+    df_dy = g
+    out = g.clone()
+
+    def nom_den(hub):
+        big = hub > d
+        safe = torch.where(big, hub, torch.ones_like(hub))
+        nom = torch.where(big, d / safe, torch.ones_like(hub))
+        den = torch.where(big, nom / (2.0 * safe * safe), torch.zeros_like(hub))
+        return nom, den
+
+    # triangle anchored at (h-1, w)   :655-686
+    a = yk - y_up
+    hub = torch.sqrt(a * a * wts.wy_0 + (y_up - y_up_rt) * (y_up - y_up_rt) * wts.wx_2)
+    nom, den = nom_den(hub)
+    out = out - (df_dy - g_up) * (wts.wy_0 * nom)
+    temp = -den * 2.0 * a * wts.wy_0
+    out = out - (df_dy - g_up) * wts.wy_0 * a * temp
+    out = out - (g_up_rt - g_up) * wts.wx_2 * (y_up_rt - y_up) * temp
+    # triangle anchored at (h, w-1)   :687-720
+    a = yk - y_lf
+    hub = torch.sqrt(a * a * wts.wx_0 + (y_lf - y_dn_lf) * (y_lf - y_dn_lf) * wts.wy_2)
+    nom, den = nom_den(hub)
+    out = out - (df_dy - g_lf) * (wts.wx_0 * nom)
+    temp = -den * 2.0 * a * wts.wx_0
+    out = out - (df_dy - g_lf) * wts.wx_0 * a * temp
+    out = out - (g_dn_lf - g_lf) * wts.wy_2 * (y_dn_lf - y_lf) * temp
+    # triangle anchored at (h, w)     :722-770
+    ax = yk - y_rt
+    ay = yk - y_dn
+    wx2 = ax * ax * wts.wx_1
+    wy2 = ay * ay * wts.wy_1
+    hub = torch.sqrt(wx2 + wy2)
+    nom, den = nom_den(hub)
+    out = out - (df_dy - g_dn) * (wts.wy_1 * nom)
+    out = out - (df_dy - g_rt) * (wts.wx_1 * nom)
+    temp = den * 2.0 * ((y_dn - yk) * wts.wy_1 + (y_rt - yk) * wts.wx_1)
+    out = out - (df_dy - g_dn) * wts.wy_1 * ay * temp
+    out = out - (df_dy - g_rt) * wts.wx_1 * ax * temp
+    # with den == 0 and nom == 1 the Huber-active expressions (:751-759) reduce to the inactive ones (:766-769)
+    dgwx = -LOCAL_GX_MULT * ax * ((df_dy - g_rt) * (nom - wx2 * den) - (df_dy - g_dn) * ax * ay * den * wts.wy_1)
+    dgwy = -LOCAL_GX_MULT * ay * ((df_dy - g_dn) * (nom - wy2 * den) - (df_dy - g_rt) * ay * ax * den * wts.wx_1)
+    dgwx = torch.where(wts.mask_x, dgwx, torch.zeros_like(dgwx)).sum(dim=1, keepdim=True)
+    dgwy = torch.where(wts.mask_y, dgwy, torch.zeros_like(dgwy)).sum(dim=1, keepdim=True)
+    return out, dgwx, dgwy
+
+
+def reverse_iteration(y, g_in, acc, x05, b, c, wts: _Weights, t: float):
+    """One launch of the reverse kernel (TVInpaintFista.cu:586-859; :862-1126 is the same with y = checkpoint).
+
+    g_in : gradient w.r.t. x^{k+3/2}   (d_gxk05_in)
+    acc  : pending momentum term       (d_gxk on entry)
+    Returns (g_out, df_dxk, acc_next, dgc, dgb, dgwx, dgwy)."""
+    df_dy_t, dgwx, dgwy = laplacian_transpose(y, g_in, wts)
+    df_dxk = acc + (1.0 + t) * df_dy_t                         # :796
+    df_dxk = torch.clamp(df_dxk, -CLIP_LOCAL_GRAD, CLIP_LOCAL_GRAD)   # :798
+    acc_next = -t * df_dy_t                                    # :801
+    g_out, dgc, dgb = _prox_reverse(df_dxk, x05, b, c)
+    return g_out, df_dxk, acc_next, dgc, dgb, dgwx, dgwy
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# per-id state and the stateful gradient conditioner
+# ---------------------------------------------------------------------------------------------------------------
+@dataclass
+class IdState:
+    """idStruct (TVInpaintFista.h:7-50): one slot per layer instance, keyed by the user's id 0..9."""
+    run: int = 0
+    av: dict = field(default_factory=lambda: {"C": 0.0, "X": 0.0, "Y": 0.0, "B": 0.0, "I": 0.0})
+    ckpts: Optional[list] = None
+    its: int = 0
+    shape: Optional[tuple] = None
+
+
+def check_grad_update(g: torch.Tensor, av_current: float) -> Tuple[torch.Tensor, float]:
+    """NaN/Inf -> 0, |g| > 1e7 -> 0, and the running mean of |g| (TVInpaintFista.cu:158-175)."""
+    flat = g.reshape(-1).clone()
+    valid = torch.isfinite(flat)
+    if bool(valid.all()):
+        tca = flat.abs().to(torch.float64)
+        av = float(tca.mean()) if flat.numel() else 0.0
+        flat[tca > MAX_TOLERANCE] = 0
+        return flat.reshape(g.shape), av
+    av = 0.0
+    vals = flat.tolist()
+    for i, v in enumerate(vals):                       # the sequential form matters once an entry is invalid
+        if math.isfinite(v):
+            tca = abs(v)
+            step = i / (i + 1.0)
+            av = (1.0 - step) * tca + step * av
+            if tca > MAX_TOLERANCE:
+                vals[i] = 0.0
+        else:
+            vals[i] = 0.0
+            av = av_current * 1000.0
+    return torch.tensor(vals, dtype=g.dtype).reshape(g.shape), av
+
+
+def update_correct_av_step(run: int, av_gc: float, av_state: float, g: torch.Tensor, run_step: float):
+    """Spike kill / rescale against the per-id running mean (TVInpaintFista.cu:128-155). Returns (g, new_state)."""
+    if run >= 10 and av_state * KILL_T < av_gc:
+        return torch.zeros_like(g), av_state * run_step + (1.0 - run_step) * SCALE_T * av_state
+    if run >= 10 and av_state * SCALE_T < av_gc:
+        mult = SCALE_T * av_state / av_gc
+        return g * mult, av_state * run_step + (1.0 - run_step) * av_gc * mult
+    return g, av_state * run_step + (1.0 - run_step) * av_gc
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# backward host driver
+# ---------------------------------------------------------------------------------------------------------------
+def tv_backward_raw(wx, wy, c, b, grad_out, its: int, ckpts, dtype=torch.float64, exact: bool = False,
+                    state: Optional[IdState] = None, init=None):
+    """Host loop of TVInpaintFista::backward (TVInpaintFista.cu:1570-1831).
+
+    exact=False reproduces the reference including its approximations:
+      (1) at the first iteration of every checkpoint segment the Laplacian Jacobian is evaluated at the
+          checkpointed y_g instead of y_{g+1} (:1724-1727),
+      (2) the returned init gradient is dL/dx_1 (:1816),
+      (7) y_{g+1} is re-derived from two stored x^{k+1/2} with rederive_y (:1708, :1717).
+    exact=True stores the true y iterates, uses them everywhere and back-propagates the first gradient step to
+    init as well; it exists to validate the reverse math against autograd and is not a reference behaviour.
+
+    Returns (g_wx, g_wy, g_c, g_b, g_init)."""
+    b = b.to(dtype)
+    c = c.to(dtype)
+    wts = _prepare_weights(wx, wy, dtype)
+    grad_in = grad_out.to(dtype).clone()
+    grad_in[~torch.isfinite(grad_in)] = 0                 # :1609-1623
+    sched = checkpoint_schedule(its)
+    steps = step_sizes(its)
+    f64 = torch.float64
+    gc_store = torch.zeros(c.shape, dtype=f64)            # the host double accumulators :1663-1666
+    gx_store = torch.zeros(c.shape, dtype=f64)
+    gy_store = torch.zeros(c.shape, dtype=f64)
+    gb_store = torch.zeros(b.shape, dtype=f64)
+    zeros_b = lambda: torch.zeros_like(b)
+    g05 = [zeros_b(), zeros_b()]      # d_gxk05_0_temp, d_gxk05_1_temp
+    gxk = [zeros_b(), zeros_b()]      # d_gxk0_temp, d_gxk1_temp   (both zero-filled at :1644-1645)
+    last_it = its
+    first = True
+    for outer in range(len(sched) - 1, -1, -1):
+        next_last = sched[outer]
+        y, x = ckpts[outer]
+        y = y.clone()
+        x = x.clone()
+        y_ckpt = y.clone()
+        npairs = (last_it - next_last) // 2
+        x05s = []
+        ys = [y.clone()]                     # ys[j] = input of local iteration j (exact mode)
+        for j in range(2 * npairs):          # :1678-1687
+            y, x, x05 = forward_iteration(y, x, b, c, wts, steps[next_last + j])
+            x05s.append(x05)
+            ys.append(y.clone())
+        dgc = torch.zeros_like(c)            # device fp32 accumulators, zeroed every segment (:193-217)
+        dgx = torch.zeros_like(c)
+        dgy = torch.zeros_like(c)
+        dgb = torch.zeros_like(b)
+        for it in range(npairs - 1, -1, -1):
+            # ---- odd local index (:1698-1712)
+            j = 2 * it + 1
+            t = steps[next_last + j]
+            if first:
+                first = False
+                g_out, a, bb = _prox_reverse(grad_in, x05s[j], b, c)      # seed kernel :222-287
+                g05[1] = g_out
+                dgc = dgc + a
+                dgb = dgb + bb
+            else:
+                yk = ys[j + 1] if exact else rederive_y(x05s[j], x05s[j - 1], b, c, t)
+                g_out, dfx, acc, a, bb, ax, ay = reverse_iteration(yk, g05[0], gxk[0], x05s[j], b, c, wts, t)
+                g05[1] = g_out
+                gxk[0] = dfx
+                gxk[1] = acc
+                dgc = dgc + a
+                dgb = dgb + bb
+                dgx = dgx + ax
+                dgy = dgy + ay
+            # ---- even local index (:1714-1728)
+            j = 2 * it
+            t = steps[next_last + j]
+            if it > 0:
+                yk = ys[j + 1] if exact else rederive_y(x05s[j], x05s[j - 1], b, c, t)
+            else:
+                yk = ys[1] if exact else y_ckpt
+            g_out, dfx, acc, a, bb, ax, ay = reverse_iteration(yk, g05[1], gxk[1], x05s[j], b, c, wts, t)
+            g05[0] = g_out
+            gxk[1] = dfx
+            gxk[0] = acc
+            dgc = dgc + a
+            dgb = dgb + bb
+            dgx = dgx + ax
+            dgy = dgy + ay
+        gc_store += dgc.to(f64)               # copy_and_set_to_0 :1730
+        gx_store += dgx.to(f64)
+        gy_store += dgy.to(f64)
+        gb_store += dgb.to(f64)
+        last_it = next_last
+    g_init = gxk[1].clone()                   # :1785, :1816
+    if exact:
+        # true gradient w.r.t. init: y_0 = init feeds the first gradient step; t_0 = 0 so x_0 has no other path
+        y0 = ckpts[0][0].to(dtype)
+        g_init, ax, ay = laplacian_transpose(y0, g05[0], wts)
+        gx_store += ax.to(f64)
+        gy_store += ay.to(f64)
+    # ---- sanitiser + conditioner (:1760-1792)
+    st = state if state is not None else IdState()
+    run_step = min(MEMORY_T, st.run / (st.run + 1.0))
+    outs = {}
+    for key, g in (("C", gc_store), ("X", gx_store), ("Y", gy_store), ("B", gb_store), ("I", g_init)):
+        g2, av = check_grad_update(g, st.av[key])
+        g2, st.av[key] = update_correct_av_step(st.run, av, st.av[key], g2, run_step)
+        outs[key] = g2
+    st.run += 1                                # :1829
+    g_c = (outs["C"] * GLOBAL_G_MULT).to(dtype)                      # :1795-1813
+    g_wx = (outs["X"] * GLOBAL_G_MULT).to(dtype) * LIPSCHITZ_INV     # :1817
+    g_wy = (outs["Y"] * GLOBAL_G_MULT).to(dtype) * LIPSCHITZ_INV     # :1818
+    g_b = (outs["B"] * GLOBAL_G_MULT).to(dtype)
+    return g_wx, g_wy, g_c, g_b, outs["I"].to(dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the reference's static C++ interface, id slots included (TVInpaintFista.h:71-96)
+# ---------------------------------------------------------------------------------------------------------------
+class TVInpaintFistaRef:
+    """forward(id) fills the checkpoint slot that backward(id) consumes; ids outside 0..9 are an error (return 1
+    in the reference, ValueError here)."""
+
+    def __init__(self, dtype=torch.float64):
+        self.dtype = dtype
+        self.ids = [IdState() for _ in range(NUM_IDS)]
+
+    def forward(self, wx, wy, c, b, init, its: int, pid: int):
+        if not 0 <= pid < NUM_IDS:
+            raise ValueError(f"id {pid} outside 0..{NUM_IDS - 1}")      # :1468-1472
+        sol, ckpts = tv_forward_raw(wx, wy, c, b, init, its, self.dtype)
+        st = self.ids[pid]
+        st.ckpts, st.its, st.shape = ckpts, its, tuple(b.shape)
+        return sol
+
+    def backward(self, grad_out, wx, wy, c, b, its: int, pid: int):
+        if not 0 <= pid < NUM_IDS:
+            raise ValueError(f"id {pid} outside 0..{NUM_IDS - 1}")      # :1580-1584
+        st = self.ids[pid]
+        if st.ckpts is None or st.its != its or st.shape != tuple(b.shape):
+            raise RuntimeError("backward(id) needs a preceding forward(id) with the same its and shape")
+        return tv_backward_raw(wx, wy, c, b, grad_out, its, st.ckpts, self.dtype, state=st)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# independent restatement used only to pin the vectorised forward: plain loops over pixels, written from the
+# per-pixel description of the iteration rather than from the vectorised code above.
+# ---------------------------------------------------------------------------------------------------------------
+def forward_iteration_loops(y, x_prev, b, c, wx, wy, t):
+    """Single-problem (C,H,W) per-pixel loop version of one forward iteration, float64 numpy.
+
+    wx[h][w] couples (h,w)-(h,w+1), wy[h][w] couples (h,w)-(h+1,w); both unscaled (the function applies L)."""
+    y = np.asarray(y, dtype=np.float64)
+    C, H, W = y.shape
+    L = LIPSCHITZ_INV
+    d = HUBER_DELTA
+
+    def Y(ch, h, w):
+        return y[ch, h, w] if (0 <= h < H and 0 <= w < W) else 0.0
+
+    def WX(h, w):
+        return wx[h, w] * L if (0 <= h < H and 0 <= w < W - 1) else 0.0
+
+    def WY(h, w):
+        return wy[h, w] * L if (0 <= h < H - 1 and 0 <= w < W) else 0.0
+
+    def s(ch, h, w):       # Huber factor of the forward-difference triangle anchored at (h, w)
+        T = math.sqrt(WX(h, w) * (Y(ch, h, w) - Y(ch, h, w + 1)) ** 2 + WY(h, w) * (Y(ch, h, w) - Y(ch, h + 1, w)) ** 2)
+        return 1.0 / max(1.0, T / d)
+
+    y_next = np.zeros_like(y)
+    x_next = np.zeros_like(y)
+    x05_out = np.zeros_like(y)
+    for ch in range(C):
+        for h in range(H):
+            for w in range(W):
+                yc = y[ch, h, w]
+                v = yc
+                v -= s(ch, h, w) * (WY(h, w) * (yc - Y(ch, h + 1, w)) + WX(h, w) * (yc - Y(ch, h, w + 1)))
+                if h > 0:
+                    v -= s(ch, h - 1, w) * WY(h - 1, w) * (yc - Y(ch, h - 1, w))
+                if w > 0:
+                    v -= s(ch, h, w - 1) * WX(h, w - 1) * (yc - Y(ch, h, w - 1))
+                cc = c[h, w]
+                bb = b[ch, h, w]
+                xx = (cc * bb + v) / (1.0 + cc)
+                if v - cc > 1.0 + bb:
+                    xx = v - cc
+                if v + cc < bb - 1.0:
+                    xx = v + cc
+                x05_out[ch, h, w] = v
+                x_next[ch, h, w] = xx
+                y_next[ch, h, w] = xx + t * (xx - x_prev[ch, h, w])
+    return y_next, x_next, x05_out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# synthetic inputs of the benchmark configurations
+# ---------------------------------------------------------------------------------------------------------------
+def _gaussian_smooth(img: torch.Tensor, sigma: float = 2.0, radius: int = 6) -> torch.Tensor:
+    xs = torch.arange(-radius, radius + 1, dtype=torch.float64)
+    k = torch.exp(-0.5 * (xs / sigma) ** 2)
+    k = (k / k.sum()).to(img.dtype)
+    n = img.shape[0]
+    pad = torch.nn.functional.pad
+    r = min(radius, img.shape[-1] - 1)
+    rh = min(radius, img.shape[-2] - 1)
+    mode_w = "reflect" if r == radius else "replicate"
+    mode_h = "reflect" if rh == radius else "replicate"
+    out = torch.nn.functional.conv2d(pad(img, (radius, radius, 0, 0), mode=mode_w), k.view(1, 1, 1, -1))
+    out = torch.nn.functional.conv2d(pad(out, (0, 0, radius, radius), mode=mode_h), k.view(1, 1, -1, 1))
+    assert out.shape[0] == n
+    return out
+
+
+def make_inputs(n: int, ch: int, h: int, w: int, seed: int = 1234, conf_p: float = 0.3):
+    """Seeded synthetic stand-in for optical-flow inpainting inputs (fp32 CPU tensors).
+
+    flow b ~ U(-20, 20); init = b; c = Bernoulli(conf_p) * U(0,1); guide I ~ N(0,1) smoothed (sigma 2);
+    wx = exp(-10 |I[h,w+1]-I[h,w]|), wy = exp(-10 |I[h+1,w]-I[h,w]|), last column / row = 1; upstream grad ~ N(0,1)."""
+    gen = torch.Generator().manual_seed(seed)
+    b = (torch.rand(n, ch, h, w, generator=gen) * 40.0 - 20.0).float()
+    mask = (torch.rand(n, 1, h, w, generator=gen) < conf_p).float()
+    c = (mask * torch.rand(n, 1, h, w, generator=gen)).float()
+    guide = _gaussian_smooth(torch.randn(n, 1, h, w, generator=gen).float())
+    wx = torch.ones(n, 1, h, w)
+    wy = torch.ones(n, 1, h, w)
+    if w > 1:
+        wx[..., :, :-1] = torch.exp(-10.0 * (guide[..., :, 1:] - guide[..., :, :-1]).abs())
+    if h > 1:
+        wy[..., :-1, :] = torch.exp(-10.0 * (guide[..., 1:, :] - guide[..., :-1, :]).abs())
+    grad = torch.randn(n, ch, h, w, generator=gen).float()
+    return {"wx": wx.contiguous(), "wy": wy.contiguous(), "c": c.contiguous(), "b": b.contiguous(),
+            "init": b.clone(), "grad": grad.contiguous()}
