@@ -1,0 +1,35 @@
+// Host-side helpers shared by the translation units of the C-ABI library: error reporting and launch accounting.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "../../include/cnl_b200.h"
+
+namespace cnl {
+
+std::string& last_error_ref();                       // thread-local message storage
+int fail(int code, const char* fmt, ...);            // records the message, returns code
+extern std::atomic<unsigned long long> g_launches;   // kernels enqueued since load
+
+inline int check_cuda(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return CNL_OK;
+    return fail(CNL_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// Counts a launch and turns a launch-configuration error into an error code.
+inline int after_launch(const char* kernel) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return check_cuda(cudaGetLastError(), kernel);
+}
+
+#define CNL_TRY(expr)                 \
+    do {                              \
+        int _rc = (expr);             \
+        if (_rc != CNL_OK) return _rc; \
+    } while (0)
+
+}  // namespace cnl

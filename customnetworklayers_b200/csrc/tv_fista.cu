@@ -1,0 +1,708 @@
+// Unrolled FISTA TV-inpainting layer for sm_100a: kernels, per-id device arenas, host drivers and C entry points.
+//
+// Data flow (all device resident, nothing is copied to the host):
+//   forward : y (ping-pong), x (= the caller's output buffer), history hist[g] = x^{g+1/2} for every iteration g,
+//             and the momentum variable y_g at the reference's checkpoint iterations (needed to reproduce the
+//             reference's segment-start evaluation point, cudaTV/cudaCode/TVInpaintFista.cu:1724-1727).
+//   backward: walks g = last .. 0; y_{g+1} is rebuilt from hist[g], hist[g-1] like the reference does (:1130-1189);
+//             per-pixel gradient accumulators live in the caller's output buffers.
+#include <cmath>
+#include <cstdlib>
+#include <mutex>
+#include <vector>
+
+#include "common.h"
+#include "tv_math.cuh"
+
+namespace cnl {
+
+// ---------------------------------------------------------------------------------------------------------------
+// one-iteration kernels (one thread per pixel, channels looped in-thread, neighbours through L1)
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kBX = 32;
+constexpr int kBY = 8;
+
+struct PixelWeights {
+    float wx_c, wy_c;   // triangle anchored at (h, w)
+    float wx_l, wy_l;   // triangle anchored at (h, w-1)
+    float wx_u, wy_u;   // triangle anchored at (h-1, w)
+};
+
+__device__ __forceinline__ PixelWeights load_weights(const float* __restrict__ wx, const float* __restrict__ wy,
+                                                     int h, int w, int H, int W) {
+    PixelWeights p;
+    const int pix = h * W + w;
+    const bool inx = w < W - 1, iny = h < H - 1;
+    p.wx_c = inx ? kLip * __ldg(wx + pix) : 0.0f;
+    p.wy_c = iny ? kLip * __ldg(wy + pix) : 0.0f;
+    p.wx_l = (w > 0) ? kLip * __ldg(wx + pix - 1) : 0.0f;
+    p.wy_l = (w > 0 && iny) ? kLip * __ldg(wy + pix - 1) : 0.0f;
+    p.wx_u = (h > 0 && inx) ? kLip * __ldg(wx + pix - W) : 0.0f;
+    p.wy_u = (h > 0) ? kLip * __ldg(wy + pix - W) : 0.0f;
+    return p;
+}
+
+struct Stencil7 {
+    float c, r, d, l, u, dl, ur;   // centre, right, down, left, up, down-left, up-right; 0 outside the image
+};
+
+__device__ __forceinline__ Stencil7 load_stencil(const float* __restrict__ a, int h, int w, int H, int W) {
+    Stencil7 s;
+    const int pix = h * W + w;
+    const bool hr = w < W - 1, hd = h < H - 1, hl = w > 0, hu = h > 0;
+    s.c = a[pix];
+    s.r = hr ? a[pix + 1] : 0.0f;
+    s.d = hd ? a[pix + W] : 0.0f;
+    s.l = hl ? a[pix - 1] : 0.0f;
+    s.u = hu ? a[pix - W] : 0.0f;
+    s.dl = (hd && hl) ? a[pix + W - 1] : 0.0f;
+    s.ur = (hu && hr) ? a[pix - W + 1] : 0.0f;
+    return s;
+}
+
+// One FISTA iteration: gradient step on y, Huber prox, momentum extrapolation; stores x^{g+1/2}.
+__global__ void __launch_bounds__(kBX* kBY)
+tv_fwd_iter_kernel(const float* __restrict__ y_in, float* __restrict__ y_out, float* __restrict__ x,
+                   const float* __restrict__ b, const float* __restrict__ c, const float* __restrict__ wx,
+                   const float* __restrict__ wy, float* __restrict__ hist, int C, int H, int W, float t) {
+    const int w = blockIdx.x * kBX + threadIdx.x;
+    const int h = blockIdx.y * kBY + threadIdx.y;
+    if (w >= W || h >= H) return;
+    const size_t plane = (size_t)H * W;
+    const size_t n = blockIdx.z;
+    const int pix = h * W + w;
+    const PixelWeights pw = load_weights(wx + n * plane, wy + n * plane, h, w, H, W);
+    const float conf = __ldg(c + n * plane + pix);
+    for (int ch = 0; ch < C; ++ch) {
+        const size_t off = (n * C + ch) * plane;
+        const Stencil7 y = load_stencil(y_in + off, h, w, H, W);
+        float fx, fy, fxl, fyu, unused;
+        tri_flux(y.c, y.r, y.d, pw.wx_c, pw.wy_c, fx, fy);
+        tri_flux(y.l, y.c, y.dl, pw.wx_l, pw.wy_l, fxl, unused);
+        tri_flux(y.u, y.ur, y.c, pw.wx_u, pw.wy_u, unused, fyu);
+        const float x05 = y.c - fx - fy + fxl + fyu;
+        const float bb = __ldg(b + off + pix);
+        const float xn = prox_huber(x05, bb, conf);
+        const float xp = x[off + pix];
+        hist[off + pix] = x05;
+        x[off + pix] = xn;
+        y_out[off + pix] = xn + t * (xn - xp);
+    }
+}
+
+// Seeds the reverse sweep at the last iteration (TVInpaintFista.cu:222-287): prox Jacobian on the upstream gradient.
+__global__ void __launch_bounds__(256)
+tv_rev_seed_kernel(const float* __restrict__ grad_out, const float* __restrict__ hist_g, const float* __restrict__ b,
+                   const float* __restrict__ c, float* __restrict__ g_out, float* __restrict__ g_c,
+                   float* __restrict__ g_b, int C, size_t plane) {
+    const size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pix >= plane) return;
+    const size_t n = blockIdx.y;
+    const float conf = __ldg(c + n * plane + pix);
+    float dgc = 0.0f;
+    for (int ch = 0; ch < C; ++ch) {
+        const size_t i = (n * C + ch) * plane + pix;
+        float up = grad_out[i];
+        if (!finite_f(up)) up = 0.0f;                       // TVInpaintFista.cu:1616
+        float dgb = 0.0f;
+        g_out[i] = prox_reverse(up, hist_g[i], __ldg(b + i), conf, dgc, dgb);
+        g_b[i] = dgb;
+    }
+    g_c[n * plane + pix] = dgc;
+}
+
+// y_{g+1} from hist[g], hist[g-1] (TVInpaintFista.cu:1130-1189).
+__global__ void __launch_bounds__(256)
+tv_rederive_y_kernel(const float* __restrict__ hist_g, const float* __restrict__ hist_gm1, const float* __restrict__ b,
+                     const float* __restrict__ c, float* __restrict__ y, int C, size_t plane, float t) {
+    const size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pix >= plane) return;
+    const size_t n = blockIdx.y;
+    const float conf = __ldg(c + n * plane + pix);
+    for (int ch = 0; ch < C; ++ch) {
+        const size_t i = (n * C + ch) * plane + pix;
+        y[i] = rederive_y(hist_g[i], hist_gm1[i], __ldg(b + i), conf, t);
+    }
+}
+
+// One reverse iteration (TVInpaintFista.cu:586-859): Laplacian-transpose at y, momentum reverse, prox Jacobian,
+// accumulation of the per-pixel gradients.  `x1bar` (optional) receives dL/dx^{g+1}, the value the reference
+// returns as the init gradient after the last reverse step (:1816).
+__global__ void __launch_bounds__(kBX* kBY)
+tv_rev_iter_kernel(const float* __restrict__ y, const float* __restrict__ g_in, float* __restrict__ g_out,
+                   float* __restrict__ acc, const float* __restrict__ hist_g, const float* __restrict__ b,
+                   const float* __restrict__ c, const float* __restrict__ wx, const float* __restrict__ wy,
+                   float* __restrict__ g_c, float* __restrict__ g_b, float* __restrict__ g_wx,
+                   float* __restrict__ g_wy, float* __restrict__ x1bar, int C, int H, int W, float t) {
+    const int w = blockIdx.x * kBX + threadIdx.x;
+    const int h = blockIdx.y * kBY + threadIdx.y;
+    if (w >= W || h >= H) return;
+    const size_t plane = (size_t)H * W;
+    const size_t n = blockIdx.z;
+    const int pix = h * W + w;
+    const PixelWeights pw = load_weights(wx + n * plane, wy + n * plane, h, w, H, W);
+    const float conf = __ldg(c + n * plane + pix);
+    float dgc = 0.0f, dgwx = 0.0f, dgwy = 0.0f;
+    for (int ch = 0; ch < C; ++ch) {
+        const size_t off = (n * C + ch) * plane;
+        const Stencil7 yy = load_stencil(y + off, h, w, H, W);
+        const Stencil7 gg = load_stencil(g_in + off, h, w, H, W);
+        float p1, p2, p1l, p2u, dwx, dwy, u0, u1, u2;
+        tri_adjoint(yy.c, yy.r, yy.d, gg.c, gg.r, gg.d, pw.wx_c, pw.wy_c, p1, p2, dwx, dwy);
+        tri_adjoint(yy.l, yy.c, yy.dl, gg.l, gg.c, gg.dl, pw.wx_l, pw.wy_l, p1l, u0, u1, u2);
+        tri_adjoint(yy.u, yy.ur, yy.c, gg.u, gg.ur, gg.c, pw.wx_u, pw.wy_u, u0, p2u, u1, u2);
+        dgwx += dwx;
+        dgwy += dwy;
+        const float ybar = gg.c - p1 - p2 + p1l + p2u;
+        const float xbar = clampf(acc[off + pix] + (1.0f + t) * ybar, -kClipLocal, kClipLocal);
+        acc[off + pix] = -t * ybar;
+        float dgb = 0.0f;
+        g_out[off + pix] = prox_reverse(xbar, hist_g[off + pix], __ldg(b + off + pix), conf, dgc, dgb);
+        g_b[off + pix] += dgb;
+        if (x1bar) x1bar[off + pix] = xbar;
+    }
+    g_c[n * plane + pix] += dgc;
+    if (w < W - 1) g_wx[n * plane + pix] += dgwx;
+    if (h < H - 1) g_wy[n * plane + pix] += dgwy;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// finalisation: sanitise, running-mean conditioner, output scalings (TVInpaintFista.cu:128-175, :1760-1818)
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kStatBlocks = 128;     // partial sums per output
+constexpr int kNumOutputs = 5;       // C, X, Y, B, I in the reference's order
+
+struct FinalizeArgs {
+    float* ptr[kNumOutputs];
+    unsigned long long count[kNumOutputs];
+    float scale[kNumOutputs];
+};
+
+// partial[o][blk] = (sum of |g| over finite entries, number of non-finite entries)
+__global__ void __launch_bounds__(256)
+tv_grad_stats_kernel(FinalizeArgs a, double* __restrict__ partial) {
+    const int o = blockIdx.y;
+    const float* p = a.ptr[o];
+    const unsigned long long cnt = a.count[o];
+    double s = 0.0, bad = 0.0;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < cnt;
+         i += (unsigned long long)gridDim.x * blockDim.x) {
+        const float v = p[i];
+        if (finite_f(v)) s += fabs((double)v); else bad += 1.0;
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        s += __shfl_down_sync(0xffffffffu, s, off);
+        bad += __shfl_down_sync(0xffffffffu, bad, off);
+    }
+    __shared__ double sh[2][8];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) { sh[0][wid] = s; sh[1][wid] = bad; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double ts = 0.0, tb = 0.0;
+        for (int i = 0; i < 8; ++i) { ts += sh[0][i]; tb += sh[1][i]; }
+        partial[(o * kStatBlocks + blockIdx.x) * 2 + 0] = ts;
+        partial[(o * kStatBlocks + blockIdx.x) * 2 + 1] = tb;
+    }
+}
+
+// One thread: combines the partials in a fixed order, updates the running means and writes one factor per output.
+// state[0..4] = running means (av_GC, av_GX, av_GY, av_GB, av_GI), factor[0..4] = multiplier for this call.
+__global__ void tv_conditioner_kernel(const double* __restrict__ partial, FinalizeArgs a, double* __restrict__ state,
+                                      float* __restrict__ factor, int run) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const double run_step = fmin(0.975, (double)run / (double)(run + 1));       // :1761
+    for (int o = 0; o < kNumOutputs; ++o) {
+        double s = 0.0, bad = 0.0;
+        for (int i = 0; i < kStatBlocks; ++i) { s += partial[(o * kStatBlocks + i) * 2]; bad += partial[(o * kStatBlocks + i) * 2 + 1]; }
+        double av = state[o];
+        // mean |g|; a non-finite entry makes the reference restart its mean from 1000 x the running mean (:171)
+        const double av_gc = (bad > 0.0) ? av * 1000.0 : (a.count[o] ? s / (double)a.count[o] : 0.0);
+        float f = 1.0f;
+        if (run >= 10 && av * 50.0 < av_gc) {                 // kill (:132-140)
+            f = 0.0f;
+            av = av * run_step + (1.0 - run_step) * 10.0 * av;
+        } else if (run >= 10 && av * 10.0 < av_gc) {          // rescale (:142-150)
+            const double mult = 10.0 * av / av_gc;
+            f = (float)mult;
+            av = av * run_step + (1.0 - run_step) * av_gc * mult;
+        } else {
+            av = av * run_step + (1.0 - run_step) * av_gc;
+        }
+        state[o] = av;
+        factor[o] = f;
+    }
+}
+
+// g = (finite and |g| <= 1e7 ? g : 0) * factor * scale      (:160-171, :1795-1818)
+__global__ void __launch_bounds__(256)
+tv_grad_apply_kernel(FinalizeArgs a, const float* __restrict__ factor) {
+    const int o = blockIdx.y;
+    float* p = a.ptr[o];
+    const unsigned long long cnt = a.count[o];
+    const float f = (factor ? factor[o] : 1.0f);
+    const float sc = a.scale[o];
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < cnt;
+         i += (unsigned long long)gridDim.x * blockDim.x) {
+        float v = p[i];
+        if (!finite_f(v) || fabsf(v) > 10000000.0f) v = 0.0f;
+        p[i] = v * f * sc;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// lambda gradient: out = sum g_c * c_raw, deterministic two-stage reduction
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kDotBlocks = 592;      // 4 x 148 SMs
+
+__global__ void __launch_bounds__(256)
+tv_dot_partial_kernel(const float* __restrict__ a, const float* __restrict__ b, long long count,
+                      float* __restrict__ partial) {
+    double s = 0.0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+        s += (double)a[i] * (double)b[i];
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+    __shared__ double sh[8];
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double ts = 0.0;
+        for (int i = 0; i < 8; ++i) ts += sh[i];
+        // a double partial is stored in two float slots so the scratch stays a float array for the caller
+        reinterpret_cast<double*>(partial)[blockIdx.x] = ts;
+    }
+}
+
+__global__ void __launch_bounds__(32)
+tv_dot_final_kernel(const float* __restrict__ partial, int nblocks, float* __restrict__ out) {
+    const double* p = reinterpret_cast<const double*>(partial);
+    double s = 0.0;
+    for (int i = threadIdx.x; i < nblocks; i += 32) s += p[i];
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+    if (threadIdx.x == 0) out[0] = (float)s;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// per-id slots
+// ---------------------------------------------------------------------------------------------------------------
+struct Slot {
+    float* arena = nullptr;
+    size_t arena_floats = 0;
+    double* cond = nullptr;          // 5 running means + stats partials + 5 float factors (separate small allocation)
+    int n = 0, ch = 0, h = 0, w = 0, its = 0;
+    bool have_forward = false;
+    int run = 0;
+    int opt_conditioner = 1;
+    int opt_fuse = 0;
+    int opt_timing = 0;
+    // timing ring: per recorded call one (start, stop) event pair around the iteration loop and its launch count
+    static constexpr int kRing = 64;
+    cudaEvent_t ev_fwd[kRing][2] = {}, ev_rev[kRing][2] = {};
+    int launches_fwd[kRing] = {}, launches_rev[kRing] = {};
+    int n_fwd = 0, n_rev = 0;
+    bool events_ready = false;
+    std::vector<int> sched;
+    std::vector<float> steps;
+};
+
+struct DeviceSlots {
+    Slot slot[CNL_NUM_IDS];
+};
+
+static std::mutex g_mutex;
+static std::vector<DeviceSlots*> g_devices;      // indexed by CUDA device ordinal
+
+static Slot* get_slot(int id, int* rc) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { *rc = check_cuda(e, "cudaGetDevice"); return nullptr; }
+    if ((size_t)dev >= g_devices.size()) g_devices.resize(dev + 1, nullptr);
+    if (!g_devices[dev]) g_devices[dev] = new DeviceSlots();
+    *rc = CNL_OK;
+    return &g_devices[dev]->slot[id];
+}
+
+static int ensure_events(Slot& s) {
+    if (s.events_ready) return CNL_OK;
+    for (int i = 0; i < Slot::kRing; ++i)
+        for (int j = 0; j < 2; ++j) {
+            CNL_TRY(check_cuda(cudaEventCreate(&s.ev_fwd[i][j]), "cudaEventCreate"));
+            CNL_TRY(check_cuda(cudaEventCreate(&s.ev_rev[i][j]), "cudaEventCreate"));
+        }
+    s.events_ready = true;
+    return CNL_OK;
+}
+
+static size_t arena_budget_floats() {
+    const char* env = std::getenv("CNL_MAX_ARENA_GB");
+    double gb = env ? std::atof(env) : 150.0;
+    if (gb <= 0) gb = 150.0;
+    return (size_t)(gb * 1024.0 * 1024.0 * 1024.0 / 4.0);
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Layout of a slot's arena, in floats.  Every sub-buffer starts on a 256-byte boundary.
+struct ArenaLayout {
+    size_t vol;       // n*ch*h*w rounded up to 64 floats
+    size_t y0, y1, hist, ckpt, ga, gb, acc, ybuf, total;
+};
+
+static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t its_eff, size_t nckpt) {
+    ArenaLayout L;
+    L.vol = align_up(n * ch * h * w, 64);
+    size_t o = 0;
+    L.y0 = o; o += L.vol;
+    L.y1 = o; o += L.vol;
+    L.ga = o; o += L.vol;
+    L.gb = o; o += L.vol;
+    L.acc = o; o += L.vol;
+    L.ybuf = o; o += L.vol;
+    L.ckpt = o; o += L.vol * nckpt;
+    L.hist = o; o += L.vol * its_eff;
+    L.total = o;
+    return L;
+}
+
+static void compute_schedule(int its, std::vector<int>& sched, std::vector<float>& steps) {
+    // checkpoint iterations and momentum table, same double arithmetic as TVInpaintFista.cu:1499-1504, :1525-1532
+    const int n = (int)std::floor(std::sqrt((double)its));
+    sched.resize(n);
+    for (int i = 0; i < n; ++i) sched[i] = (int)(std::floor(i * std::sqrt((double)its) * 0.5) * 2);
+    steps.resize(its);
+    double t = 1.0, t_ = 1.0;
+    for (int i = 0; i < its; ++i) {
+        t_ = t;
+        t = (1.0 + std::sqrt(1.0 + 4.0 * t * t)) / 2.0;
+        steps[i] = (float)std::max(0.0, (t_ - 1.0) / t);
+    }
+}
+
+static int check_common(const void* const* ptrs, int nptr, int n, int ch, int h, int w, int its, int id) {
+    if (id < 0 || id >= CNL_NUM_IDS)
+        return fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1);
+    if (n < 1 || ch < 1 || h < 1 || w < 1)
+        return fail(CNL_ERR_BAD_SHAPE, "n, ch, h, w must be >= 1 (got %d, %d, %d, %d)", n, ch, h, w);
+    if ((long long)h * w > 0x3fffffffLL || n > 65535)
+        return fail(CNL_ERR_BAD_SHAPE, "image of %d x %d pixels or batch %d is beyond the supported range", h, w, n);
+    if (its < 2) return fail(CNL_ERR_BAD_ITS, "its must be >= 2 (got %d)", its);
+    for (int i = 0; i < nptr; ++i)
+        if (!ptrs[i]) return fail(CNL_ERR_NULL, "null pointer argument (position %d)", i);
+    return CNL_OK;
+}
+
+static int ensure_arena(Slot& s, size_t floats) {
+    if (s.arena && s.arena_floats >= floats) return CNL_OK;
+    if (floats > arena_budget_floats())
+        return fail(CNL_ERR_ALLOC, "iterate history needs %.2f GB, above the CNL_MAX_ARENA_GB budget",
+                    floats * 4.0 / (1024.0 * 1024.0 * 1024.0));
+    if (s.arena) {
+        CNL_TRY(check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
+        cudaFree(s.arena);
+        s.arena = nullptr;
+        s.arena_floats = 0;
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, floats * sizeof(float));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(CNL_ERR_ALLOC, "cudaMalloc of %.2f GB failed: %s", floats * 4.0 / (1024.0 * 1024.0 * 1024.0),
+                    cudaGetErrorString(e));
+    }
+    s.arena = static_cast<float*>(p);
+    s.arena_floats = floats;
+    return CNL_OK;
+}
+
+constexpr size_t kCondDoubles = kNumOutputs + (size_t)kNumOutputs * kStatBlocks * 2 + 4;   // means, partials, factors
+
+static int ensure_cond(Slot& s) {
+    if (s.cond) return CNL_OK;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, kCondDoubles * sizeof(double));
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(CNL_ERR_ALLOC, "cudaMalloc (conditioner state) failed"); }
+    s.cond = static_cast<double*>(p);
+    return check_cuda(cudaMemset(s.cond, 0, kCondDoubles * sizeof(double)), "cudaMemset");
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// host drivers
+// ---------------------------------------------------------------------------------------------------------------
+static int tv_forward_impl(const float* wx, const float* wy, const float* c, const float* b, const float* init,
+                           float* out, int n, int ch, int h, int w, int its, int id, cudaStream_t st) {
+    const void* ptrs[] = {wx, wy, c, b, init, out};
+    CNL_TRY(check_common(ptrs, 6, n, ch, h, w, its, id));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    if (!sp) return rc;
+    Slot& s = *sp;
+    s.have_forward = false;
+    compute_schedule(its, s.sched, s.steps);
+    const int its_eff = 2 * (its / 2);
+    const ArenaLayout L = make_layout(n, ch, h, w, its_eff, s.sched.size());
+    CNL_TRY(ensure_arena(s, L.total));
+    const size_t vol_bytes = (size_t)n * ch * h * w * sizeof(float);
+    float* y0 = s.arena + L.y0;
+    float* y1 = s.arena + L.y1;
+    CNL_TRY(check_cuda(cudaMemcpyAsync(out, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->x"));
+    CNL_TRY(check_cuda(cudaMemcpyAsync(y0, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->y"));
+    const dim3 block(kBX, kBY);
+    const dim3 grid((w + kBX - 1) / kBX, (h + kBY - 1) / kBY, n);
+    size_t next_ckpt = 0;
+    const bool timing = s.opt_timing && s.n_fwd < Slot::kRing;
+    const unsigned long long launches0 = g_launches.load();
+    if (timing) {
+        CNL_TRY(ensure_events(s));
+        CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][0], st), "cudaEventRecord"));
+    }
+    for (int g = 0; g < its_eff; ++g) {
+        float* yin = (g & 1) ? y1 : y0;
+        float* yout = (g & 1) ? y0 : y1;
+        if (next_ckpt < s.sched.size() && s.sched[next_ckpt] == g) {
+            CNL_TRY(check_cuda(cudaMemcpyAsync(s.arena + L.ckpt + next_ckpt * L.vol, yin, vol_bytes,
+                                               cudaMemcpyDeviceToDevice, st), "checkpoint y"));
+            ++next_ckpt;
+        }
+        tv_fwd_iter_kernel<<<grid, block, 0, st>>>(yin, yout, out, b, c, wx, wy, s.arena + L.hist + (size_t)g * L.vol,
+                                                   ch, h, w, s.steps[g]);
+        CNL_TRY(after_launch("tv_fwd_iter_kernel"));
+    }
+    if (timing) {
+        CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][1], st), "cudaEventRecord"));
+        s.launches_fwd[s.n_fwd] = (int)(g_launches.load() - launches0);
+        s.n_fwd += 1;
+    }
+    s.n = n; s.ch = ch; s.h = h; s.w = w; s.its = its;
+    s.have_forward = true;
+    return CNL_OK;
+}
+
+static int tv_backward_impl(const float* wx, const float* wy, const float* c, const float* b, const float* grad_out,
+                            float* g_wx, float* g_wy, float* g_c, float* g_b, float* g_init,
+                            int n, int ch, int h, int w, int its, int id, cudaStream_t st) {
+    const void* ptrs[] = {wx, wy, c, b, grad_out, g_wx, g_wy, g_c, g_b, g_init};
+    CNL_TRY(check_common(ptrs, 10, n, ch, h, w, its, id));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    if (!sp) return rc;
+    Slot& s = *sp;
+    if (!s.have_forward || s.n != n || s.ch != ch || s.h != h || s.w != w || s.its != its)
+        return fail(CNL_ERR_NO_FORWARD, "backward(id=%d) needs a preceding forward(id=%d) with the same shape and its",
+                    id, id);
+    CNL_TRY(ensure_cond(s));
+    const int its_eff = 2 * (its / 2);
+    const ArenaLayout L = make_layout(n, ch, h, w, its_eff, s.sched.size());
+    const size_t plane = (size_t)h * w;
+    const size_t vol_bytes = (size_t)n * ch * plane * sizeof(float);
+    const size_t map_bytes = (size_t)n * plane * sizeof(float);
+    float* ga = s.arena + L.ga;      // d_gxk05_0_temp
+    float* gb = s.arena + L.gb;      // d_gxk05_1_temp
+    float* acc = s.arena + L.acc;
+    float* ybuf = s.arena + L.ybuf;
+    const float* hist = s.arena + L.hist;
+    CNL_TRY(check_cuda(cudaMemsetAsync(acc, 0, vol_bytes, st), "zero acc"));
+    CNL_TRY(check_cuda(cudaMemsetAsync(g_wx, 0, map_bytes, st), "zero g_wx"));
+    CNL_TRY(check_cuda(cudaMemsetAsync(g_wy, 0, map_bytes, st), "zero g_wy"));
+
+    const dim3 block(kBX, kBY);
+    const dim3 grid((w + kBX - 1) / kBX, (h + kBY - 1) / kBY, n);
+    const dim3 pgrid((unsigned)((plane + 255) / 256), n);
+    int ckpt_idx = (int)s.sched.size() - 1;
+    const bool timing = s.opt_timing && s.n_rev < Slot::kRing;
+    const unsigned long long launches0 = g_launches.load();
+    if (timing) {
+        CNL_TRY(ensure_events(s));
+        CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][0], st), "cudaEventRecord"));
+    }
+    for (int g = its_eff - 1; g >= 0; --g) {
+        const float t = s.steps[g];
+        const float* hg = hist + (size_t)g * L.vol;
+        float* gout = (g & 1) ? gb : ga;
+        const float* gin = (g & 1) ? ga : gb;
+        if (g == its_eff - 1) {
+            tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hg, b, c, gout, g_c, g_b, ch, plane);
+            CNL_TRY(after_launch("tv_rev_seed_kernel"));
+            continue;
+        }
+        const float* yk;
+        while (ckpt_idx >= 0 && s.sched[ckpt_idx] > g) --ckpt_idx;
+        if (ckpt_idx >= 0 && s.sched[ckpt_idx] == g) {
+            yk = s.arena + L.ckpt + (size_t)ckpt_idx * L.vol;      // segment start: the checkpointed y_g (:1724-1727)
+        } else {
+            tv_rederive_y_kernel<<<pgrid, 256, 0, st>>>(hg, hg - L.vol, b, c, ybuf, ch, plane, t);
+            CNL_TRY(after_launch("tv_rederive_y_kernel"));
+            yk = ybuf;
+        }
+        tv_rev_iter_kernel<<<grid, block, 0, st>>>(yk, gin, gout, acc, hg, b, c, wx, wy, g_c, g_b, g_wx, g_wy,
+                                                   g == 0 ? g_init : nullptr, ch, h, w, t);
+        CNL_TRY(after_launch("tv_rev_iter_kernel"));
+    }
+    if (timing) {
+        CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][1], st), "cudaEventRecord"));
+        s.launches_rev[s.n_rev] = (int)(g_launches.load() - launches0);
+        s.n_rev += 1;
+    }
+
+    FinalizeArgs fa;
+    fa.ptr[0] = g_c;  fa.count[0] = (unsigned long long)n * plane;      fa.scale[0] = kGlobalG;
+    fa.ptr[1] = g_wx; fa.count[1] = (unsigned long long)n * plane;      fa.scale[1] = kGlobalG * kLip;
+    fa.ptr[2] = g_wy; fa.count[2] = (unsigned long long)n * plane;      fa.scale[2] = kGlobalG * kLip;
+    fa.ptr[3] = g_b;  fa.count[3] = (unsigned long long)n * ch * plane; fa.scale[3] = kGlobalG;
+    fa.ptr[4] = g_init; fa.count[4] = (unsigned long long)n * ch * plane; fa.scale[4] = 1.0f;
+    double* state = s.cond;
+    double* partial = s.cond + kNumOutputs;
+    float* factor = reinterpret_cast<float*>(s.cond + kNumOutputs + (size_t)kNumOutputs * kStatBlocks * 2);
+    if (s.opt_conditioner) {
+        tv_grad_stats_kernel<<<dim3(kStatBlocks, kNumOutputs), 256, 0, st>>>(fa, partial);
+        CNL_TRY(after_launch("tv_grad_stats_kernel"));
+        tv_conditioner_kernel<<<1, 32, 0, st>>>(partial, fa, state, factor, s.run);
+        CNL_TRY(after_launch("tv_conditioner_kernel"));
+    }
+    tv_grad_apply_kernel<<<dim3(296, kNumOutputs), 256, 0, st>>>(fa, s.opt_conditioner ? factor : nullptr);
+    CNL_TRY(after_launch("tv_grad_apply_kernel"));
+    s.run += 1;
+    return CNL_OK;
+}
+
+}  // namespace cnl
+
+// ---------------------------------------------------------------------------------------------------------------
+// C entry points
+// ---------------------------------------------------------------------------------------------------------------
+using namespace cnl;
+
+extern "C" int cnl_tv_forward(const float* wx, const float* wy, const float* c, const float* b, const float* init,
+                              float* out, int n, int ch, int h, int w, int its, int id, void* stream) {
+    return tv_forward_impl(wx, wy, c, b, init, out, n, ch, h, w, its, id, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cnl_tv_backward(const float* wx, const float* wy, const float* c, const float* b,
+                               const float* grad_out, float* g_wx, float* g_wy, float* g_c, float* g_b,
+                               float* g_init, int n, int ch, int h, int w, int its, int id, void* stream) {
+    return tv_backward_impl(wx, wy, c, b, grad_out, g_wx, g_wy, g_c, g_b, g_init, n, ch, h, w, its, id,
+                            static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cnl_tv_release(int id) {
+    if (id < 0 || id >= CNL_NUM_IDS) return fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    if (!sp) return rc;
+    CNL_TRY(check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
+    if (sp->arena) cudaFree(sp->arena);
+    if (sp->cond) cudaFree(sp->cond);
+    if (sp->events_ready)
+        for (int i = 0; i < Slot::kRing; ++i)
+            for (int j = 0; j < 2; ++j) { cudaEventDestroy(sp->ev_fwd[i][j]); cudaEventDestroy(sp->ev_rev[i][j]); }
+    const int keep_cond = sp->opt_conditioner, keep_fuse = sp->opt_fuse;
+    *sp = Slot();
+    sp->opt_conditioner = keep_cond;
+    sp->opt_fuse = keep_fuse;
+    return CNL_OK;
+}
+
+static int read_iterate(int id, int idx, bool checkpoint, float* dst, void* stream) {
+    if (id < 0 || id >= CNL_NUM_IDS) return fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1);
+    if (!dst) return fail(CNL_ERR_NULL, "null destination");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    if (!sp) return rc;
+    if (!sp->have_forward) return fail(CNL_ERR_NO_FORWARD, "slot %d holds no forward pass", id);
+    const int its_eff = 2 * (sp->its / 2);
+    const int limit = checkpoint ? (int)sp->sched.size() : its_eff;
+    if (idx < 0 || idx >= limit) return fail(CNL_ERR_BAD_SHAPE, "index %d is outside 0..%d", idx, limit - 1);
+    const ArenaLayout L = make_layout(sp->n, sp->ch, sp->h, sp->w, its_eff, sp->sched.size());
+    const float* src = sp->arena + (checkpoint ? L.ckpt : L.hist) + (size_t)idx * L.vol;
+    const size_t bytes = (size_t)sp->n * sp->ch * sp->h * sp->w * sizeof(float);
+    return check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)),
+                      "copy stored iterate");
+}
+
+extern "C" int cnl_tv_read_history(int id, int g, float* dst, void* stream) {
+    return read_iterate(id, g, false, dst, stream);
+}
+
+extern "C" int cnl_tv_read_checkpoint(int id, int k, float* dst, void* stream) {
+    return read_iterate(id, k, true, dst, stream);
+}
+
+extern "C" int cnl_tv_num_checkpoints(int id) {
+    if (id < 0 || id >= CNL_NUM_IDS) { fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1); return -1; }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    if (!sp || !sp->have_forward) return -1;
+    return (int)sp->sched.size();
+}
+
+extern "C" int cnl_tv_set_option(int id, int option, int value) {
+    if (id < 0 || id >= CNL_NUM_IDS) return fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    if (!sp) return rc;
+    switch (option) {
+        case CNL_OPT_CONDITIONER: sp->opt_conditioner = value ? 1 : 0; return CNL_OK;
+        case CNL_OPT_TIMING:
+            sp->opt_timing = value ? 1 : 0;
+            sp->n_fwd = sp->n_rev = 0;
+            return CNL_OK;
+        case CNL_OPT_FUSE:
+            if (value < 0 || value > 4) return fail(CNL_ERR_BAD_OPTION, "fuse factor %d is outside 0..4", value);
+            sp->opt_fuse = value;
+            return CNL_OK;
+        default: return fail(CNL_ERR_BAD_OPTION, "unknown option %d", option);
+    }
+}
+
+extern "C" int cnl_tv_get_timing(int id, double* out_host) {
+    if (id < 0 || id >= CNL_NUM_IDS) return fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1);
+    if (!out_host) return fail(CNL_ERR_NULL, "null output");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    if (!sp) return rc;
+    double ms_f = 0, ms_r = 0, lf = 0, lr = 0;
+    for (int i = 0; i < sp->n_fwd; ++i) {
+        float ms = 0;
+        CNL_TRY(check_cuda(cudaEventSynchronize(sp->ev_fwd[i][1]), "cudaEventSynchronize"));
+        CNL_TRY(check_cuda(cudaEventElapsedTime(&ms, sp->ev_fwd[i][0], sp->ev_fwd[i][1]), "cudaEventElapsedTime"));
+        ms_f += ms; lf += sp->launches_fwd[i];
+    }
+    for (int i = 0; i < sp->n_rev; ++i) {
+        float ms = 0;
+        CNL_TRY(check_cuda(cudaEventSynchronize(sp->ev_rev[i][1]), "cudaEventSynchronize"));
+        CNL_TRY(check_cuda(cudaEventElapsedTime(&ms, sp->ev_rev[i][0], sp->ev_rev[i][1]), "cudaEventElapsedTime"));
+        ms_r += ms; lr += sp->launches_rev[i];
+    }
+    out_host[0] = ms_f; out_host[1] = lf; out_host[2] = sp->n_fwd;
+    out_host[3] = ms_r; out_host[4] = lr; out_host[5] = sp->n_rev;
+    sp->n_fwd = sp->n_rev = 0;
+    return CNL_OK;
+}
+
+extern "C" int cnl_tv_run_count(int id) {
+    if (id < 0 || id >= CNL_NUM_IDS) { fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1); return -1; }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    return sp ? sp->run : -1;
+}
+
+extern "C" int cnl_dot_scratch_floats(void) { return 2 * kDotBlocks; }
+
+extern "C" int cnl_tv_lambda_grad(const float* g_c, const float* c_raw, long long count, float* out, float* scratch,
+                                  void* stream) {
+    if (!g_c || !c_raw || !out || !scratch) return fail(CNL_ERR_NULL, "null pointer argument");
+    if (count < 0) return fail(CNL_ERR_BAD_SHAPE, "negative element count");
+    if ((reinterpret_cast<size_t>(scratch) & 7) != 0) return fail(CNL_ERR_BAD_SHAPE, "scratch must be 8-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    tv_dot_partial_kernel<<<kDotBlocks, 256, 0, st>>>(g_c, c_raw, count, scratch);
+    CNL_TRY(after_launch("tv_dot_partial_kernel"));
+    tv_dot_final_kernel<<<1, 32, 0, st>>>(scratch, kDotBlocks, out);
+    return after_launch("tv_dot_final_kernel");
+}

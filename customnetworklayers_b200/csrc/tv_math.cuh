@@ -1,0 +1,108 @@
+// Per-pixel arithmetic of the Huber-TV FISTA iteration and of its reverse sweep, shared by every kernel.
+//
+// Formulation.  The reference gathers three Huber-weighted "triangles" per pixel
+// (cudaTV/cudaCode/TVInpaintFista.cu:1247-1274).  Here each triangle, anchored at pixel p with edges to p+x and
+// p+y, is evaluated once and produces two fluxes
+//     fx(p) = s(p) wx(p) (y[p]-y[p+x]),   fy(p) = s(p) wy(p) (y[p]-y[p+y]),   s = min(1, delta / sqrt(A)),
+//     A(p) = wx(p) (y[p]-y[p+x])^2 + wy(p) (y[p]-y[p+y])^2,
+// and the gradient step is the divergence  x05[p] = y[p] - fx(p) - fy(p) + fx(p-x) + fy(p-y).
+// The reverse sweep has the same shape with adjoint fluxes phi1, phi2 (TVInpaintFista.cu:651-771).
+// Weights are pre-multiplied by 1/8 and are zero across the image border (TVInpaintFista.cu:1204-1211, :1478).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace cnl {
+
+constexpr float kDelta = 0.1f;            // __HDelta1__     TVInpaintFista.cu:44
+constexpr float kClipLocal = 10000.0f;    // clipLocalGrad   :52
+constexpr float kLocalGC = 0.1f;          // localGCMult     :63
+constexpr float kLocalGX = 0.1f;          // localGXMult     :65
+constexpr float kLocalGB = 1.0f;          // localGBMult     :67
+constexpr float kGlobalG = 0.1f;          // globalGMult     :69
+constexpr float kLip = 0.125f;            // 1/Lipschitz     :1478
+
+// Fluxes of the forward-difference triangle anchored at a pixel.
+__device__ __forceinline__ void tri_flux(float yc, float yr, float yd, float wx, float wy, float& fx, float& fy) {
+    const float d1 = yc - yr;
+    const float d2 = yc - yd;
+    const float A = wx * d1 * d1 + wy * d2 * d2;
+    const float T = sqrtf(A);
+    const float s = (T > kDelta) ? kDelta / T : 1.0f;
+    fx = s * wx * d1;
+    fy = s * wy * d2;
+}
+
+// Huber data-term prox (TVInpaintFista.cu:1288-1292).
+__device__ __forceinline__ float prox_huber(float x05, float b, float c) {
+    float x = (c * b + x05) / (1.0f + c);
+    const float lo = x05 - c;
+    const float hi = x05 + c;
+    if (lo > 1.0f + b) x = lo;
+    if (hi < b - 1.0f) x = hi;
+    return x;
+}
+
+// y^{k+1} rebuilt from two stored pre-prox iterates, exactly as the reference's reverse sweep does
+// (TVInpaintFista.cu:1151-1165): the zone of iterate `it` selects the formula applied to BOTH iterates.
+__device__ __forceinline__ float rederive_y(float x05, float x05m, float b, float c, float t) {
+    const float diff = b - x05;
+    const float sign = (diff < 0.0f) ? -1.0f : 1.0f;
+    if (1.0f + c >= sign * diff) {
+        const float xk = (c * b + x05) / (1.0f + c);
+        const float xkm = (c * b + x05m) / (1.0f + c);
+        return xk + t * (xk - xkm);
+    }
+    const float xk = (c <= sign * diff) ? b - diff + sign * c : b;
+    const float diff2 = b - x05m;
+    const float sign2 = (diff2 < 0.0f) ? -1.0f : 1.0f;
+    const float xkm = (c <= sign2 * diff2) ? b - diff2 + sign2 * c : b;
+    return xk + t * (xk - xkm);
+}
+
+// Adjoint fluxes of one triangle and its contribution to the edge-weight gradients.
+//   e1 = g[p]-g[p+x], e2 = g[p]-g[p+y];  S = wx d1 e1 + wy d2 e2
+//   phi1 = nom wx e1 - 2 den wx d1 S,  phi2 = nom wy e2 - 2 den wy d2 S
+//   dwx  = -kLocalGX d1 (e1 (nom - wx d1^2 den) - e2 d1 d2 den wy)      (TVInpaintFista.cu:751-753)
+//   dwy  = -kLocalGX d2 (e2 (nom - wy d2^2 den) - e1 d2 d1 den wx)      (TVInpaintFista.cu:757-759)
+// with nom = delta/T, den = nom/(2 T^2) when T > delta, else nom = 1, den = 0 (:662-665, :761-769).
+__device__ __forceinline__ void tri_adjoint(float yc, float yr, float yd, float gc, float gr, float gd,
+                                            float wx, float wy, float& phi1, float& phi2, float& dwx, float& dwy) {
+    const float d1 = yc - yr;
+    const float d2 = yc - yd;
+    const float e1 = gc - gr;
+    const float e2 = gc - gd;
+    const float A = wx * d1 * d1 + wy * d2 * d2;
+    const float T = sqrtf(A);
+    float nom = 1.0f, den = 0.0f;
+    if (T > kDelta) {
+        nom = kDelta / T;
+        den = nom / (2.0f * T * T);
+    }
+    const float S = wx * d1 * e1 + wy * d2 * e2;
+    const float k = 2.0f * den * S;
+    phi1 = wx * (nom * e1 - k * d1);
+    phi2 = wy * (nom * e2 - k * d2);
+    dwx = -kLocalGX * d1 * (e1 * (nom - wx * d1 * d1 * den) - e2 * d1 * d2 * den * wy);
+    dwy = -kLocalGX * d2 * (e2 * (nom - wy * d2 * d2 * den) - e1 * d2 * d1 * den * wx);
+}
+
+// Prox Jacobian applied to df_dxk = dL/dx^{k+1} (TVInpaintFista.cu:806-828 and the seed kernel :240-255).
+// Returns dL/dx^{k+1/2}; adds the (locally scaled) confidence and rhs contributions.
+__device__ __forceinline__ float prox_reverse(float df_dxk, float x05, float b, float c, float& dgc, float& dgb) {
+    const float diff = b - x05;
+    const float sign = (diff < 0.0f) ? -1.0f : 1.0f;
+    const float opc = 1.0f + c;
+    if (opc >= sign * diff) {
+        dgc += df_dxk * (b / opc - (c * b + x05) / (opc * opc)) * kLocalGC;
+        dgb += df_dxk * c / opc * kLocalGB;
+        return df_dxk / opc;
+    }
+    dgc += sign * df_dxk * kLocalGC;
+    return df_dxk;
+}
+
+__device__ __forceinline__ float clampf(float v, float lo, float hi) { return fminf(fmaxf(v, lo), hi); }
+
+__device__ __forceinline__ bool finite_f(float v) { return fabsf(v) <= 3.402823466e38f; }   // false for NaN / Inf
+
+}  // namespace cnl

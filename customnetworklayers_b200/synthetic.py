@@ -1,0 +1,43 @@
+"""Seeded synthetic inputs of the benchmark configurations (CPU tensors; no CUDA needed).
+
+They stand in for the optical-flow benchmark images the reference's paper was evaluated on, which are not
+available offline: same shapes and value ranges, generated from a seed."""
+from __future__ import annotations
+
+import torch
+
+def _gaussian_smooth(img: torch.Tensor, sigma: float = 2.0, radius: int = 6) -> torch.Tensor:
+    xs = torch.arange(-radius, radius + 1, dtype=torch.float64)
+    k = torch.exp(-0.5 * (xs / sigma) ** 2)
+    k = (k / k.sum()).to(img.dtype)
+    n = img.shape[0]
+    pad = torch.nn.functional.pad
+    r = min(radius, img.shape[-1] - 1)
+    rh = min(radius, img.shape[-2] - 1)
+    mode_w = "reflect" if r == radius else "replicate"
+    mode_h = "reflect" if rh == radius else "replicate"
+    out = torch.nn.functional.conv2d(pad(img, (radius, radius, 0, 0), mode=mode_w), k.view(1, 1, 1, -1))
+    out = torch.nn.functional.conv2d(pad(out, (0, 0, radius, radius), mode=mode_h), k.view(1, 1, -1, 1))
+    assert out.shape[0] == n
+    return out
+
+
+def make_inputs(n: int, ch: int, h: int, w: int, seed: int = 1234, conf_p: float = 0.3):
+    """Seeded synthetic stand-in for optical-flow inpainting inputs (fp32 CPU tensors).
+
+    flow b ~ U(-20, 20); init = b; c = Bernoulli(conf_p) * U(0,1); guide I ~ N(0,1) smoothed (sigma 2);
+    wx = exp(-10 |I[h,w+1]-I[h,w]|), wy = exp(-10 |I[h+1,w]-I[h,w]|), last column / row = 1; upstream grad ~ N(0,1)."""
+    gen = torch.Generator().manual_seed(seed)
+    b = (torch.rand(n, ch, h, w, generator=gen) * 40.0 - 20.0).float()
+    mask = (torch.rand(n, 1, h, w, generator=gen) < conf_p).float()
+    c = (mask * torch.rand(n, 1, h, w, generator=gen)).float()
+    guide = _gaussian_smooth(torch.randn(n, 1, h, w, generator=gen).float())
+    wx = torch.ones(n, 1, h, w)
+    wy = torch.ones(n, 1, h, w)
+    if w > 1:
+        wx[..., :, :-1] = torch.exp(-10.0 * (guide[..., :, 1:] - guide[..., :, :-1]).abs())
+    if h > 1:
+        wy[..., :-1, :] = torch.exp(-10.0 * (guide[..., 1:, :] - guide[..., :-1, :]).abs())
+    grad = torch.randn(n, ch, h, w, generator=gen).float()
+    return {"wx": wx.contiguous(), "wy": wy.contiguous(), "c": c.contiguous(), "b": b.contiguous(),
+            "init": b.clone(), "grad": grad.contiguous()}

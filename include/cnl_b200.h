@@ -1,0 +1,122 @@
+/*
+ * C ABI of the B200 optimisation layers.  Plain pointers and sizes only; every pointer is a DEVICE pointer on the
+ * current CUDA device unless its name ends in _host.  All calls enqueue work on `stream` (a cudaStream_t passed
+ * as void*) and return without synchronising the host unless stated otherwise.
+ *
+ * Return value: 0 on success, one of the CNL_ERR_* codes otherwise; cnl_last_error() gives a message for the
+ * calling thread's last failure.
+ *
+ * Tensor layouts (row-major, fp32):
+ *   b, init, out, grad_out, g_b, g_init : [n][ch][h][w]
+ *   wx, wy, c, g_wx, g_wy, g_c          : [n][1][h][w]
+ *   wx[h][w] couples pixel (h,w) with (h,w+1); wy[h][w] couples (h,w) with (h+1,w).
+ */
+#ifndef CNL_B200_H
+#define CNL_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CNL_OK 0
+#define CNL_ERR_BAD_ID 1      /* id outside 0..9: same code the reference returns (cudaTV/cudaCode/TVInpaintFista.cu:1468-1472) */
+#define CNL_ERR_BAD_SHAPE 2   /* n, ch, h or w < 1, or sizes beyond the supported range */
+#define CNL_ERR_BAD_ITS 3     /* fewer than 2 iterations */
+#define CNL_ERR_NO_FORWARD 4  /* backward(id) without a matching forward(id) (same n, ch, h, w, its) */
+#define CNL_ERR_ALLOC 5       /* device allocation failed or the history would exceed the configured budget */
+#define CNL_ERR_CUDA 6        /* a CUDA runtime call or kernel launch reported an error */
+#define CNL_ERR_NULL 7        /* a required pointer is null */
+#define CNL_ERR_BAD_OPTION 8
+
+#define CNL_NUM_IDS 10        /* __uniqueIds__, cudaTV/cudaCode/TVInpaintFista.h:5 */
+
+/* options for cnl_tv_set_option */
+#define CNL_OPT_CONDITIONER 1   /* 1 (default): stateful spike kill / rescale of returned gradients after 10 runs
+                                   (cudaTV/cudaCode/TVInpaintFista.cu:128-155, :1760-1792); 0: off */
+#define CNL_OPT_FUSE 2          /* iterations fused per launch: 0 = automatic (default), 1 = one launch per iteration,
+                                   2..4 = fixed temporal-blocking factor */
+
+#define CNL_OPT_TIMING 3        /* 1: bracket the forward and the reverse iteration loop of every call with CUDA events on
+                                   the caller's stream (up to 64 calls are kept); setting the option clears the records */
+
+/*
+ * Forward pass of the unrolled FISTA TV-inpainting layer: 2*floor(its/2) iterations starting from x = y = init.
+ * Replaces  static int TVInpaintFista::forward(float* d_dx, float* d_dy, float* d_c, float* d_b, float* d_i,
+ * float* d_solution, int ic, int ih, int iw, int its, int id)   (cudaTV/cudaCode/TVInpaintFista.h:71-72,
+ * TVInpaintFista.cu:1463-1559), extended by a leading batch dimension n and an explicit stream.
+ * Stores the iterate history that cnl_tv_backward(id) consumes in the slot `id` (0..9) of the current device.
+ * Inputs are not modified.
+ */
+int cnl_tv_forward(const float* wx, const float* wy, const float* c, const float* b, const float* init,
+                   float* out, int n, int ch, int h, int w, int its, int id, void* stream);
+
+/*
+ * Hand-derived reverse sweep.  Replaces  static int TVInpaintFista::backward(float* d_dx, float* d_dy, float* d_c,
+ * float* d_b, float* d_inGrad, float* d_outGradX, float* d_outGradY, float* d_outGradC, float* d_outGradB,
+ * float* d_outGradI, int ic, int ih, int iw, int its, int id)   (cudaTV/cudaCode/TVInpaintFista.h:81-85,
+ * TVInpaintFista.cu:1570-1831).  The five outputs are overwritten.  Returned scalings follow the reference:
+ * g_c and g_wx/g_wy carry 0.01 x the true gradient, g_b 0.1 x, g_init is the gradient w.r.t. the first primal
+ * iterate.  Non-finite entries of grad_out are treated as 0.
+ */
+int cnl_tv_backward(const float* wx, const float* wy, const float* c, const float* b, const float* grad_out,
+                    float* g_wx, float* g_wy, float* g_c, float* g_b, float* g_init,
+                    int n, int ch, int h, int w, int its, int id, void* stream);
+
+/*
+ * Frees the device memory held by slot `id` on the current device and resets its run counter and running means.
+ * Replaces idStruct::free_buf (cudaTV/cudaCode/TVInpaintFista.h:23-37).  Synchronises the device.
+ */
+int cnl_tv_release(int id);
+
+/*
+ * Copies one stored iterate of the last forward(id) into dst (device memory, n*ch*h*w floats):
+ *   cnl_tv_read_history   : x^{g+1/2}, the pre-prox iterate of iteration g, 0 <= g < 2*floor(its/2)
+ *                           (the reference's d_xk05, cudaTV/cudaCode/TVInpaintFista.cu:1414, :1660)
+ *   cnl_tv_read_checkpoint: the momentum variable y at the k-th checkpoint iteration floor(k*sqrt(its)/2)*2
+ *                           (the reference's intermediate_y[k], TVInpaintFista.cu:1504, :1543)
+ * Used by the parity tests to run the oracle's reverse sweep on exactly the iterates the device produced.
+ */
+int cnl_tv_read_history(int id, int g, float* dst, void* stream);
+int cnl_tv_read_checkpoint(int id, int k, float* dst, void* stream);
+int cnl_tv_num_checkpoints(int id);
+
+/* Per-slot options (see CNL_OPT_*).  No reference counterpart beyond its compile-time #defines
+ * (cudaTV/cudaCode/TVInpaintFista.cu:22-90). */
+int cnl_tv_set_option(int id, int option, int value);
+
+/*
+ * Reads and clears the CUDA-event records made under CNL_OPT_TIMING.  out_host (HOST memory, 6 doubles) receives
+ * {forward loop ms (summed over recorded calls), kernel launches inside those loops, recorded forward calls,
+ *  reverse loop ms, launches, recorded backward calls}.  Waits for the recorded events.  No reference counterpart
+ * (the reference has no timing code).
+ */
+int cnl_tv_get_timing(int id, double* out_host);
+
+/* Number of forward+backward pairs completed on slot `id` (idStruct::run, cudaTV/cudaCode/TVInpaintFista.h:39);
+ * negative on error. */
+int cnl_tv_run_count(int id);
+
+/* Kernel launches enqueued by this library on the calling thread's process since load (for benchmark accounting). */
+unsigned long long cnl_launch_count(void);
+
+/*
+ * Gradient of the loss w.r.t. a scalar lambda that multiplies a raw confidence map (c = lambda * c_raw):
+ * out[0] = sum_i g_c[i] * c_raw[i], a deterministic two-stage shuffle reduction.  This is the one value the
+ * data-parallel layer all-reduces.  The reference has no learned scalar; its per-pixel confidence gradient is
+ * d_outGradC (cudaTV/cudaCode/TVInpaintFista.cu:1795-1798).
+ * `scratch` must hold at least cnl_dot_scratch_floats() floats of device memory.
+ */
+int cnl_tv_lambda_grad(const float* g_c, const float* c_raw, long long count, float* out, float* scratch,
+                       void* stream);
+int cnl_dot_scratch_floats(void);
+
+/* Message for the last error on the calling thread ("" if none). */
+const char* cnl_last_error(void);
+
+/* Library version string. */
+const char* cnl_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CNL_B200_H */

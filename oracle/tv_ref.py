@@ -186,6 +186,26 @@ def tv_forward_raw(wx, wy, c, b, init, its: int, dtype=torch.float64):
     return x, ckpts
 
 
+def tv_forward_history(wx, wy, c, b, init, its: int, dtype=torch.float64):
+    """Forward pass that also returns every pre-prox iterate: (solution, hist [its_eff,N,C,H,W], ckpt_y [K,N,C,H,W]).
+
+    hist[g] is what the reference's recomputation stores in d_xk05 (:1414); ckpt_y[i] is intermediate_y[i] (:1543)."""
+    b = b.to(dtype)
+    c = c.to(dtype)
+    wts = _prepare_weights(wx, wy, dtype)
+    x = init.to(dtype).clone()
+    y = init.to(dtype).clone()
+    sched = checkpoint_schedule(its)
+    steps = step_sizes(its)
+    hist, cks = [], []
+    for g in range(effective_iterations(its)):
+        if g in sched:
+            cks.append(y.clone())
+        y, x, x05 = forward_iteration(y, x, b, c, wts, steps[g])
+        hist.append(x05)
+    return x, torch.stack(hist), torch.stack(cks)
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # reverse sweep
 # ---------------------------------------------------------------------------------------------------------------
@@ -356,7 +376,7 @@ def update_correct_av_step(run: int, av_gc: float, av_state: float, g: torch.Ten
 # backward host driver
 # ---------------------------------------------------------------------------------------------------------------
 def tv_backward_raw(wx, wy, c, b, grad_out, its: int, ckpts, dtype=torch.float64, exact: bool = False,
-                    state: Optional[IdState] = None, init=None):
+                    state: Optional[IdState] = None, hist=None, ckpt_y=None):
     """Host loop of TVInpaintFista::backward (TVInpaintFista.cu:1570-1831).
 
     exact=False reproduces the reference including its approximations:
@@ -367,10 +387,17 @@ def tv_backward_raw(wx, wy, c, b, grad_out, its: int, ckpts, dtype=torch.float64
     exact=True stores the true y iterates, uses them everywhere and back-propagates the first gradient step to
     init as well; it exists to validate the reverse math against autograd and is not a reference behaviour.
 
+    hist / ckpt_y (optional, not with exact=True): a stored history x^{g+1/2} as [its_eff, N, C, H, W] and the
+    checkpointed y as [len(schedule), N, C, H, W].  When given, the segment recomputation (:1678-1687) is skipped
+    and these values are used instead, so a device implementation's reverse sweep can be checked on exactly the
+    iterates it saw (the sweep is discontinuous in y at the Huber thresholds, so two fp32 forward passes that
+    differ in the last bit can legitimately produce visibly different gradients).
+
     Returns (g_wx, g_wy, g_c, g_b, g_init)."""
     b = b.to(dtype)
     c = c.to(dtype)
     wts = _prepare_weights(wx, wy, dtype)
+    assert not (exact and hist is not None)
     grad_in = grad_out.to(dtype).clone()
     grad_in[~torch.isfinite(grad_in)] = 0                 # :1609-1623
     sched = checkpoint_schedule(its)
@@ -387,17 +414,22 @@ def tv_backward_raw(wx, wy, c, b, grad_out, its: int, ckpts, dtype=torch.float64
     first = True
     for outer in range(len(sched) - 1, -1, -1):
         next_last = sched[outer]
-        y, x = ckpts[outer]
-        y = y.clone()
-        x = x.clone()
-        y_ckpt = y.clone()
         npairs = (last_it - next_last) // 2
-        x05s = []
-        ys = [y.clone()]                     # ys[j] = input of local iteration j (exact mode)
-        for j in range(2 * npairs):          # :1678-1687
-            y, x, x05 = forward_iteration(y, x, b, c, wts, steps[next_last + j])
-            x05s.append(x05)
-            ys.append(y.clone())
+        if hist is not None:
+            y_ckpt = ckpt_y[outer].to(dtype)
+            x05s = [hist[next_last + j].to(dtype) for j in range(2 * npairs)]
+            ys = None
+        else:
+            y, x = ckpts[outer]
+            y = y.clone()
+            x = x.clone()
+            y_ckpt = y.clone()
+            x05s = []
+            ys = [y.clone()]                     # ys[j] = input of local iteration j (exact mode)
+            for j in range(2 * npairs):          # :1678-1687
+                y, x, x05 = forward_iteration(y, x, b, c, wts, steps[next_last + j])
+                x05s.append(x05)
+                ys.append(y.clone())
         dgc = torch.zeros_like(c)            # device fp32 accumulators, zeroed every segment (:193-217)
         dgx = torch.zeros_like(c)
         dgy = torch.zeros_like(c)
@@ -545,41 +577,5 @@ def forward_iteration_loops(y, x_prev, b, c, wx, wy, t):
     return y_next, x_next, x05_out
 
 
-# ---------------------------------------------------------------------------------------------------------------
-# synthetic inputs of the benchmark configurations
-# ---------------------------------------------------------------------------------------------------------------
-def _gaussian_smooth(img: torch.Tensor, sigma: float = 2.0, radius: int = 6) -> torch.Tensor:
-    xs = torch.arange(-radius, radius + 1, dtype=torch.float64)
-    k = torch.exp(-0.5 * (xs / sigma) ** 2)
-    k = (k / k.sum()).to(img.dtype)
-    n = img.shape[0]
-    pad = torch.nn.functional.pad
-    r = min(radius, img.shape[-1] - 1)
-    rh = min(radius, img.shape[-2] - 1)
-    mode_w = "reflect" if r == radius else "replicate"
-    mode_h = "reflect" if rh == radius else "replicate"
-    out = torch.nn.functional.conv2d(pad(img, (radius, radius, 0, 0), mode=mode_w), k.view(1, 1, 1, -1))
-    out = torch.nn.functional.conv2d(pad(out, (0, 0, radius, radius), mode=mode_h), k.view(1, 1, -1, 1))
-    assert out.shape[0] == n
-    return out
-
-
-def make_inputs(n: int, ch: int, h: int, w: int, seed: int = 1234, conf_p: float = 0.3):
-    """Seeded synthetic stand-in for optical-flow inpainting inputs (fp32 CPU tensors).
-
-    flow b ~ U(-20, 20); init = b; c = Bernoulli(conf_p) * U(0,1); guide I ~ N(0,1) smoothed (sigma 2);
-    wx = exp(-10 |I[h,w+1]-I[h,w]|), wy = exp(-10 |I[h+1,w]-I[h,w]|), last column / row = 1; upstream grad ~ N(0,1)."""
-    gen = torch.Generator().manual_seed(seed)
-    b = (torch.rand(n, ch, h, w, generator=gen) * 40.0 - 20.0).float()
-    mask = (torch.rand(n, 1, h, w, generator=gen) < conf_p).float()
-    c = (mask * torch.rand(n, 1, h, w, generator=gen)).float()
-    guide = _gaussian_smooth(torch.randn(n, 1, h, w, generator=gen).float())
-    wx = torch.ones(n, 1, h, w)
-    wy = torch.ones(n, 1, h, w)
-    if w > 1:
-        wx[..., :, :-1] = torch.exp(-10.0 * (guide[..., :, 1:] - guide[..., :, :-1]).abs())
-    if h > 1:
-        wy[..., :-1, :] = torch.exp(-10.0 * (guide[..., 1:, :] - guide[..., :-1, :]).abs())
-    grad = torch.randn(n, ch, h, w, generator=gen).float()
-    return {"wx": wx.contiguous(), "wy": wy.contiguous(), "c": c.contiguous(), "b": b.contiguous(),
-            "init": b.clone(), "grad": grad.contiguous()}
+# synthetic inputs live with the package (the benchmark needs them without importing the oracle)
+from customnetworklayers_b200.synthetic import make_inputs  # noqa: E402,F401
