@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "common.h"
+#include "tv_fused.cuh"
 #include "tv_math.cuh"
 
 namespace cnl {
@@ -345,7 +346,7 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 // Layout of a slot's arena, in floats.  Every sub-buffer starts on a 256-byte boundary.
 struct ArenaLayout {
     size_t vol;       // n*ch*h*w rounded up to 64 floats
-    size_t y0, y1, hist, ckpt, ga, gb, acc, ybuf, total;
+    size_t y0, y1, xbuf, hist, ckpt, ga, gb, acc, acc2, ybuf, total;
 };
 
 static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t its_eff, size_t nckpt) {
@@ -357,6 +358,8 @@ static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t i
     L.ga = o; o += L.vol;
     L.gb = o; o += L.vol;
     L.acc = o; o += L.vol;
+    L.acc2 = o; o += L.vol;
+    L.xbuf = o; o += L.vol;
     L.ybuf = o; o += L.vol;
     L.ckpt = o; o += L.vol * nckpt;
     L.hist = o; o += L.vol * its_eff;
@@ -445,6 +448,54 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
     const size_t vol_bytes = (size_t)n * ch * h * w * sizeof(float);
     float* y0 = s.arena + L.y0;
     float* y1 = s.arena + L.y1;
+    const void* aligned[] = {wx, wy, c, b, init, out, s.arena};
+    int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
+    if (fuse > 1 && fused_supported(w, aligned, 7)) {
+        // temporally blocked path: `fuse` iterations per launch; x and y ping-pong between launches so that no CTA
+        // reads a halo another CTA is writing, and the last launch writes x into the caller's buffer
+        const bool timing = s.opt_timing && s.n_fwd < Slot::kRing;
+        const unsigned long long launches0 = g_launches.load();
+        if (timing) {
+            CNL_TRY(ensure_events(s));
+            CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][0], st), "cudaEventRecord"));
+        }
+        const int nlaunch = (its_eff + fuse - 1) / fuse;
+        float* xbuf = s.arena + L.xbuf;
+        const float* y_in = init;
+        const float* x_in = init;
+        size_t next_ckpt = 0;
+        for (int i = 0, g0 = 0; i < nlaunch; ++i) {
+            const int K = std::min(fuse, its_eff - g0);
+            FwdFusedParams fp{};
+            fp.y_in = y_in; fp.x_in = x_in;
+            fp.y_out = (i & 1) ? y1 : y0;
+            fp.x_out = ((nlaunch - 1 - i) & 1) ? xbuf : out;
+            fp.b = b; fp.c = c; fp.wx = wx; fp.wy = wy;
+            fp.N = n; fp.C = ch; fp.H = h; fp.W = w;
+            for (int j = 0; j < K; ++j) {
+                const int g = g0 + j;
+                fp.hist[j] = s.arena + L.hist + (size_t)g * L.vol;
+                fp.t[j] = s.steps[g];
+                fp.ckpt[j] = nullptr;
+                if (next_ckpt < s.sched.size() && s.sched[next_ckpt] == g) {
+                    fp.ckpt[j] = s.arena + L.ckpt + next_ckpt * L.vol;
+                    ++next_ckpt;
+                }
+            }
+            CNL_TRY(launch_tv_fwd_fused(fp, K, st));
+            y_in = fp.y_out;
+            x_in = fp.x_out;
+            g0 += K;
+        }
+        if (timing) {
+            CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][1], st), "cudaEventRecord"));
+            s.launches_fwd[s.n_fwd] = (int)(g_launches.load() - launches0);
+            s.n_fwd += 1;
+        }
+        s.n = n; s.ch = ch; s.h = h; s.w = w; s.its = its;
+        s.have_forward = true;
+        return CNL_OK;
+    }
     CNL_TRY(check_cuda(cudaMemcpyAsync(out, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->x"));
     CNL_TRY(check_cuda(cudaMemcpyAsync(y0, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->y"));
     const dim3 block(kBX, kBY);
@@ -509,35 +560,70 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     const dim3 block(kBX, kBY);
     const dim3 grid((w + kBX - 1) / kBX, (h + kBY - 1) / kBY, n);
     const dim3 pgrid((unsigned)((plane + 255) / 256), n);
-    int ckpt_idx = (int)s.sched.size() - 1;
     const bool timing = s.opt_timing && s.n_rev < Slot::kRing;
     const unsigned long long launches0 = g_launches.load();
     if (timing) {
         CNL_TRY(ensure_events(s));
         CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][0], st), "cudaEventRecord"));
     }
-    for (int g = its_eff - 1; g >= 0; --g) {
-        const float t = s.steps[g];
-        const float* hg = hist + (size_t)g * L.vol;
-        float* gout = (g & 1) ? gb : ga;
-        const float* gin = (g & 1) ? ga : gb;
-        if (g == its_eff - 1) {
-            tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hg, b, c, gout, g_c, g_b, ch, plane);
-            CNL_TRY(after_launch("tv_rev_seed_kernel"));
-            continue;
+    auto ckpt_of = [&](int g) -> const float* {
+        for (size_t i = 0; i < s.sched.size(); ++i)
+            if (s.sched[i] == g) return s.arena + L.ckpt + i * L.vol;      // segment start: the checkpointed y_g (:1724-1727)
+        return nullptr;
+    };
+    // seed at the last iteration (its_eff - 1 is odd, so the seed lands in the "odd" buffer like the reference's)
+    {
+        const int g = its_eff - 1;
+        tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hist + (size_t)g * L.vol, b, c, gb, g_c, g_b, ch, plane);
+        CNL_TRY(after_launch("tv_rev_seed_kernel"));
+    }
+    const void* aligned[] = {wx, wy, c, b, g_wx, g_wy, g_c, g_b, g_init, s.arena};
+    const int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
+    if (fuse > 1 && fused_supported(w, aligned, 10)) {
+        float* acc2 = s.arena + L.acc2;
+        const float* g_cur = gb;
+        const float* acc_cur = acc;
+        int flip = 0;
+        for (int g0 = its_eff - 2; g0 >= 0;) {
+            const int K = std::min(fuse, g0 + 1);
+            RevFusedParams rp{};
+            rp.g_in = g_cur; rp.acc_in = acc_cur;
+            rp.g_out = flip ? gb : ga;
+            rp.acc_out = flip ? acc : acc2;
+            rp.b = b; rp.c = c; rp.wx = wx; rp.wy = wy;
+            rp.g_c = g_c; rp.g_b = g_b; rp.g_wx = g_wx; rp.g_wy = g_wy;
+            rp.N = n; rp.C = ch; rp.H = h; rp.W = w;
+            for (int j = 0; j <= K; ++j) {
+                const int g = g0 - j;
+                rp.hist[j] = g >= 0 ? hist + (size_t)g * L.vol : nullptr;
+                if (j < K) {
+                    rp.t[j] = s.steps[g];
+                    rp.ckpt[j] = ckpt_of(g);
+                }
+            }
+            rp.x1bar = (g0 - K + 1 == 0) ? g_init : nullptr;
+            CNL_TRY(launch_tv_rev_fused(rp, K, st));
+            g_cur = rp.g_out;
+            acc_cur = rp.acc_out;
+            flip ^= 1;
+            g0 -= K;
         }
-        const float* yk;
-        while (ckpt_idx >= 0 && s.sched[ckpt_idx] > g) --ckpt_idx;
-        if (ckpt_idx >= 0 && s.sched[ckpt_idx] == g) {
-            yk = s.arena + L.ckpt + (size_t)ckpt_idx * L.vol;      // segment start: the checkpointed y_g (:1724-1727)
-        } else {
-            tv_rederive_y_kernel<<<pgrid, 256, 0, st>>>(hg, hg - L.vol, b, c, ybuf, ch, plane, t);
-            CNL_TRY(after_launch("tv_rederive_y_kernel"));
-            yk = ybuf;
+    } else {
+        for (int g = its_eff - 2; g >= 0; --g) {
+            const float t = s.steps[g];
+            const float* hg = hist + (size_t)g * L.vol;
+            float* gout = (g & 1) ? gb : ga;
+            const float* gin = (g & 1) ? ga : gb;
+            const float* yk = ckpt_of(g);
+            if (!yk) {
+                tv_rederive_y_kernel<<<pgrid, 256, 0, st>>>(hg, hg - L.vol, b, c, ybuf, ch, plane, t);
+                CNL_TRY(after_launch("tv_rederive_y_kernel"));
+                yk = ybuf;
+            }
+            tv_rev_iter_kernel<<<grid, block, 0, st>>>(yk, gin, gout, acc, hg, b, c, wx, wy, g_c, g_b, g_wx, g_wy,
+                                                       g == 0 ? g_init : nullptr, ch, h, w, t);
+            CNL_TRY(after_launch("tv_rev_iter_kernel"));
         }
-        tv_rev_iter_kernel<<<grid, block, 0, st>>>(yk, gin, gout, acc, hg, b, c, wx, wy, g_c, g_b, g_wx, g_wy,
-                                                   g == 0 ? g_init : nullptr, ch, h, w, t);
-        CNL_TRY(after_launch("tv_rev_iter_kernel"));
     }
     if (timing) {
         CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][1], st), "cudaEventRecord"));

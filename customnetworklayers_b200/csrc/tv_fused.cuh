@@ -1,0 +1,63 @@
+// Register-tiled, temporally blocked TV-FISTA kernels: interface between the host driver and tv_fused.cu.
+//
+// Geometry shared by the forward and the reverse kernel.  A CTA of 16 warps owns a region of 32 rows x 128 columns
+// of one image; warp w owns rows 2w, 2w+1 and lane l owns columns 4l..4l+3 of them, so every global access is one
+// aligned 16-byte vector per lane and 512 contiguous bytes per warp.  K iterations are fused per launch: the
+// region's outer K rows (4 columns) are a halo that is recomputed redundantly and never written back, so the
+// interior that a CTA stores is (32-2K) x 120 pixels.  Horizontal neighbours travel by warp shuffle, vertical
+// neighbours across warps through two 512-byte rows of shared memory per warp; all pointwise state of the
+// iteration lives in registers.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace cnl {
+
+constexpr int kFuseMax = 4;          // iterations fused per launch at most (= column halo)
+constexpr int kRegionH = 32;
+constexpr int kRegionW = 128;
+constexpr int kHaloX = 4;
+constexpr int kTileW = kRegionW - 2 * kHaloX;     // 120
+
+struct FwdFusedParams {
+    const float* y_in;
+    const float* x_in;
+    float* y_out;
+    float* x_out;
+    const float* b;
+    const float* c;
+    const float* wx;
+    const float* wy;
+    float* hist[kFuseMax];      // destination of x^{g+1/2} for each fused iteration
+    float* ckpt[kFuseMax];      // if non-null: y before fused iteration j is stored here (checkpoint)
+    float t[kFuseMax];          // momentum factors
+    int N, C, H, W;
+};
+
+struct RevFusedParams {
+    const float* g_in;          // dL/dx^{g+3/2} entering the first fused reverse iteration
+    float* g_out;
+    const float* acc_in;        // pending momentum term
+    float* acc_out;
+    const float* b;
+    const float* c;
+    const float* wx;
+    const float* wy;
+    const float* hist[kFuseMax + 1];   // hist[j] = x^{g_j+1/2} of fused reverse step j (g_j = g_first - j); hist[K] = one older
+    const float* ckpt[kFuseMax];       // if non-null: y is read from here instead of being rebuilt (segment start)
+    float t[kFuseMax];
+    float* g_c;
+    float* g_b;
+    float* g_wx;
+    float* g_wy;
+    float* x1bar;               // if non-null: dL/dx of the last fused step is stored here (init gradient)
+    int N, C, H, W;
+};
+
+// True if the fused kernels can run on this shape / these pointers (16-byte vectors need W % 4 == 0).
+bool fused_supported(int W, const void* const* ptrs, int nptr);
+
+// Enqueue K (1..kFuseMax) fused iterations.  Return 0 or a CNL_ERR_* code.
+int launch_tv_fwd_fused(const FwdFusedParams& p, int K, cudaStream_t st);
+int launch_tv_rev_fused(const RevFusedParams& p, int K, cudaStream_t st);
+
+}  // namespace cnl

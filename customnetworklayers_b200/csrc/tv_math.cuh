@@ -106,3 +106,70 @@ __device__ __forceinline__ float clampf(float v, float lo, float hi) { return fm
 __device__ __forceinline__ bool finite_f(float v) { return fabsf(v) <= 3.402823466e38f; }   // false for NaN / Inf
 
 }  // namespace cnl
+
+// ---------------------------------------------------------------------------------------------------------------
+// Fast variants used by the register-tiled kernels: MUFU reciprocal square root / reciprocal (max 2 ulp) instead of
+// IEEE sqrt and divide.  rsqrtf(0) = +inf makes s = min(1, inf) = 1, the same value the exact form gives.
+// ---------------------------------------------------------------------------------------------------------------
+namespace cnl {
+
+__device__ __forceinline__ void tri_flux_fast(float yc, float yr, float yd, float wx, float wy, float& fx, float& fy) {
+    const float wd1 = wx * (yc - yr);
+    const float wd2 = wy * (yc - yd);
+    const float A = fmaf(wd1, yc - yr, wd2 * (yc - yd));
+    const float s = fminf(1.0f, kDelta * rsqrtf(A));
+    fx = s * wd1;
+    fy = s * wd2;
+}
+
+// prox with the reciprocal of (1 + c) supplied by the caller
+__device__ __forceinline__ float prox_huber_fast(float x05, float b, float c, float inv1pc) {
+    float x = fmaf(c, b, x05) * inv1pc;
+    const float lo = x05 - c;
+    const float hi = x05 + c;
+    if (lo > 1.0f + b) x = lo;
+    if (hi < b - 1.0f) x = hi;
+    return x;
+}
+
+__device__ __forceinline__ float rederive_y_fast(float x05, float x05m, float b, float c, float inv1pc, float t) {
+    const float diff = b - x05;
+    const float ad = fabsf(diff);
+    const float diff2 = b - x05m;
+    const float ad2 = fabsf(diff2);
+    // quadratic zone of iterate `it`: both iterates through the quadratic formula
+    const float xq = fmaf(c, b, x05) * inv1pc;
+    const float xqm = fmaf(c, b, x05m) * inv1pc;
+    // otherwise: both through the soft threshold (b inside the dead zone)
+    const float xl = (c <= ad) ? x05 + copysignf(c, diff) : b;
+    const float xlm = (c <= ad2) ? x05m + copysignf(c, diff2) : b;
+    const bool quad = (1.0f + c >= ad);
+    const float xk = quad ? xq : xl;
+    const float xkm = quad ? xqm : xlm;
+    return fmaf(t, xk - xkm, xk);
+}
+
+__device__ __forceinline__ void tri_adjoint_fast(float yc, float yr, float yd, float gc, float gr, float gd,
+                                                 float wx, float wy, float& phi1, float& phi2, float& dwx, float& dwy) {
+    const float d1 = yc - yr;
+    const float d2 = yc - yd;
+    const float e1 = gc - gr;
+    const float e2 = gc - gd;
+    const float wd1 = wx * d1;
+    const float wd2 = wy * d2;
+    const float A = fmaf(wd1, d1, wd2 * d2);
+    const float r = rsqrtf(A);                   // 1/T
+    const bool big = kDelta * r < 1.0f;          // T > delta
+    const float nom = big ? kDelta * r : 1.0f;
+    const float den = big ? 0.5f * nom * r * r : 0.0f;
+    const float S = fmaf(wd1, e1, wd2 * e2);
+    const float k2 = 2.0f * den * S;
+    phi1 = wx * fmaf(nom, e1, -k2 * d1);
+    phi2 = wy * fmaf(nom, e2, -k2 * d2);
+    // dwx = -kLocalGX d1 (nom e1 - den d1 (wx d1 e1 + wy d2 e2)) ; same for y
+    const float dS = den * S;
+    dwx = -kLocalGX * d1 * fmaf(nom, e1, -dS * d1);
+    dwy = -kLocalGX * d2 * fmaf(nom, e2, -dS * d2);
+}
+
+}  // namespace cnl

@@ -76,6 +76,33 @@ def test_reverse_sweep_matches_oracle_on_device_history(ext, case):
         assert_close(g, r, name)
 
 
+FUSE_CASES = [(2, 2, 40, 72, 20), (1, 3, 33, 64, 21), (1, 2, 64, 96, 100), (2, 1, 7, 8, 6), (1, 2, 100, 260, 14)]
+
+
+@pytest.mark.parametrize("fuse", [1, 2, 3, 4])
+@pytest.mark.parametrize("case", FUSE_CASES, ids=lambda c: "n%d_c%d_%dx%d_its%d" % c)
+def test_every_fuse_factor_matches_oracle(ext, case, fuse):
+    """The temporally blocked kernels (2..4 iterations per launch) and the one-launch-per-iteration kernels must all
+    agree with the oracle; widths are multiples of 4 so the blocked path is the one that runs for fuse > 1."""
+    n, ch, h, w, its = case
+    I = R.make_inputs(n, ch, h, w, seed=777 + h + w + its)
+    D = _dev(I)
+    ext.release(2)
+    ext.set_option(2, 1, 0)
+    ext.set_option(2, 2, fuse)
+    try:
+        sol, hist, cky, grads = _run_cuda(ext, D, its, 2)
+    finally:
+        ext.set_option(2, 2, 0)
+    ref_sol, ref_hist, ref_cky = R.tv_forward_history(I["wx"], I["wy"], I["c"], I["b"], I["init"], its)
+    assert_close(sol, ref_sol, "solution")
+    assert_close(hist, ref_hist, "history")
+    assert_close(cky, ref_cky, "checkpointed y")
+    ref = R.tv_backward_raw(I["wx"], I["wy"], I["c"], I["b"], I["grad"], its, None, hist=hist.cpu(), ckpt_y=cky.cpu())
+    for name, g, r in zip(GRAD_NAMES, grads, ref):
+        assert_close(g, r, name)
+
+
 def test_end_to_end_gradient_gap_is_reported_and_bounded(ext):
     """End to end (oracle recomputes its own fp64 forward) the difference is dominated by threshold flips; it must
     stay within a small multiple of what the fp32 oracle itself shows against the fp64 oracle."""
