@@ -110,6 +110,18 @@ int cnl_tv_lambda_grad(const float* g_c, const float* c_raw, long long count, fl
                        void* stream);
 int cnl_dot_scratch_floats(void);
 
+/*
+ * The same reduction for callers that must not allocate device memory (real-time loops, plugins inside an engine
+ * that owns all device memory): no scratch argument; the block partials live in a 32 KiB array inside the library
+ * that every GPU loading the library holds until exit.  No counterpart in the reference.
+ * Limits: count <= cnl_tv_lambda_grad_static_max_count() (16,777,216), otherwise CNL_ERR_BAD_SHAPE.  All calls on a
+ * device share the array: calls that overlap on the GPU (different streams) race; calls on one stream are safe.
+ * The first call on each device resolves the array's address and should be made outside stream capture.
+ * Allocates nothing (no cudaMalloc / cudaFree).
+ */
+int cnl_tv_lambda_grad_static(const float* g_c, const float* c_raw, long long count, float* out, void* stream);
+long long cnl_tv_lambda_grad_static_max_count(void);
+
 /* Message for the last error on the calling thread ("" if none). */
 const char* cnl_last_error(void);
 
