@@ -136,6 +136,37 @@ def cpu_baseline_sample(ch, h, w, its, budget_s=20.0):
             "sample": f"fp32 torch-CPU oracle, 1 image {ch}x{sh}x{sw}, {its} iterations, fwd+bwd once after a warm-up probe, {dt:.1f} s"}
 
 
+def reference_cuda_sample(ch, h, w, its):
+    """The reference's OWN cudaTV kernels (oracle/_ref/libtvref.so, built unmodified against a small ImageUtilities
+    stand-in) timed on this GPU: one image per call is all the reference supports.  None if not built."""
+    try:
+        from oracle import ref_cuda
+        if not ref_cuda.available() or h % 16 or w % 32:
+            return None
+        import torch
+        from customnetworklayers_b200.synthetic import make_inputs
+        I = make_inputs(1, ch, h, w, seed=1236)
+        D = {k: v.cuda() for k, v in I.items()}
+
+        def once():
+            ref_cuda.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, 9)
+            ref_cuda.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, 9)
+
+        once()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        reps = 2
+        for _ in range(reps):
+            once()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": h * w * 2 * (its // 2) / dt / 1e9, "unit": UNIT, "ms_per_image": dt * 1e3,
+                "sample": f"reference cudaTV kernels (unmodified, sm_100a build), 1 image {ch}x{h}x{w}, {its} iterations, "
+                          "fwd+bwd, host wall clock around its blocking calls (its checkpoints go through host memory)"}
+    except Exception as e:          # the second checker is optional
+        return {"unavailable": str(e)[:200]}
+
+
 def run_reference_arm(args, rank, world):
     """--impl reference: the reference math on the host cores (oracle port, all threads), same metric and config."""
     if rank != 0:
@@ -175,6 +206,14 @@ def run_reference_arm(args, rank, world):
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    try:
+        import torch as _t
+        if _t.cuda.is_available():
+            rc = reference_cuda_sample(ch, h, w, its)
+            if rc is not None:
+                line["reference_cuda"] = rc
+    except Exception:
+        pass
     print(json.dumps(line), flush=True)
 
 
@@ -185,6 +224,7 @@ def run_ours(args, rank, local_rank, world):
     import torch
     import torch.distributed as dist
     from customnetworklayers_b200 import _lib, tvInpaint_cuda_ext as ext
+    from customnetworklayers_b200.dist import allreduce_scalar_grads
     from customnetworklayers_b200.synthetic import make_inputs
 
     if not torch.cuda.is_available():
@@ -219,8 +259,7 @@ def run_ours(args, rank, local_rank, world):
         sol = ext.forward(D["wx"], D["wy"], c, D["b"], D["init"], its, pid)[0]
         grads = ext.backward(D["grad"], D["wx"], D["wy"], c, D["b"], its, pid)
         g_lam = ext.lambda_grad(grads[2], c_raw)
-        if world > 1:
-            dist.all_reduce(g_lam)
+        allreduce_scalar_grads(g_lam)
         return sol, grads, g_lam
 
     host_out = {"sol": torch.empty_like(host["b"]).pin_memory(),
@@ -233,8 +272,7 @@ def run_ours(args, rank, local_rank, world):
         sol = ext.forward(d["wx"], d["wy"], c, d["b"], d["init"], its, pid)[0]
         grads = ext.backward(d["grad"], d["wx"], d["wy"], c, d["b"], its, pid)
         g_lam = ext.lambda_grad(grads[2], d["c"])
-        if world > 1:
-            dist.all_reduce(g_lam)
+        allreduce_scalar_grads(g_lam)
         host_out["sol"].copy_(sol, non_blocking=True)
         for dst, src in zip(host_out["g"], grads):
             dst.copy_(src, non_blocking=True)
@@ -314,6 +352,9 @@ def run_ours(args, rank, local_rank, world):
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample(ch, h, w, its)
+            rc = reference_cuda_sample(ch, h, w, its)
+            if rc is not None:
+                line["reference_cuda"] = rc
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -207,15 +207,24 @@ tv_grad_stats_kernel(FinalizeArgs a, double* __restrict__ partial) {
     }
 }
 
-// One thread: combines the partials in a fixed order, updates the running means and writes one factor per output.
+// One warp: combines the partials in a fixed order (lane-strided sums + shuffle tree, so the result does not depend
+// on timing), updates the running means and writes one factor per output.
 // state[0..4] = running means (av_GC, av_GX, av_GY, av_GB, av_GI), factor[0..4] = multiplier for this call.
-__global__ void tv_conditioner_kernel(const double* __restrict__ partial, FinalizeArgs a, double* __restrict__ state,
-                                      float* __restrict__ factor, int run) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+__global__ void __launch_bounds__(32)
+tv_conditioner_kernel(const double* __restrict__ partial, FinalizeArgs a, double* __restrict__ state,
+                      float* __restrict__ factor, int run) {
     const double run_step = fmin(0.975, (double)run / (double)(run + 1));       // :1761
     for (int o = 0; o < kNumOutputs; ++o) {
         double s = 0.0, bad = 0.0;
-        for (int i = 0; i < kStatBlocks; ++i) { s += partial[(o * kStatBlocks + i) * 2]; bad += partial[(o * kStatBlocks + i) * 2 + 1]; }
+        for (int i = threadIdx.x; i < kStatBlocks; i += 32) {
+            s += partial[(o * kStatBlocks + i) * 2];
+            bad += partial[(o * kStatBlocks + i) * 2 + 1];
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            s += __shfl_down_sync(0xffffffffu, s, off);
+            bad += __shfl_down_sync(0xffffffffu, bad, off);
+        }
+        if (threadIdx.x != 0) continue;
         double av = state[o];
         // mean |g|; a non-finite entry makes the reference restart its mean from 1000 x the running mean (:171)
         const double av_gc = (bad > 0.0) ? av * 1000.0 : (a.count[o] ? s / (double)a.count[o] : 0.0);

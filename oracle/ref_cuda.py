@@ -1,0 +1,54 @@
+"""ctypes loader for oracle/_ref/libtvref.so: the reference's own cudaTV kernels, built unmodified by
+oracle/build_ref.py.  TEST INFRASTRUCTURE ONLY (second checker on a GPU box, and the reference's own B200 timing).
+
+The reference handles one image per call (batch 1), image height a multiple of 16 and width a multiple of 32."""
+import ctypes
+import os
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "libtvref.so")
+_lib = None
+
+
+def available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def load():
+    global _lib
+    if _lib is None:
+        lib = ctypes.CDLL(LIB_PATH)
+        lib.ref_tv_forward.restype = ctypes.c_int
+        lib.ref_tv_forward.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 5
+        lib.ref_tv_backward.restype = ctypes.c_int
+        lib.ref_tv_backward.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 5
+        _lib = lib
+    return _lib
+
+
+def forward(wx, wy, c, b, init, its, pid):
+    """Tensors are CUDA fp32, shapes [1,1,H,W] / [1,C,H,W]; returns the solution [1,C,H,W]."""
+    import torch
+    assert b.shape[0] == 1
+    _, ch, h, w = b.shape
+    out = torch.zeros_like(b)
+    torch.cuda.synchronize()
+    rc = load().ref_tv_forward(wx.data_ptr(), wy.data_ptr(), c.data_ptr(), b.data_ptr(), init.data_ptr(),
+                               out.data_ptr(), ch, h, w, int(its), int(pid))
+    if rc != 0:
+        raise RuntimeError(f"reference forward returned {rc}")
+    return out
+
+
+def backward(grad, wx, wy, c, b, its, pid):
+    import torch
+    assert b.shape[0] == 1
+    _, ch, h, w = b.shape
+    g = [torch.zeros_like(t) for t in (wx, wy, c, b, b)]
+    grad = grad.clone()          # the reference zeroes non-finite entries of the upstream gradient in place
+    torch.cuda.synchronize()
+    rc = load().ref_tv_backward(wx.data_ptr(), wy.data_ptr(), c.data_ptr(), b.data_ptr(), grad.data_ptr(),
+                                g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), g[3].data_ptr(), g[4].data_ptr(),
+                                ch, h, w, int(its), int(pid))
+    if rc != 0:
+        raise RuntimeError(f"reference backward returned {rc}")
+    return g

@@ -3,9 +3,12 @@
 TEST INFRASTRUCTURE ONLY.  This module is the checker for the CUDA path and the timed CPU baseline of the
 benchmark.  Nothing in the shipped package imports it; the product path has no CPU fallback.
 
-Parity status: PARITY UNPINNED by the reference's own tests -- the reference ships no tests, golden vectors or
-fixtures, and its CUDA sources cannot be built without the un-vendored ImageUtilities library.  What pins this
-restatement instead:
+Parity status: the reference ships no tests, golden vectors or fixtures of its own.  This restatement is pinned
+against OUTPUTS OF THE REFERENCE ITSELF: its unmodified cudaTV kernels, compiled against a small ImageUtilities
+stand-in (oracle/build_ref.py -> oracle/_ref/libtvref.so) and run on a B200, produced the golden vectors in
+tests/golden/tv_reference_cuda.npz (generator: tests/golden/make_golden.py), which this module reproduces to
+~1e-6 in fp64 and fp32 (tests/test_golden.py); tests/test_reference_cuda_gpu.py repeats the comparison live on a
+GPU box.  Independently of that:
   * the reverse-sweep math is checked against ``torch.autograd`` of the forward restatement (``exact=True`` mode),
   * the forward is checked against an independent per-pixel loop restatement (``forward_iteration_loops``),
   * the reference-only approximations ("quirks") are small, separately switchable deltas on top of that.

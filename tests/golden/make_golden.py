@@ -1,0 +1,46 @@
+"""Generates tests/golden/tv_reference_cuda.npz: inputs and outputs of the REFERENCE's own cudaTV kernels
+(oracle/_ref/libtvref.so, built unmodified by oracle/build_ref.py) on a few small problems.  Needs a GPU:
+
+    python tests/golden/make_golden.py gpurun_out/tv_reference_cuda.npz      # on the GPU box
+    cp gpurun_out/tv_reference_cuda.npz tests/golden/                        # back in the working tree
+
+The committed file pins the CPU oracle (tests/test_golden.py, no GPU needed) and the CUDA path."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+CASES = [  # channels, height, width, its, seed
+    (2, 16, 32, 4, 101),
+    (1, 32, 32, 7, 102),
+    (2, 32, 64, 10, 103),
+    (3, 16, 64, 20, 104),
+]
+
+
+def main(out_path):
+    from customnetworklayers_b200.synthetic import make_inputs
+    from oracle import ref_cuda
+    data = {"n_cases": np.array(len(CASES))}
+    for i, (ch, h, w, its, seed) in enumerate(CASES):
+        I = make_inputs(1, ch, h, w, seed=seed)
+        I["init"] = I["b"] + 0.25 * I["grad"].flip(-1)          # an init that differs from b
+        D = {k: v.cuda() for k, v in I.items()}
+        sol = ref_cuda.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, i % 10)
+        grads = ref_cuda.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, i % 10)
+        data[f"case{i}_its"] = np.array(its)
+        for k, v in I.items():
+            data[f"case{i}_{k}"] = v.numpy()
+        data[f"case{i}_sol"] = sol.cpu().numpy()
+        for name, g in zip(("g_wx", "g_wy", "g_c", "g_b", "g_init"), grads):
+            data[f"case{i}_{name}"] = g.cpu().numpy()
+    np.savez_compressed(out_path, **data)
+    print("wrote", out_path, os.path.getsize(out_path), "bytes")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(__file__), "tv_reference_cuda.npz"))
