@@ -262,24 +262,21 @@ def run_ours(args, rank, local_rank, world):
         allreduce_scalar_grads(g_lam)
         return sol, grads, g_lam
 
-    host_out = {"sol": torch.empty_like(host["b"]).pin_memory(),
-                "g": [torch.empty_like(host[k]).pin_memory() for k in ("wx", "wy", "c", "b", "init")],
-                "lam": torch.empty(1).pin_memory()}
+    host_out = {"lam": torch.empty(1).pin_memory()}
+
+    from customnetworklayers_b200.host_pipeline import HostPipeline, tv_fwd_bwd_from_host
+    pipe = HostPipeline(dev)
+    out_keys = ("sol", "g_wx", "g_wy", "g_c", "g_b", "g_init")
+    like = {"sol": "b", "g_wx": "wx", "g_wy": "wy", "g_c": "c", "g_b": "b", "g_init": "b"}
+    host_res = {k: torch.empty_like(host[like[k]]).pin_memory() for k in out_keys}
 
     def step_e2e():
-        d = {k: host[k].to(dev, non_blocking=True) for k in keys}
-        c = d["c"] * lam
-        sol = ext.forward(d["wx"], d["wy"], c, d["b"], d["init"], its, pid)[0]
-        grads = ext.backward(d["grad"], d["wx"], d["wy"], c, d["b"], its, pid)
-        g_lam = ext.lambda_grad(grads[2], d["c"])
-        allreduce_scalar_grads(g_lam)
-        host_out["sol"].copy_(sol, non_blocking=True)
-        for dst, src in zip(host_out["g"], grads):
-            dst.copy_(src, non_blocking=True)
-        host_out["lam"].copy_(g_lam, non_blocking=True)
+        # the public host-buffer API: chunked H2D copy -> forward -> backward -> D2H copy, copies overlapped
+        tv_fwd_bwd_from_host(pipe, host, host_res, its, pid, lam=lam, chunk=args.e2e_chunk,
+                             host_lam_grad=host_out["lam"])
 
     h2d = sum(host[k].numel() * 4 for k in keys)
-    d2h = host_out["sol"].numel() * 4 + sum(t.numel() * 4 for t in host_out["g"]) + 4
+    d2h = sum(t.numel() * 4 for t in host_res.values()) + 4
 
     def barrier():
         if world > 1:
@@ -346,7 +343,8 @@ def run_ours(args, rank, local_rank, world):
                          "forward_kernel": {"achieved": fwd_achieved, "frac": fwd_achieved / peak, "launch_ms": fwd_launch_ms},
                          "whole_step": {"achieved": whole, "frac": whole / peak}},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e / args.steps},
+                    "ms_per_step": ms_e2e / args.steps, "api": "host_pipeline.tv_fwd_bwd_from_host",
+                    "chunk_images": args.e2e_chunk},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
@@ -371,6 +369,7 @@ def main():
     ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
     ap.add_argument("--fuse", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunk", type=int, default=2, help="images per chunk of the host-buffer pipeline")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -99,10 +99,10 @@ tv_fwd_fused_kernel(const __grid_constant__ FwdFusedParams p) {
     load_maps(p, g, n, c, wx, wy);
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
-        inv[r].x = __fdividef(1.0f, 1.0f + c[r].x);
-        inv[r].y = __fdividef(1.0f, 1.0f + c[r].y);
-        inv[r].z = __fdividef(1.0f, 1.0f + c[r].z);
-        inv[r].w = __fdividef(1.0f, 1.0f + c[r].w);
+        inv[r].x = rcp_approx(1.0f + c[r].x);
+        inv[r].y = rcp_approx(1.0f + c[r].y);
+        inv[r].z = rcp_approx(1.0f + c[r].z);
+        inv[r].w = rcp_approx(1.0f + c[r].w);
     }
     for (int ch = 0; ch < p.C; ++ch) {
         float4 y[kRows], x[kRows], b[kRows];
@@ -209,7 +209,7 @@ __device__ __forceinline__ float reverse_point(float ybar, float& acc, float x05
     acc = -t * ybar;
     xbar_out = xbar;
     const float diff = b - x05;
-    const float inv = __fdividef(1.0f, 1.0f + c);
+    const float inv = rcp_approx(1.0f + c);
     if (1.0f + c >= fabsf(diff)) {
         // d/dc of (c b + x05)/(1+c) = (b - x)/(1+c) with x the prox output
         const float xq = fmaf(c, b, x05) * inv;
@@ -276,10 +276,10 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
             } else {
 #pragma unroll
                 for (int r = 0; r < kRows; ++r) {
-                    y[r].x = rederive_y_fast(xh[r].x, xhm[r].x, b[r].x, c[r].x, __fdividef(1.0f, 1.0f + c[r].x), t);
-                    y[r].y = rederive_y_fast(xh[r].y, xhm[r].y, b[r].y, c[r].y, __fdividef(1.0f, 1.0f + c[r].y), t);
-                    y[r].z = rederive_y_fast(xh[r].z, xhm[r].z, b[r].z, c[r].z, __fdividef(1.0f, 1.0f + c[r].z), t);
-                    y[r].w = rederive_y_fast(xh[r].w, xhm[r].w, b[r].w, c[r].w, __fdividef(1.0f, 1.0f + c[r].w), t);
+                    y[r].x = rederive_y_fast(xh[r].x, xhm[r].x, b[r].x, c[r].x, rcp_approx(1.0f + c[r].x), t);
+                    y[r].y = rederive_y_fast(xh[r].y, xhm[r].y, b[r].y, c[r].y, rcp_approx(1.0f + c[r].y), t);
+                    y[r].z = rederive_y_fast(xh[r].z, xhm[r].z, b[r].z, c[r].z, rcp_approx(1.0f + c[r].z), t);
+                    y[r].w = rederive_y_fast(xh[r].w, xhm[r].w, b[r].w, c[r].w, rcp_approx(1.0f + c[r].w), t);
                 }
             }
             sh_y[g.warp][g.lane] = y[0];

@@ -113,11 +113,23 @@ __device__ __forceinline__ bool finite_f(float v) { return fabsf(v) <= 3.4028234
 // ---------------------------------------------------------------------------------------------------------------
 namespace cnl {
 
+// Single-instruction MUFU approximations (flush-to-zero, max 2 ulp).  rsqrt(0) = +inf, rcp(inf) = 0.
+__device__ __forceinline__ float rsqrt_approx(float x) {
+    float r;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
 __device__ __forceinline__ void tri_flux_fast(float yc, float yr, float yd, float wx, float wy, float& fx, float& fy) {
     const float wd1 = wx * (yc - yr);
     const float wd2 = wy * (yc - yd);
     const float A = fmaf(wd1, yc - yr, wd2 * (yc - yd));
-    const float s = fminf(1.0f, kDelta * rsqrtf(A));
+    const float s = fminf(1.0f, kDelta * rsqrt_approx(A));
     fx = s * wd1;
     fy = s * wd2;
 }
@@ -141,7 +153,7 @@ __device__ __forceinline__ float rederive_y_fast(float x05, float x05m, float b,
     const float xq = fmaf(c, b, x05) * inv1pc;
     const float xqm = fmaf(c, b, x05m) * inv1pc;
     // otherwise: both through the soft threshold (b inside the dead zone)
-    const float xl = (c <= ad) ? x05 + copysignf(c, diff) : b;
+    const float xl = x05 + copysignf(c, diff);          // outside the quadratic zone |diff| > 1 + c >= c always holds
     const float xlm = (c <= ad2) ? x05m + copysignf(c, diff2) : b;
     const bool quad = (1.0f + c >= ad);
     const float xk = quad ? xq : xl;
@@ -158,7 +170,7 @@ __device__ __forceinline__ void tri_adjoint_fast(float yc, float yr, float yd, f
     const float wd1 = wx * d1;
     const float wd2 = wy * d2;
     const float A = fmaf(wd1, d1, wd2 * d2);
-    const float r = rsqrtf(A);                   // 1/T
+    const float r = rsqrt_approx(A);             // 1/T
     const bool big = kDelta * r < 1.0f;          // T > delta
     const float nom = big ? kDelta * r : 1.0f;
     const float den = big ? 0.5f * nom * r * r : 0.0f;
