@@ -26,6 +26,8 @@ SIGNATURES = {
     "cnl_dot_scratch_floats": (c_int, []),
     "cnl_tv_lambda_grad_static": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]),
     "cnl_tv_lambda_grad_static_max_count": (c_longlong, []),
+    "cnl_median_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "cnl_median_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "cnl_last_error": (c_char_p, []),
     "cnl_version": (c_char_p, []),
 }

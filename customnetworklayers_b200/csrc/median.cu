@@ -1,0 +1,165 @@
+// Weighted-median selection layer for sm_100a: forward and gradient over a channel-last weight volume
+// [N, H, W, K] (reference: cudaMedian/cudaCode/medimax.cu, kMedianScore :17-42 and kMedianScoreGrad :44-100).
+//
+// Both kernels are HBM bound (K floats in, 2 out / K floats in, K out per pixel).  A warp stages the K weights of
+// its 32 pixels, which are contiguous in memory, with coalesced loads into shared memory (row stride K|1, odd, so
+// the per-thread sequential scans are bank-conflict free), then every thread scans its own row.  The running sum
+// is the same sequential fp32 sum in bin order as the reference's, so the crossing index is bit-identical.
+#include "common.h"
+
+namespace cnl {
+
+constexpr int kMedWarps = 4;
+constexpr int kMedThreads = kMedWarps * 32;
+
+__device__ __forceinline__ int med_stride(int k) { return k | 1; }
+
+// Cooperative, coalesced copy of the rows of this warp's 32 pixels into shared memory.
+__device__ __forceinline__ void stage_rows(const float* __restrict__ src, float* __restrict__ dst, long long first_pixel,
+                                           long long total_pixels, int k, int lane) {
+    const int stride = med_stride(k);
+    long long npix = total_pixels - first_pixel;
+    if (npix > 32) npix = 32;
+    const long long count = npix * k;
+    const float* base = src + first_pixel * k;
+    for (long long i = lane; i < count; i += 32) {
+        const int p = (int)(i / k), c = (int)(i - (long long)p * k);
+        dst[p * stride + c] = __ldg(base + i);
+    }
+}
+
+__global__ void __launch_bounds__(kMedThreads)
+median_forward_kernel(const float* __restrict__ vol, float* __restrict__ out, int* __restrict__ index,
+                      long long plane, int n_images, int k) {
+    extern __shared__ float sh[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long total = plane * n_images;
+    const long long first = ((long long)blockIdx.x * kMedWarps + warp) * 32;
+    if (first >= total) return;
+    float* rows = sh + (size_t)warp * 32 * med_stride(k);
+    stage_rows(vol, rows, first, total, k, lane);
+    __syncwarp();
+    const long long pix = first + lane;
+    if (pix >= total) return;
+    const float* row = rows + lane * med_stride(k);
+    float score = 0.0f, o0 = 0.0f, o1 = 0.0f;
+    int hit = -1;
+    for (int c = 0; c < k; ++c) {
+        const float p = row[c];
+        const float nxt = score + p;
+        if (score < 0.5f && nxt >= 0.5f) {                           // medimax.cu:30
+            const double alpha = (1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p);     // :33
+            o0 = (float)((double)c + alpha);                         // :34
+            o1 = p;                                                  // :35
+            hit = c;
+            break;
+        }
+        score = nxt;
+    }
+    const long long img = pix / plane, off = pix - img * plane;
+    out[(img * 2 + 0) * plane + off] = o0;
+    out[(img * 2 + 1) * plane + off] = o1;
+    if (index) index[pix] = hit;
+}
+
+__global__ void __launch_bounds__(kMedThreads)
+median_backward_kernel(const float* __restrict__ vol, const float* __restrict__ grad, float* __restrict__ gvol,
+                       long long plane, int n_images, int k) {
+    extern __shared__ float sh[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long total = plane * n_images;
+    const long long first = ((long long)blockIdx.x * kMedWarps + warp) * 32;
+    if (first >= total) return;
+    const int stride = med_stride(k);
+    float* rows = sh + (size_t)warp * 32 * stride;
+    stage_rows(vol, rows, first, total, k, lane);
+    __syncwarp();
+    const long long pix = first + lane;
+    if (pix < total) {
+        float* row = rows + lane * stride;
+        const long long img = pix / plane, off = pix - img * plane;
+        const float g0 = grad[(img * 2 + 0) * plane + off];
+        const float g1 = grad[(img * 2 + 1) * plane + off];
+        // pass 1: crossing bin (medimax.cu:55-80)
+        float score = 0.0f, pmid = 1.0f, gmid = 0.0f;
+        int hit = -1;
+        for (int c = 0; c < k; ++c) {
+            const float p = row[c];
+            const float nxt = score + p;
+            if (score < 0.5f && nxt >= 0.5f) {
+                const float alpha = (float)((1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p));
+                gmid = __fadd_rn(__fdiv_rn(__fmul_rn(g0, alpha), -p), g1);       // :73, fp32, no contraction
+                pmid = p;
+                hit = c;
+                break;
+            }
+            score = nxt;
+        }
+        // pass 2: bins before / after the crossing (:82-99); the row in shared memory is overwritten by its gradient
+        const float half = (float)((double)g0 / (2.0 * (double)pmid));
+        score = 0.0f;
+        for (int c = 0; c < k; ++c) {
+            const float p = row[c];
+            const float nxt = score + p;
+            float g = 0.0f;
+            if (nxt < 0.5f) g = -half;
+            else if (score >= 0.5f) g = half;
+            if (c == hit) g = gmid;
+            row[c] = g;
+            score = nxt;
+        }
+    }
+    __syncwarp();
+    // coalesced write-back of the warp's rows
+    long long npix = total - first;
+    if (npix > 32) npix = 32;
+    const long long count = npix * k;
+    float* base = gvol + first * k;
+    for (long long i = lane; i < count; i += 32) {
+        const int p = (int)(i / k), c = (int)(i - (long long)p * k);
+        base[i] = rows[p * stride + c];
+    }
+}
+
+static int median_check(const void* a, const void* b, int n, int h, int w, int k) {
+    if (!a || !b) return fail(CNL_ERR_NULL, "null pointer argument");
+    if (n < 1 || h < 1 || w < 1 || k < 1) return fail(CNL_ERR_BAD_SHAPE, "n, h, w, k must be >= 1 (got %d, %d, %d, %d)", n, h, w, k);
+    if (k > 1024) return fail(CNL_ERR_BAD_SHAPE, "at most 1024 bins are supported (got %d)", k);
+    return CNL_OK;
+}
+
+static int median_smem(int k) { return kMedWarps * 32 * (k | 1) * (int)sizeof(float); }
+
+template <typename Kern>
+static int median_prepare(Kern kern, int k) {
+    const int bytes = median_smem(k);
+    if (bytes > 48 * 1024)
+        return check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "cudaFuncSetAttribute");
+    return CNL_OK;
+}
+
+}  // namespace cnl
+
+using namespace cnl;
+
+extern "C" int cnl_median_forward(const float* vol, float* out, int* index, int n, int h, int w, int k, void* stream) {
+    CNL_TRY(median_check(vol, out, n, h, w, k));
+    CNL_TRY(median_prepare(median_forward_kernel, k));
+    const long long plane = (long long)h * w;
+    const long long warps = (plane * n + 31) / 32;
+    const unsigned blocks = (unsigned)((warps + kMedWarps - 1) / kMedWarps);
+    median_forward_kernel<<<blocks, kMedThreads, median_smem(k), static_cast<cudaStream_t>(stream)>>>(vol, out, index, plane, n, k);
+    return after_launch("median_forward_kernel");
+}
+
+extern "C" int cnl_median_backward(const float* vol, const float* grad, float* gvol, int n, int h, int w, int k,
+                                   void* stream) {
+    CNL_TRY(median_check(vol, gvol, n, h, w, k));
+    if (!grad) return fail(CNL_ERR_NULL, "null pointer argument");
+    CNL_TRY(median_prepare(median_backward_kernel, k));
+    const long long plane = (long long)h * w;
+    const long long warps = (plane * n + 31) / 32;
+    const unsigned blocks = (unsigned)((warps + kMedWarps - 1) / kMedWarps);
+    median_backward_kernel<<<blocks, kMedThreads, median_smem(k), static_cast<cudaStream_t>(stream)>>>(vol, grad, gvol, plane, n, k);
+    return after_launch("median_backward_kernel");
+}

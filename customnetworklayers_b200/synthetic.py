@@ -41,3 +41,17 @@ def make_inputs(n: int, ch: int, h: int, w: int, seed: int = 1234, conf_p: float
     grad = torch.randn(n, ch, h, w, generator=gen).float()
     return {"wx": wx.contiguous(), "wy": wy.contiguous(), "c": c.contiguous(), "b": b.contiguous(),
             "init": b.clone(), "grad": grad.contiguous()}
+
+
+def make_median_volume(n: int, h: int, w: int, k: int, seed: int = 1238, peaky: bool = True):
+    """Per-pixel weight vectors [n,h,w,k] that sum to 1 (fp32): U(0.5,1.5) weights, optionally sharpened so that the
+    crossing bin varies over the whole range, plus an upstream gradient [n,2,h,w] ~ N(0,1)."""
+    gen = torch.Generator().manual_seed(seed)
+    vol = torch.rand(n, h, w, k, generator=gen) + 0.5
+    if peaky:
+        centre = torch.randint(0, k, (n, h, w, 1), generator=gen).float()
+        bins = torch.arange(k).float().view(1, 1, 1, k)
+        vol = vol * torch.exp(-0.5 * ((bins - centre) / max(1.0, k / 8.0)) ** 2) + 1e-3 * vol
+    vol = (vol / vol.sum(dim=-1, keepdim=True)).float().contiguous()
+    grad = torch.randn(n, 2, h, w, generator=gen).float()
+    return vol, grad

@@ -122,6 +122,21 @@ int cnl_dot_scratch_floats(void);
 int cnl_tv_lambda_grad_static(const float* g_c, const float* c_raw, long long count, float* out, void* stream);
 long long cnl_tv_lambda_grad_static_max_count(void);
 
+/*
+ * Weighted-median selection over a channel-last weight volume vol [n][h][w][k] whose k weights per pixel sum to 1.
+ * Replaces  static int MediMax::forward(float* d_vol, float* d_out_FS, int in, int ih, int iw, int numDisp)  and
+ * MediMax::backward(float* d_vol, float* d_inGrad, float* d_outGrad0, int in, int ih, int iw, int numDisp)
+ * (cudaMedian/cudaCode/medimax.h:13-14, medimax.cu:142-204).
+ *   out   [n][2][h][w]: channel 0 = crossing position c + alpha, channel 1 = weight of the crossing bin; (0, 0) where
+ *                       the weights never reach 0.5.
+ *   index [n][h][w] (optional, may be null): crossing bin, -1 if none.  No reference counterpart (debug / tests).
+ *   grad  [n][2][h][w] upstream gradient; gvol [n][h][w][k] gradient w.r.t. vol (fully overwritten).
+ * Unlike the reference, n > 1 is decoded correctly (the reference decodes pixel indices against the 2-channel
+ * output, medimax.cu:18-22).
+ */
+int cnl_median_forward(const float* vol, float* out, int* index, int n, int h, int w, int k, void* stream);
+int cnl_median_backward(const float* vol, const float* grad, float* gvol, int n, int h, int w, int k, void* stream);
+
 /* Message for the last error on the calling thread ("" if none). */
 const char* cnl_last_error(void);
 

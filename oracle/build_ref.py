@@ -1,5 +1,5 @@
-"""Recipe that compiles the reference's own cudaTV kernels (unmodified, from /root/reference) against the small
-ImageUtilities stand-in in oracle/iu_shim into oracle/_ref/libtvref.so.  TEST INFRASTRUCTURE ONLY.
+"""Recipe that compiles the reference's own CUDA kernels (unmodified, from /root/reference) against the small
+ImageUtilities stand-in in oracle/iu_shim into shared libraries under oracle/_ref/ (libtvref.so, libmedianref.so, ...).  TEST INFRASTRUCTURE ONLY.
 
     python oracle/build_ref.py
 
@@ -11,25 +11,36 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_SRC = "/root/reference/cudaTV/cudaCode"
+REF_ROOT = "/root/reference"
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "libtvref.so")
+# output library -> (wrapper source, reference source directory)
+TARGETS = {
+    "libtvref.so": ("ref_tv_wrapper.cu", "cudaTV/cudaCode"),
+    "libmedianref.so": ("ref_median_wrapper.cu", "cudaMedian/cudaCode"),
+    "libquadfitref.so": ("ref_quadfit_wrapper.cu", "cudaQuadFit/cudaCode"),
+    "libtgvref.so": ("ref_tgv_wrapper.cu", "cudaTGV/cudaCode"),
+}
 
 
 def build() -> str:
-    if not os.path.isdir(REF_SRC):
-        print("reference sources not present; keeping", OUT if os.path.exists(OUT) else "(nothing)")
+    if not os.path.isdir(REF_ROOT):
+        print("reference sources not present; keeping what is in", OUT_DIR)
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
-    cmd = ["/usr/local/cuda/bin/nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
-           "--extended-lambda", "-Xcompiler", "-fPIC", "-shared", "--cudart", "shared", "-w",
-           "-I", os.path.join(HERE, "iu_shim"), "-I", REF_SRC,
-           os.path.join(HERE, "ref_tv_wrapper.cu"), "-o", OUT]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
-        raise RuntimeError("building the reference's cudaTV kernels failed")
-    print("built", OUT)
+    for lib, (wrapper, src_dir) in TARGETS.items():
+        wrapper_path = os.path.join(HERE, wrapper)
+        if not os.path.exists(wrapper_path):
+            continue
+        out = os.path.join(OUT_DIR, lib)
+        cmd = ["/usr/local/cuda/bin/nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
+               "--extended-lambda", "-Xcompiler", "-fPIC", "-shared", "--cudart", "shared", "-w",
+               "-I", os.path.join(HERE, "iu_shim"), "-I", os.path.join(REF_ROOT, src_dir), wrapper_path, "-o", out]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError(f"building {lib} from the reference's {src_dir} failed")
+        print("built", out)
     return OUT
 
 

@@ -1,4 +1,4 @@
-// Minimal stand-in for the ImageUtilities headers, written from the call sites in the reference's cudaTV sources
+// Minimal stand-in for the ImageUtilities headers, written from the call sites in the reference's CUDA sources
 // (not from ImageUtilities itself), so that the UNMODIFIED reference translation unit compiles with nvcc.
 // TEST INFRASTRUCTURE ONLY: used by oracle/build_ref.py to build oracle/_ref/libtvref.so, the reference's own CUDA
 // kernels, as a second checker on a GPU box.
@@ -7,7 +7,7 @@
 //   iu::TensorGpu_32f(ptr, N, C, H, W, ext, NCHW)   wrap caller memory
 //   iu::TensorGpu_32f(N, C, H, W, NCHW)             own allocation
 //   .data(), .begin(), .end(), .width(), .height(), .samples(), .channels()
-//   conversion to TensorKernelData with operator()(n, c, h, w) and fields N, C, H, W
+//   conversion to TensorKernelData with operator()(n, c, h, w), coords(idx, &n, &c, &h, &w), fields N, C, H, W, length_
 //   iu::ImageGpu_32f_C1(ptr, w, h, pitch, ext=false)   COPIES the data; .begin(), .end(), .getTexture()
 //   texture: unnormalised coordinates, clamp addressing, point filtering, element reads
 #pragma once
@@ -17,9 +17,12 @@
 #include <thrust/functional.h>
 #include <thrust/transform.h>
 
+#include <cmath>
 #include <cstddef>
 #include <cstdio>
 #include <cstdlib>
+#include <iostream>
+#include <vector>
 
 namespace iu {
 
@@ -40,6 +43,14 @@ public:
         int N, C, H, W;
         __device__ float& operator()(int n, int c, int h, int w) {
             return data_[((static_cast<size_t>(n) * C + c) * H + h) * W + w];
+        }
+        // linear index -> (n, c, h, w) of the row-major 4-D layout
+        template <typename I>
+        __device__ void coords(unsigned int idx, I* n, I* c, I* h, I* w) const {
+            *w = static_cast<I>(idx % W);
+            *h = static_cast<I>((idx / W) % H);
+            *c = static_cast<I>((idx / (static_cast<unsigned int>(W) * H)) % C);
+            *n = static_cast<I>(idx / (static_cast<unsigned int>(W) * H * C));
         }
     };
 

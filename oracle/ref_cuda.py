@@ -52,3 +52,47 @@ def backward(grad, wx, wy, c, b, its, pid):
     if rc != 0:
         raise RuntimeError(f"reference backward returned {rc}")
     return g
+
+
+# ---- cudaMedian -------------------------------------------------------------------------------------------------
+MEDIAN_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "libmedianref.so")
+_median = None
+
+
+def median_available() -> bool:
+    return os.path.exists(MEDIAN_LIB_PATH)
+
+
+def _load_median():
+    global _median
+    if _median is None:
+        lib = ctypes.CDLL(MEDIAN_LIB_PATH)
+        lib.ref_median_forward.restype = ctypes.c_int
+        lib.ref_median_forward.argtypes = [ctypes.c_void_p] * 2 + [ctypes.c_int] * 4
+        lib.ref_median_backward.restype = ctypes.c_int
+        lib.ref_median_backward.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4
+        _median = lib
+    return _median
+
+
+def median_forward(vol):
+    """vol: CUDA fp32 [1,H,W,K] -> [1,2,H,W] from the reference's kMedianScore."""
+    import torch
+    n, h, w, k = vol.shape
+    out = torch.zeros((n, 2, h, w), device=vol.device)
+    torch.cuda.synchronize()
+    rc = _load_median().ref_median_forward(vol.data_ptr(), out.data_ptr(), n, h, w, k)
+    if rc != 0:
+        raise RuntimeError(f"reference median forward returned {rc}")
+    return out
+
+
+def median_backward(vol, grad):
+    import torch
+    n, h, w, k = vol.shape
+    g = torch.zeros_like(vol)
+    torch.cuda.synchronize()
+    rc = _load_median().ref_median_backward(vol.data_ptr(), grad.data_ptr(), g.data_ptr(), n, h, w, k)
+    if rc != 0:
+        raise RuntimeError(f"reference median backward returned {rc}")
+    return g

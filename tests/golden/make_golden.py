@@ -1,8 +1,8 @@
 """Generates tests/golden/tv_reference_cuda.npz: inputs and outputs of the REFERENCE's own cudaTV kernels
 (oracle/_ref/libtvref.so, built unmodified by oracle/build_ref.py) on a few small problems.  Needs a GPU:
 
-    python tests/golden/make_golden.py gpurun_out/tv_reference_cuda.npz      # on the GPU box
-    cp gpurun_out/tv_reference_cuda.npz tests/golden/                        # back in the working tree
+    python tests/golden/make_golden.py gpurun_out [tv] [median] ...          # on the GPU box
+    cp gpurun_out/*_reference_cuda.npz tests/golden/                         # back in the working tree
 
 The committed file pins the CPU oracle (tests/test_golden.py, no GPU needed) and the CUDA path."""
 import os
@@ -42,5 +42,30 @@ def main(out_path):
     print("wrote", out_path, os.path.getsize(out_path), "bytes")
 
 
+
+
+def median_main(out_path):
+    """tests/golden/median_reference_cuda.npz: the reference's own cudaMedian kernels (oracle/_ref/libmedianref.so)."""
+    from customnetworklayers_b200.synthetic import make_median_volume
+    from oracle import ref_cuda
+    cases = [(12, 16, 49, 201), (9, 7, 9, 202), (5, 6, 121, 203)]
+    data = {"n_cases": np.array(len(cases))}
+    for i, (h, w, k, seed) in enumerate(cases):
+        vol, grad = make_median_volume(1, h, w, k, seed=seed)
+        vol[0, 0, 0] = 0.1 / k                      # one pixel without a crossing
+        v, g = vol.cuda(), grad.cuda()
+        data[f"case{i}_vol"] = vol.numpy()
+        data[f"case{i}_grad"] = grad.numpy()
+        data[f"case{i}_out"] = ref_cuda.median_forward(v).cpu().numpy()
+        data[f"case{i}_gvol"] = ref_cuda.median_backward(v, g).cpu().numpy()
+    np.savez_compressed(out_path, **data)
+    print("wrote", out_path, os.path.getsize(out_path), "bytes")
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(__file__), "tv_reference_cuda.npz"))
+    out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.dirname(os.path.abspath(__file__))
+    which = sys.argv[2:] or ["tv", "median"]
+    if "tv" in which:
+        main(os.path.join(out_dir, "tv_reference_cuda.npz"))
+    if "median" in which:
+        median_main(os.path.join(out_dir, "median_reference_cuda.npz"))
