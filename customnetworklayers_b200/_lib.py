@@ -28,6 +28,10 @@ SIGNATURES = {
     "cnl_tv_lambda_grad_static_max_count": (c_longlong, []),
     "cnl_median_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "cnl_median_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "cnl_quadfit_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 4 + [c_void_p]),
+    "cnl_quadfit_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 4 + [c_void_p]),
+    "cnl_quadfit_cost_forward": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "cnl_quadfit_cost_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "cnl_last_error": (c_char_p, []),
     "cnl_version": (c_char_p, []),
 }

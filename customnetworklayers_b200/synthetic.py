@@ -55,3 +55,34 @@ def make_median_volume(n: int, h: int, w: int, k: int, seed: int = 1238, peaky: 
     vol = (vol / vol.sum(dim=-1, keepdim=True)).float().contiguous()
     grad = torch.randn(n, 2, h, w, generator=gen).float()
     return vol, grad
+
+
+def make_quadfit_inputs(n: int, c: int, h: int, w: int, seed: int = 1237, max_disp: float = 6.0):
+    """Feature maps whose correlation peaks near the true displacement: feat1 is feat0 warped by a smooth integer-ish
+    flow plus noise; the initial flow is the true one perturbed by up to half a pixel (and pushed out of the image
+    in one corner).  Returns fp32 CPU tensors feat0, feat1 [n,c,h,w], flow [n,2,h,w], grad [n,3,h,w]."""
+    gen = torch.Generator().manual_seed(seed)
+    base = _gaussian_smooth(torch.randn(n * c, 1, h, w, generator=gen).float(), sigma=1.5, radius=4).view(n, c, h, w)
+    feat0 = base / base.std() if base.numel() > 1 else base + 1.0
+    dx = int(max_disp // 2)
+    feat1 = torch.roll(feat0, shifts=(1, dx), dims=(2, 3)) + 0.05 * torch.randn(n, c, h, w, generator=gen)
+    flow = torch.empty(n, 2, h, w)
+    flow[:, 0] = dx + (torch.rand(n, h, w, generator=gen) - 0.5)
+    flow[:, 1] = 1 + (torch.rand(n, h, w, generator=gen) - 0.5)
+    flow[:, :, : max(1, h // 8), : max(1, w // 8)] -= 3.0 * max_disp          # leaves the image
+    grad = torch.randn(n, 3, h, w, generator=gen).float()
+    return feat0.float().contiguous(), feat1.float().contiguous(), flow.float().contiguous(), grad
+
+
+def make_cost_patches(n: int, h: int, w: int, seed: int = 1237):
+    """5-point stencils of a score to maximise: minus (quadratic bowl with sub-pixel minimum in (-0.5,0.5)^2 and
+    curvature U(0.5,2) plus N(0,0.05) noise).  Returns cost5 [n,5,h,w] ordered (c00, c0+, c+0, c0-, c-0) and the
+    true sub-pixel offsets [n,2,h,w]."""
+    gen = torch.Generator().manual_seed(seed)
+    off = torch.rand(n, 2, h, w, generator=gen) - 0.5
+    curv = torch.rand(n, 2, h, w, generator=gen) * 1.5 + 0.5
+    def bowl(dx, dy):
+        v = curv[:, 0] * (dx - off[:, 0]) ** 2 + curv[:, 1] * (dy - off[:, 1]) ** 2
+        return -(v + 0.05 * torch.randn(n, h, w, generator=gen))
+    cost5 = torch.stack([bowl(0, 0), bowl(1, 0), bowl(0, 1), bowl(-1, 0), bowl(0, -1)], dim=1)
+    return cost5.float().contiguous(), off.float()

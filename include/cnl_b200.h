@@ -137,6 +137,28 @@ long long cnl_tv_lambda_grad_static_max_count(void);
 int cnl_median_forward(const float* vol, float* out, int* index, int n, int h, int w, int k, void* stream);
 int cnl_median_backward(const float* vol, const float* grad, float* gvol, int n, int h, int w, int k, void* stream);
 
+/*
+ * Differentiable quadratic fit around the rounded displaced pixel.  Replaces
+ *   static int FlowQuadFitting::forward(float* d_input0, float* d_input1, float* d_dxdy, float* d_outF, int in, int ic, int ih, int iw)
+ *   static int FlowQuadFitting::backward(float* d_input0, float* d_input1, float* d_dxdy, float* d_inGrad,
+ *                                        float* d_outGradIm0, float* d_outGradIm1, int in, int ic, int ih, int iw)
+ * (cudaQuadFit/cudaCode/quadFit.h:24-31, quadFit.cu:303-360).
+ *   feat0, feat1 [n][c][h][w]; flow [n][flow_channels][h][w] (only channels 0, 1 = x, y displacement are read; the
+ *   reference's Python layer passes three); out [n][3][h][w] = (fx, fy, fitted score), zero where the displaced
+ *   location leaves the image; loc (optional, may be null) [n][2][h][w] int = rounded location (x, y), -1 outside.
+ *   grad [n][3][h][w]; g_feat0, g_feat1 [n][c][h][w] are overwritten.  g_feat1 is accumulated with fp32 atomics (as in
+ *   the reference), so its last bits depend on scheduling.  No gradient w.r.t. flow (quadFit.h:10-12).
+ * cnl_quadfit_cost_*: the same fit applied to a given stencil cost5 [n][5][h][w] = (c00, c0+, c+0, c0-, c-0) of a
+ * correlation to maximise, without the image-border tests; no reference counterpart as an entry point (it is the
+ * fit of quadFit.cu:74-134 and its derivative :245-281).
+ */
+int cnl_quadfit_forward(const float* feat0, const float* feat1, const float* flow, int flow_channels, float* out,
+                        int* loc, int n, int c, int h, int w, void* stream);
+int cnl_quadfit_backward(const float* feat0, const float* feat1, const float* flow, int flow_channels,
+                         const float* grad, float* g_feat0, float* g_feat1, int n, int c, int h, int w, void* stream);
+int cnl_quadfit_cost_forward(const float* cost5, float* out, int n, int h, int w, void* stream);
+int cnl_quadfit_cost_backward(const float* cost5, const float* grad, float* g_cost5, int n, int h, int w, void* stream);
+
 /* Message for the last error on the calling thread ("" if none). */
 const char* cnl_last_error(void);
 

@@ -96,3 +96,48 @@ def median_backward(vol, grad):
     if rc != 0:
         raise RuntimeError(f"reference median backward returned {rc}")
     return g
+
+
+# ---- cudaQuadFit ------------------------------------------------------------------------------------------------
+QUADFIT_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "libquadfitref.so")
+_quadfit = None
+
+
+def quadfit_available() -> bool:
+    return os.path.exists(QUADFIT_LIB_PATH)
+
+
+def _load_quadfit():
+    global _quadfit
+    if _quadfit is None:
+        lib = ctypes.CDLL(QUADFIT_LIB_PATH)
+        lib.ref_quadfit_forward.restype = ctypes.c_int
+        lib.ref_quadfit_forward.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 4
+        lib.ref_quadfit_backward.restype = ctypes.c_int
+        lib.ref_quadfit_backward.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 4
+        _quadfit = lib
+    return _quadfit
+
+
+def quadfit_forward(f0, f1, flow2):
+    """CUDA fp32 tensors [N,C,H,W], flow2 [N,2,H,W] -> [N,3,H,W] from the reference's kQuadFitFlow."""
+    import torch
+    n, c, h, w = f0.shape
+    out = torch.zeros((n, 3, h, w), device=f0.device)
+    torch.cuda.synchronize()
+    rc = _load_quadfit().ref_quadfit_forward(f0.data_ptr(), f1.data_ptr(), flow2.data_ptr(), out.data_ptr(), n, c, h, w)
+    if rc != 0:
+        raise RuntimeError(f"reference quadfit forward returned {rc}")
+    return out
+
+
+def quadfit_backward(f0, f1, flow2, grad):
+    import torch
+    n, c, h, w = f0.shape
+    g0, g1 = torch.zeros_like(f0), torch.zeros_like(f1)
+    torch.cuda.synchronize()
+    rc = _load_quadfit().ref_quadfit_backward(f0.data_ptr(), f1.data_ptr(), flow2.data_ptr(), grad.data_ptr(),
+                                              g0.data_ptr(), g1.data_ptr(), n, c, h, w)
+    if rc != 0:
+        raise RuntimeError(f"reference quadfit backward returned {rc}")
+    return g0, g1

@@ -62,10 +62,29 @@ def median_main(out_path):
     print("wrote", out_path, os.path.getsize(out_path), "bytes")
 
 
+def quadfit_main(out_path):
+    """tests/golden/quadfit_reference_cuda.npz: the reference's own cudaQuadFit kernels (oracle/_ref/libquadfitref.so)."""
+    from customnetworklayers_b200.synthetic import make_quadfit_inputs
+    from oracle import ref_cuda
+    cases = [(1, 4, 12, 16, 301), (2, 7, 9, 11, 302), (1, 16, 20, 24, 303)]
+    data = {"n_cases": np.array(len(cases))}
+    for i, (n, c, h, w, seed) in enumerate(cases):
+        f0, f1, flow, grad = make_quadfit_inputs(n, c, h, w, seed=seed)
+        D = [t.cuda() for t in (f0, f1, flow, grad)]
+        out = ref_cuda.quadfit_forward(D[0], D[1], D[2])
+        g0, g1 = ref_cuda.quadfit_backward(D[0], D[1], D[2], D[3])
+        for k, v in (("feat0", f0), ("feat1", f1), ("flow", flow), ("grad", grad), ("out", out), ("g0", g0), ("g1", g1)):
+            data[f"case{i}_{k}"] = v.cpu().numpy()
+    np.savez_compressed(out_path, **data)
+    print("wrote", out_path, os.path.getsize(out_path), "bytes")
+
+
 if __name__ == "__main__":
     out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.dirname(os.path.abspath(__file__))
-    which = sys.argv[2:] or ["tv", "median"]
+    which = sys.argv[2:] or ["tv", "median", "quadfit"]
     if "tv" in which:
         main(os.path.join(out_dir, "tv_reference_cuda.npz"))
     if "median" in which:
         median_main(os.path.join(out_dir, "median_reference_cuda.npz"))
+    if "quadfit" in which:
+        quadfit_main(os.path.join(out_dir, "quadfit_reference_cuda.npz"))
