@@ -86,3 +86,17 @@ def make_cost_patches(n: int, h: int, w: int, seed: int = 1237):
         return -(v + 0.05 * torch.randn(n, h, w, generator=gen))
     cost5 = torch.stack([bowl(0, 0), bowl(1, 0), bowl(0, 1), bowl(-1, 0), bowl(0, -1)], dim=1)
     return cost5.float().contiguous(), off.float()
+
+
+def make_tgv_inputs(n: int, ch: int, h: int, w: int, seed: int = 1236, conf_p: float = 0.2, alpha0: float = 1.0,
+                    alpha1: float = 2.0):
+    """TGV stand-in inputs: dx = [alpha0*wx, alpha1*1], dy = [alpha0*wy, alpha1*1] as [n,2,h,w]; b ~ U(-20,20);
+    c = Bernoulli(conf_p)*U(0,1); init = [b, 0, 0] as [n,3,ch,h,w]; upstream gradient ~ N(0,1) on all three planes."""
+    I = make_inputs(n, ch, h, w, seed=seed, conf_p=conf_p)
+    gen = torch.Generator().manual_seed(seed + 7)
+    dx = torch.cat([alpha0 * I["wx"], torch.full_like(I["wx"], alpha1)], dim=1).contiguous()
+    dy = torch.cat([alpha0 * I["wy"], torch.full_like(I["wy"], alpha1)], dim=1).contiguous()
+    init = torch.zeros(n, 3, ch, h, w)
+    init[:, 0] = I["b"]
+    grad = torch.randn(n, 3, ch, h, w, generator=gen).float()
+    return {"dx": dx, "dy": dy, "c": I["c"], "b": I["b"], "init": init.contiguous(), "grad": grad.contiguous()}

@@ -28,13 +28,15 @@ def build() -> str:
         print("reference sources not present; keeping what is in", OUT_DIR)
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
+    # -maxrregcount=128: the reference launches 512-thread blocks without __launch_bounds__; built for sm_100a its TGV
+    # reverse kernels otherwise need more than 128 registers per thread and every launch fails (out of resources)
     for lib, (wrapper, src_dir) in TARGETS.items():
         wrapper_path = os.path.join(HERE, wrapper)
         if not os.path.exists(wrapper_path):
             continue
         out = os.path.join(OUT_DIR, lib)
         cmd = ["/usr/local/cuda/bin/nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
-               "--extended-lambda", "-Xcompiler", "-fPIC", "-shared", "--cudart", "shared", "-w",
+               "--extended-lambda", "-maxrregcount=128", "-Xcompiler", "-fPIC", "-shared", "--cudart", "shared", "-w",
                "-I", os.path.join(HERE, "iu_shim"), "-I", os.path.join(REF_ROOT, src_dir), wrapper_path, "-o", out]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:

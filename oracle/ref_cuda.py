@@ -141,3 +141,53 @@ def quadfit_backward(f0, f1, flow2, grad):
     if rc != 0:
         raise RuntimeError(f"reference quadfit backward returned {rc}")
     return g0, g1
+
+
+# ---- cudaTGV ----------------------------------------------------------------------------------------------------
+TGV_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "libtgvref.so")
+_tgv = None
+
+
+def tgv_available() -> bool:
+    return os.path.exists(TGV_LIB_PATH)
+
+
+def _load_tgv():
+    global _tgv
+    if _tgv is None:
+        lib = ctypes.CDLL(TGV_LIB_PATH)
+        lib.ref_tgv_forward.restype = ctypes.c_int
+        lib.ref_tgv_forward.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 5
+        lib.ref_tgv_backward.restype = ctypes.c_int
+        lib.ref_tgv_backward.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 5
+        _tgv = lib
+    return _tgv
+
+
+def tgv_forward(dx, dy, c, b, init, its, pid):
+    """CUDA fp32: dx, dy [1,2,H,W]; c [1,1,H,W]; b [1,C,H,W]; init [1,3,C,H,W] -> solution [1,3,C,H,W]."""
+    import torch
+    assert b.shape[0] == 1
+    _, ch, h, w = b.shape
+    out = torch.zeros_like(init)
+    torch.cuda.synchronize()
+    rc = _load_tgv().ref_tgv_forward(dx.data_ptr(), dy.data_ptr(), c.data_ptr(), b.data_ptr(), init.data_ptr(),
+                                     out.data_ptr(), ch, h, w, int(its), int(pid))
+    if rc != 0:
+        raise RuntimeError(f"reference TGV forward returned {rc}")
+    return out
+
+
+def tgv_backward(grad, dx, dy, c, b, its, pid):
+    import torch
+    assert b.shape[0] == 1
+    _, ch, h, w = b.shape
+    g = [torch.zeros_like(dx), torch.zeros_like(dy), torch.zeros_like(c), torch.zeros_like(b), torch.zeros_like(grad)]
+    grad = grad.clone()
+    torch.cuda.synchronize()
+    rc = _load_tgv().ref_tgv_backward(dx.data_ptr(), dy.data_ptr(), c.data_ptr(), b.data_ptr(), grad.data_ptr(),
+                                      g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), g[3].data_ptr(), g[4].data_ptr(),
+                                      ch, h, w, int(its), int(pid))
+    if rc != 0:
+        raise RuntimeError(f"reference TGV backward returned {rc}")
+    return g

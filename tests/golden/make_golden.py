@@ -79,12 +79,37 @@ def quadfit_main(out_path):
     print("wrote", out_path, os.path.getsize(out_path), "bytes")
 
 
+def tgv_main(out_path):
+    """tests/golden/tgv_reference_cuda.npz: the reference's own cudaTGV kernels (oracle/_ref/libtgvref.so); one
+    channel runs its generic kernels, two channels its two-channel kernels."""
+    from customnetworklayers_b200.synthetic import make_tgv_inputs
+    from oracle import ref_cuda
+    cases = [(1, 16, 32, 4, 401), (2, 16, 32, 6, 402), (1, 32, 32, 10, 403), (2, 32, 64, 20, 404), (3, 16, 32, 8, 405)]
+    data = {"n_cases": np.array(len(cases))}
+    for i, (ch, h, w, its, seed) in enumerate(cases):
+        I = make_tgv_inputs(1, ch, h, w, seed=seed)
+        I["init"][:, 1:] = 0.1 * torch.randn(I["init"][:, 1:].shape, generator=torch.Generator().manual_seed(seed))
+        D = {k: v.cuda() for k, v in I.items()}
+        sol = ref_cuda.tgv_forward(D["dx"], D["dy"], D["c"], D["b"], D["init"], its, i % 10)
+        grads = ref_cuda.tgv_backward(D["grad"], D["dx"], D["dy"], D["c"], D["b"], its, i % 10)
+        data[f"case{i}_its"] = np.array(its)
+        for k, v in I.items():
+            data[f"case{i}_{k}"] = v.numpy()
+        data[f"case{i}_sol"] = sol.cpu().numpy()
+        for name, g in zip(("g_dx", "g_dy", "g_c", "g_b", "g_init"), grads):
+            data[f"case{i}_{name}"] = g.cpu().numpy()
+    np.savez_compressed(out_path, **data)
+    print("wrote", out_path, os.path.getsize(out_path), "bytes")
+
+
 if __name__ == "__main__":
     out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.dirname(os.path.abspath(__file__))
-    which = sys.argv[2:] or ["tv", "median", "quadfit"]
+    which = sys.argv[2:] or ["tv", "median", "quadfit", "tgv"]
     if "tv" in which:
         main(os.path.join(out_dir, "tv_reference_cuda.npz"))
     if "median" in which:
         median_main(os.path.join(out_dir, "median_reference_cuda.npz"))
+    if "tgv" in which:
+        tgv_main(os.path.join(out_dir, "tgv_reference_cuda.npz"))
     if "quadfit" in which:
         quadfit_main(os.path.join(out_dir, "quadfit_reference_cuda.npz"))
