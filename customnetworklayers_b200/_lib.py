@@ -32,6 +32,12 @@ SIGNATURES = {
     "cnl_quadfit_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 4 + [c_void_p]),
     "cnl_quadfit_cost_forward": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "cnl_quadfit_cost_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "cnl_tgv_forward": (c_int, [c_void_p] * 6 + [c_int] * 6 + [c_void_p]),
+    "cnl_tgv_backward": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),
+    "cnl_tgv_release": (c_int, [c_int]),
+    "cnl_tgv_set_option": (c_int, [c_int, c_int, c_int]),
+    "cnl_tgv_read_state": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p]),
+    "cnl_tgv_num_checkpoints": (c_int, [c_int]),
     "cnl_last_error": (c_char_p, []),
     "cnl_version": (c_char_p, []),
 }

@@ -159,6 +159,33 @@ int cnl_quadfit_backward(const float* feat0, const float* feat1, const float* fl
 int cnl_quadfit_cost_forward(const float* cost5, float* out, int n, int h, int w, void* stream);
 int cnl_quadfit_cost_backward(const float* cost5, const float* grad, float* g_cost5, int n, int h, int w, void* stream);
 
+/*
+ * Unrolled FISTA TGV-inpainting layer (second-order TGV: primary plane u and auxiliary planes v1, v2 per channel).
+ * Replaces  static int FistaTGVHuberB2_id::forward(float* d_x, float* d_y, float* d_c, float* d_b, float* d_i, float* d_out,
+ * int ic, int ih, int iw, int its, int id)  and  ::backward(float* d_dx, float* d_dy, float* d_c, float* d_b, float* d_inGrad,
+ * float* d_outGradX, float* d_outGradY, float* d_outGradC, float* d_outGradB, float* d_outGradI, int ic, int ih, int iw,
+ * int its, int id)   (cudaTGV/cudaCode/TGVInpaintFista.h:66-86, TGVInpaintFistaBetas.cu:2475-2618, :2621-3063),
+ * extended by a batch dimension and a stream.
+ *   dx = [wx, beta_x], dy = [wy, beta_y] : [n][2][h][w];  c [n][1][h][w];  b [n][ch][h][w]
+ *   init, out, grad_out, g_init          : [n][3*ch][h][w] ordered u(ch), v1(ch), v2(ch)  (what the reference's kernels
+ *                                          index; its binding allocates too few planes, TGVInpaintFista_cuda.cpp:91, :157)
+ *   g_dx, g_dy [n][2][h][w]; g_c [n][1][h][w]; g_b [n][ch][h][w]
+ * 1/Lipschitz is computed per image from the weights on every call and treated as a constant by the gradient.
+ * cnl_tgv_backward synchronises the stream once: like the reference it returns all-zero gradients when grad_out holds
+ * a non-finite value or is identically zero (TGVInpaintFistaBetas.cu:2698-2703), and that decision is taken on the host.
+ * cnl_tgv_read_state copies stored iterates for the parity tests: kind 0 = pre-prox iterate of iteration idx,
+ * kind 1 = checkpointed y number idx (both n*3*ch*h*w floats), kind 2 = the n per-image 1/Lipschitz factors.
+ */
+int cnl_tgv_forward(const float* dx, const float* dy, const float* c, const float* b, const float* init, float* out,
+                    int n, int ch, int h, int w, int its, int id, void* stream);
+int cnl_tgv_backward(const float* dx, const float* dy, const float* c, const float* b, const float* grad_out,
+                     float* g_dx, float* g_dy, float* g_c, float* g_b, float* g_init,
+                     int n, int ch, int h, int w, int its, int id, void* stream);
+int cnl_tgv_release(int id);
+int cnl_tgv_set_option(int id, int option, int value);
+int cnl_tgv_read_state(int id, int kind, int idx, float* dst, void* stream);
+int cnl_tgv_num_checkpoints(int id);
+
 /* Message for the last error on the calling thread ("" if none). */
 const char* cnl_last_error(void);
 

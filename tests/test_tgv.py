@@ -88,3 +88,98 @@ def test_zero_or_nonfinite_upstream_gradient_returns_zeros():
     g = I["grad"].clone(); g[0, 1, 0, 2, 3] = float("nan")
     z = G.tgv_backward(I["dx"], I["dy"], I["c"], I["b"], g, 4, hist, cky)
     assert all(float(t.abs().max()) == 0 for t in z)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def _run_cuda(ext, D, its, pid, n, ch, h, w):
+    flat = lambda t: t.reshape(n, 3 * ch, h, w)
+    sol = ext.forward(D["dx"], D["dy"], D["c"], D["b"], flat(D["init"]), its, pid)[0]
+    hist, cky, L = ext.read_history(pid, flat(D["init"]), its)
+    grads = ext.backward(flat(D["grad"]), D["dx"], D["dy"], D["c"], D["b"], its, pid)
+    torch.cuda.synchronize()
+    five = lambda t: t.reshape(t.shape[:-3] + (3, ch, h, w))
+    return five(sol), five(hist), five(cky), L, grads[:4] + [five(grads[4])]
+
+
+GPU_CASES = [(1, 1, 1, 1, 2), (1, 2, 5, 37, 4), (1, 1, 29, 3, 6), (2, 2, 40, 72, 20), (1, 3, 17, 33, 21), (1, 2, 96, 320, 20),
+             (1, 2, 64, 96, 50)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", GPU_CASES, ids=lambda c: "n%d_c%d_%dx%d_its%d" % c)
+def test_cuda_forward_history_and_reverse_sweep_match_oracle(case):
+    from customnetworklayers_b200 import tgvInpaint_cuda_ext as ext
+    n, ch, h, w, its = case
+    I = make_tgv_inputs(n, ch, h, w, seed=50 + h + w)
+    I["init"][:, 1:] = 0.1 * I["grad"][:, 1:]
+    D = {k: v.cuda() for k, v in I.items()}
+    ext.release(3)
+    ext.set_option(3, 1, 0)
+    sol, hist, cky, L, grads = _run_cuda(ext, D, its, 3, n, ch, h, w)
+    r_sol, r_hist, r_cky, _, r_L = G.tgv_forward_history(I["dx"], I["dy"], I["c"], I["b"], I["init"], its)
+    assert torch.equal(L.cpu(), r_L.reshape(-1)), "1/Lipschitz must be bit-exact"
+    assert_close(sol, r_sol, "solution")
+    assert_close(hist, r_hist, "history")
+    assert_close(cky, r_cky, "checkpointed y")
+    # reverse sweep on exactly the iterates the device stored (it is discontinuous at the Huber thresholds)
+    ref = G.tgv_backward(I["dx"], I["dy"], I["c"], I["b"], I["grad"], its, hist.cpu(), cky.cpu())
+    for name, g, r in zip(NAMES, grads, ref):
+        assert_close(g, r, name)
+
+
+@pytest.mark.gpu
+def test_cuda_reproduces_reference_kernel_outputs():
+    from customnetworklayers_b200 import tgvInpaint_cuda_ext as ext
+    for i, its, I, out in _golden_cases():
+        n, ch, h, w = I["b"].shape
+        D = {k: v.cuda() for k, v in I.items()}
+        ext.release(4)
+        ext.set_option(4, 1, 0)
+        sol, _, _, _, grads = _run_cuda(ext, D, its, 4, n, ch, h, w)
+        assert_close(sol, out["sol"], f"case {i} solution")
+        for name, g in zip(NAMES, grads):
+            assert_close(g, out[name], f"case {i} {name}")
+
+
+@pytest.mark.gpu
+def test_cuda_batch_equals_single_calls_and_skip_rule():
+    from customnetworklayers_b200 import tgvInpaint_cuda_ext as ext
+    n, ch, h, w, its = 3, 2, 30, 44, 8
+    I = make_tgv_inputs(n, ch, h, w, seed=77)
+    I["dx"][1, 1] = 30.0          # a different Lipschitz constant for the second image
+    D = {k: v.cuda() for k, v in I.items()}
+    for pid in (5, 6):
+        ext.release(pid)
+        ext.set_option(pid, 1, 0)
+    sol, _, _, L, grads = _run_cuda(ext, D, its, 5, n, ch, h, w)
+    assert float(L[1]) < float(L[0])
+    for i in range(n):
+        Di = {k: v[i:i + 1].contiguous() for k, v in D.items()}
+        s1, _, _, _, g1 = _run_cuda(ext, Di, its, 6, 1, ch, h, w)
+        assert torch.equal(s1[0], sol[i])
+        for name, a, b in zip(NAMES, g1, grads):
+            assert torch.equal(a[0], b[i]), name
+    # an identically zero or non-finite upstream gradient yields all-zero gradients
+    flat = lambda t: t.reshape(n, 3 * ch, h, w)
+    ext.forward(D["dx"], D["dy"], D["c"], D["b"], flat(D["init"]), its, 5)
+    z = ext.backward(torch.zeros_like(flat(D["grad"])), D["dx"], D["dy"], D["c"], D["b"], its, 5)
+    assert all(float(t.abs().max()) == 0 for t in z)
+    bad = flat(D["grad"]).clone(); bad[0, 0, 1, 1] = float("inf")
+    z = ext.backward(bad, D["dx"], D["dy"], D["c"], D["b"], its, 5)
+    assert all(float(t.abs().max()) == 0 for t in z)
+
+
+@pytest.mark.gpu
+def test_tgv_layer_api():
+    from customnetworklayers_b200.TGVInpainting import TGVInpaint
+    ch, h, w, its = 2, 24, 32, 6
+    I = make_tgv_inputs(1, ch, h, w, seed=9)
+    hwc = lambda t: t[0].permute(1, 2, 0).contiguous().cuda()
+    leaves = [hwc(I["dx"]), hwc(I["dy"]), hwc(I["c"]), hwc(I["b"]), hwc(I["init"].reshape(1, 3 * ch, h, w))]
+    leaves = [t.requires_grad_(True) for t in leaves]
+    out = TGVInpaint("cuda", its, pid=7)(*leaves)
+    assert out.shape == (h, w, 3 * ch)
+    out.backward(hwc(I["grad"].reshape(1, 3 * ch, h, w)))
+    assert all(t.grad is not None and torch.isfinite(t.grad).all() for t in leaves)
+    r_sol, *_ = G.tgv_forward_history(I["dx"], I["dy"], I["c"], I["b"], I["init"], its)
+    assert_close(out.permute(2, 0, 1).reshape(1, 3, ch, h, w), r_sol, "layer output")
