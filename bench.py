@@ -28,6 +28,7 @@ WORKLOADS = {
     "cfg1": (8, 2, 384, 1280, 100),
     "cfg0": (1, 2, 96, 320, 20),
     "small": (2, 2, 384, 1280, 20),      # profiling case: a few hundred MB on the device
+    "cfg2": (8, 2, 436, 1024, 100),      # TGV-FISTA (secondary workload, run with --workload cfg2)
 }
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
                "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -359,6 +360,78 @@ def run_ours(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_tgv(args, rank, local_rank, world):
+    """Secondary workload: TGV-FISTA fwd+bwd (batch 8 per GPU, 2x436x1024, 100 iterations); same JSON contract, the
+    roofline entry is the whole step against 376 B per pixel-iteration ((16C+5)*4 forward + (21C+15)*4 reverse)."""
+    import torch
+    import torch.distributed as dist
+    from customnetworklayers_b200 import _lib, tgvInpaint_cuda_ext as ext
+    from customnetworklayers_b200.dist import allreduce_scalar_grads
+    from customnetworklayers_b200.synthetic import make_tgv_inputs
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    nb, ch, h, w, its = WORKLOADS[args.workload]
+    its_eff = 2 * (its // 2)
+    I = make_tgv_inputs(nb, ch, h, w, seed=1236 + 1000 * rank)
+    D = {k: v.to(dev) for k, v in I.items()}
+    flat = lambda t: t.reshape(nb, 3 * ch, h, w)
+    alpha = torch.tensor([1.0, 2.0], device=dev)          # learned scalars alpha0 (edge weights), alpha1 (beta)
+    pid = 1
+
+    def step():
+        sol = ext.forward(D["dx"], D["dy"], D["c"], D["b"], flat(D["init"]), its, pid)[0]
+        g = ext.backward(flat(D["grad"]), D["dx"], D["dy"], D["c"], D["b"], its, pid)
+        # d/d alpha_k = sum over pixels of grad * raw map; dx = [alpha0*wx, alpha1*1]
+        g_alpha = torch.stack([(g[0][:, 0] * D["dx"][:, 0]).sum() + (g[1][:, 0] * D["dy"][:, 0]).sum(),
+                               (g[0][:, 1] * D["dx"][:, 1]).sum() + (g[1][:, 1] * D["dy"][:, 1]).sum()]) / alpha
+        allreduce_scalar_grads(g_alpha)
+        return sol, g_alpha
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = _lib.load().cnl_launch_count()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    launches = _lib.load().cnl_launch_count() - l0
+    clocks = sampler.stop()
+    if rank == 0:
+        pixel_iters = world * nb * h * w * its_eff
+        value = pixel_iters * args.steps / (ms * 1e-3) / 1e9
+        bytes_pi = (16 * ch + 5) * 4 + (21 * ch + 15) * 4
+        peak, kind = measured_peak_gbs()
+        ach = bytes_pi * pixel_iters / world * args.steps / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "tgv_fista_fwd_bwd_gpixel_iters_per_s", "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"cfg2: TGV-FISTA fwd+bwd, per-GPU batch {nb}, flow {ch}x{h}x{w} + 2 auxiliary planes per channel, {its} iterations, alpha gradients all-reduced",
+                       "global_batch": nb * world, "parallelism": f"dp{world}"},
+            "roofline": {"bound": "hbm", "kernel": "whole step (one launch per iteration)", "achieved": ach, "peak": peak,
+                         "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_kind": kind},
+            "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -384,6 +457,8 @@ def main():
         raise RuntimeError(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
+    elif args.workload == "cfg2":
+        run_tgv(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
 
