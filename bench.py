@@ -29,6 +29,7 @@ WORKLOADS = {
     "cfg0": (1, 2, 96, 320, 20),
     "small": (2, 2, 384, 1280, 20),      # profiling case: a few hundred MB on the device
     "cfg2": (8, 2, 436, 1024, 100),      # TGV-FISTA (secondary workload, run with --workload cfg2)
+    "cfg2small": (2, 2, 436, 1024, 10),  # TGV profiling case
 }
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
                "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -457,7 +458,7 @@ def main():
         raise RuntimeError(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
-    elif args.workload == "cfg2":
+    elif args.workload.startswith("cfg2"):
         run_tgv(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)

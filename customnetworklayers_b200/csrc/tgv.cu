@@ -79,11 +79,33 @@ __global__ void tgv_lipschitz_final_kernel(const int* __restrict__ lip_bits, flo
 
 // ---- shared-memory staging ------------------------------------------------------------------------------------
 // Copies the (TH+2) x (TW+2) frame of one plane into shared memory; zero outside the image.
-__device__ __forceinline__ void stage_plane(const float* __restrict__ src, float* __restrict__ dst, int h0, int w0, int H, int W) {
-    for (int i = threadIdx.x; i < YH * YW; i += NT) {
-        const int r = i / YW, c = i - r * YW;
-        const int h = h0 - 1 + r, w = w0 - 1 + c;
-        dst[i] = (h >= 0 && h < H && w >= 0 && w < W) ? src[(size_t)h * W + w] : 0.0f;
+constexpr int kStagePasses = (YH * YW + NT - 1) / NT;
+
+// Frame element handled by this thread in staging pass k: offset into the image plane, or -1 outside the image / frame.
+__device__ __forceinline__ long long stage_offset(int k, int h0, int w0, int H, int W) {
+    const int i = threadIdx.x + k * NT;
+    const int r = i / YW, c = i - r * YW;
+    const int h = h0 - 1 + r, w = w0 - 1 + c;
+    return (i < YH * YW && h >= 0 && h < H && w >= 0 && w < W) ? (long long)h * W + w : -1;
+}
+
+// All loads of the three planes are issued before the first shared-memory store (15 independent loads per thread).
+__device__ __forceinline__ void stage_planes3(const float* __restrict__ src, size_t plane_stride, float* __restrict__ dst,
+                                              int h0, int w0, int H, int W) {
+    float v[3][kStagePasses];
+#pragma unroll
+    for (int k = 0; k < kStagePasses; ++k) {
+        const long long o = stage_offset(k, h0, w0, H, W);
+#pragma unroll
+        for (int q = 0; q < 3; ++q) v[q][k] = o >= 0 ? src[(size_t)q * plane_stride + o] : 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < kStagePasses; ++k) {
+        const int i = threadIdx.x + k * NT;
+        if (i < YH * YW) {
+#pragma unroll
+            for (int q = 0; q < 3; ++q) dst[q * YH * YW + i] = v[q][k];
+        }
     }
 }
 
@@ -124,7 +146,7 @@ __device__ __forceinline__ Tri triangle(const float* __restrict__ Y, int r, int 
 }
 
 // ---- forward iteration (:1546-1776, with the history store of :2005-2236) ---------------------------------------
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NT, 2)
 tgv_fwd_kernel(const float* __restrict__ y_in, float* __restrict__ y_out, float* __restrict__ x,
                const float* __restrict__ b, const float* __restrict__ cf, const float* __restrict__ dx,
                const float* __restrict__ dy, const float* __restrict__ Lbuf, float* __restrict__ hist,
@@ -139,10 +161,12 @@ tgv_fwd_kernel(const float* __restrict__ y_in, float* __restrict__ y_out, float*
     for (int ch = 0; ch < C; ++ch) {
         const size_t base = n * 3 * C * plane + (size_t)ch * plane;        // plane k of this channel: base + k*C*plane
         __syncthreads();
-#pragma unroll
-        for (int k = 0; k < 3; ++k) stage_plane(y_in + base + (size_t)k * C * plane, Y + k * YH * YW, h0, w0, H, W);
+        stage_planes3(y_in + base, (size_t)C * plane, Y, h0, w0, H, W);
         __syncthreads();
-        for (int i = threadIdx.x; i < FH * FW; i += NT) {
+#pragma unroll
+        for (int kk = 0; kk < (FH * FW + NT - 1) / NT; ++kk) {
+            const int i = threadIdx.x + kk * NT;
+            if (i >= FH * FW) break;
             const int r = i / FW, c = i - r * FW;
             const Tri tr = triangle(Y, r, c, h0 - 1 + r, w0 - 1 + c, H, W, m, L);
             F[0 * FH * FW + i] = tr.wx * tr.z1 * tr.Hu;
@@ -153,7 +177,22 @@ tgv_fwd_kernel(const float* __restrict__ y_in, float* __restrict__ y_out, float*
             F[5 * FH * FW + i] = tr.b[1] * tr.a2[1] * tr.H[1];
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < TH * TW; i += NT) {
+        float xin[(TH * TW) / NT][3], bin[(TH * TW) / NT], cin[(TH * TW) / NT];
+#pragma unroll
+        for (int kk = 0; kk < (TH * TW) / NT; ++kk) {
+            const int i = threadIdx.x + kk * NT;
+            const int r = i / TW, c = i - r * TW;
+            const int h = h0 + r, w = w0 + c;
+            const bool ok = h < H && w < W;
+            const size_t pix = ok ? (size_t)h * W + w : 0;
+#pragma unroll
+            for (int q = 0; q < 3; ++q) xin[kk][q] = ok ? x[base + (size_t)q * C * plane + pix] : 0.f;
+            bin[kk] = ok ? __ldg(b + (n * C + ch) * plane + pix) : 0.f;
+            cin[kk] = ok ? __ldg(cf + n * plane + pix) : 0.f;
+        }
+#pragma unroll
+        for (int kk = 0; kk < (TH * TW) / NT; ++kk) {
+            const int i = threadIdx.x + kk * NT;
             const int r = i / TW, c = i - r * TW;
             const int h = h0 + r, w = w0 + c;
             if (h >= H || w >= W) continue;
@@ -168,15 +207,13 @@ tgv_fwd_kernel(const float* __restrict__ y_in, float* __restrict__ y_out, float*
                 const float* Gy = F + (3 + 2 * j) * FH * FW;
                 vnew[j] = Y[(1 + j) * YH * YW + yo] + Gx[fo] + Gy[fo] - Gx[fo - 1] - Gy[fo - FW] + (j == 0 ? Fx[fo] : Fy[fo]);
             }
-            const float conf = __ldg(cf + n * plane + pix);
-            const float bb = __ldg(b + (n * C + ch) * plane + pix);
-            const float xu = prox_huber(u_half, bb, conf);
+            const float xu = prox_huber(u_half, bin[kk], cin[kk]);
             const float news[3] = {xu, vnew[0], vnew[1]};
             const float halfs[3] = {u_half, vnew[0], vnew[1]};
 #pragma unroll
             for (int k = 0; k < 3; ++k) {
                 const size_t o = base + (size_t)k * C * plane + pix;
-                const float xp = x[o];
+                const float xp = xin[kk][k];
                 hist[o] = halfs[k];
                 x[o] = news[k];
                 y_out[o] = news[k] + t * (news[k] - xp);
@@ -217,7 +254,7 @@ constexpr int kPixPasses = (TH * TW) / NT;
 //   ckpt             : if non-null all three planes of y come from this checkpoint instead
 //   typo             : reproduce the reference's factor W/rsqrt(A)^2 in the v2 term arriving from the triangle
 //                      above (:355, :804); the reference's segment-start kernel does not have it
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NT, 2)
 tgv_rev_kernel(const float* __restrict__ hist_g, const float* __restrict__ hist_gm1, const float* __restrict__ ckpt,
                const float* __restrict__ g_in, float* __restrict__ g_out, float* __restrict__ acc,
                const float* __restrict__ b, const float* __restrict__ cf, const float* __restrict__ dx,
@@ -244,25 +281,34 @@ tgv_rev_kernel(const float* __restrict__ hist_g, const float* __restrict__ hist_
         const size_t base = n * 3 * C * plane + (size_t)ch * plane;
         const size_t bbase = (n * C + ch) * plane;
         __syncthreads();
-        // phase 0: stage y and the incoming adjoint
-        for (int i = threadIdx.x; i < YH * YW; i += NT) {
-            const int r = i / YW, c = i - r * YW;
-            const int h = h0 - 1 + r, w = w0 - 1 + c;
-            float yu = 0.f, y1 = 0.f, y2 = 0.f, q0 = 0.f, q1 = 0.f, q2 = 0.f;
-            if (h >= 0 && h < H && w >= 0 && w < W) {
-                const size_t pix = (size_t)h * W + w;
-                const size_t o = base + pix;
-                if (ckpt) {
-                    yu = ckpt[o]; y1 = ckpt[o + (size_t)C * plane]; y2 = ckpt[o + 2 * (size_t)C * plane];
-                } else {
-                    yu = rederive_y(hist_g[o], hist_gm1[o], __ldg(b + bbase + pix), __ldg(cf + n * plane + pix), t);
-                    y1 = hist_g[o + (size_t)C * plane];
-                    y2 = hist_g[o + 2 * (size_t)C * plane];
+        // phase 0: stage y and the incoming adjoint; every load of a pass is issued before the arithmetic
+        {
+            float hg[3][kStagePasses], hm[kStagePasses], bq[kStagePasses], cq[kStagePasses], qq[3][kStagePasses];
+#pragma unroll
+            for (int k = 0; k < kStagePasses; ++k) {
+                const long long pix = stage_offset(k, h0, w0, H, W);
+                const bool ok = pix >= 0;
+                const size_t o = base + (ok ? (size_t)pix : 0);
+                const float* ysrc = ckpt ? ckpt : hist_g;
+#pragma unroll
+                for (int q = 0; q < 3; ++q) {
+                    hg[q][k] = ok ? ysrc[o + (size_t)q * C * plane] : 0.f;
+                    qq[q][k] = ok ? g_in[o + (size_t)q * C * plane] : 0.f;
                 }
-                q0 = g_in[o]; q1 = g_in[o + (size_t)C * plane]; q2 = g_in[o + 2 * (size_t)C * plane];
+                hm[k] = (ok && !ckpt) ? hist_gm1[o] : 0.f;
+                bq[k] = (ok && !ckpt) ? __ldg(b + bbase + pix) : 0.f;
+                cq[k] = (ok && !ckpt) ? __ldg(cf + n * plane + pix) : 0.f;
             }
-            Y[i] = yu; Y[YH * YW + i] = y1; Y[2 * YH * YW + i] = y2;
-            Gq[i] = q0; Gq[YH * YW + i] = q1; Gq[2 * YH * YW + i] = q2;
+#pragma unroll
+            for (int k = 0; k < kStagePasses; ++k) {
+                const int i = threadIdx.x + k * NT;
+                if (i >= YH * YW) break;
+                const bool ok = stage_offset(k, h0, w0, H, W) >= 0;
+                float yu = hg[0][k];
+                if (ok && !ckpt) yu = rederive_y(hg[0][k], hm[k], bq[k], cq[k], t);
+                Y[i] = yu; Y[YH * YW + i] = hg[1][k]; Y[2 * YH * YW + i] = hg[2][k];
+                Gq[i] = qq[0][k]; Gq[YH * YW + i] = qq[1][k]; Gq[2 * YH * YW + i] = qq[2][k];
+            }
         }
         __syncthreads();
         // phase 1: adjoint fluxes per triangle
@@ -309,7 +355,23 @@ tgv_rev_kernel(const float* __restrict__ hist_g, const float* __restrict__ hist_
             gw[k][0] += gwu_x; gw[k][1] += gbeta[0]; gw[k][2] += gwu_y; gw[k][3] += gbeta[1];
         }
         __syncthreads();
-        // phase 2: divergence of the adjoint fluxes, momentum reverse, prox Jacobian
+        // phase 2: divergence of the adjoint fluxes, momentum reverse, prox Jacobian.  The pointwise operands of all
+        // passes are loaded first so that their latencies overlap.
+        float accv[kPixPasses][3], hu[kPixPasses], bv[kPixPasses], cv[kPixPasses], gbv[kPixPasses];
+#pragma unroll
+        for (int k = 0; k < kPixPasses; ++k) {
+            const int i = threadIdx.x + k * NT;
+            const int r = i / TW, c = i - r * TW;
+            const int h = h0 + r, w = w0 + c;
+            const bool ok = h < H && w < W;
+            const size_t pix = ok ? (size_t)h * W + w : 0;
+#pragma unroll
+            for (int q = 0; q < 3; ++q) accv[k][q] = ok ? acc[base + (size_t)q * C * plane + pix] : 0.f;
+            hu[k] = ok ? hist_g[base + pix] : 0.f;
+            bv[k] = ok ? __ldg(b + bbase + pix) : 0.f;
+            cv[k] = ok ? __ldg(cf + n * plane + pix) : 0.f;
+            gbv[k] = ok ? g_b[bbase + pix] : 0.f;
+        }
 #pragma unroll
         for (int k = 0; k < kPixPasses; ++k) {
             const int i = threadIdx.x + k * NT;
@@ -329,14 +391,13 @@ tgv_rev_kernel(const float* __restrict__ hist_g, const float* __restrict__ hist_
 #pragma unroll
             for (int q = 0; q < 3; ++q) {
                 const size_t o = base + (size_t)q * C * plane + pix;
-                xbar[q] = clampf(acc[o] + (1.0f + t) * ybar[q], -kClip, kClip);
+                xbar[q] = clampf(accv[k][q] + (1.0f + t) * ybar[q], -kClip, kClip);
                 acc[o] = -t * ybar[q];
                 if (x1bar) x1bar[o] = xbar[q];
             }
             float dgb = 0.f;
-            g_out[base + pix] = prox_reverse(xbar[0], hist_g[base + pix], __ldg(b + bbase + pix), __ldg(cf + n * plane + pix),
-                                             gconf[k], dgb);
-            g_b[bbase + pix] += dgb;
+            g_out[base + pix] = prox_reverse(xbar[0], hu[k], bv[k], cv[k], gconf[k], dgb);
+            g_b[bbase + pix] = gbv[k] + dgb;
             g_out[base + (size_t)C * plane + pix] = xbar[1];
             g_out[base + 2 * (size_t)C * plane + pix] = xbar[2];
         }
