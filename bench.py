@@ -30,6 +30,7 @@ WORKLOADS = {
     "small": (2, 2, 384, 1280, 20),      # profiling case: a few hundred MB on the device
     "cfg2": (8, 2, 436, 1024, 100),      # TGV-FISTA (secondary workload, run with --workload cfg2)
     "cfg2small": (2, 2, 436, 1024, 10),  # TGV profiling case
+    "cfg3": (16, 2, 512, 960, 50),       # coarse-to-fine stack of three TV layers (ids 0,1,2) with quadratic-fit refinement
 }
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
                "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -433,6 +434,77 @@ def run_tgv(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_hierarchy(args, rank, local_rank, world):
+    """Secondary workload: three TV layers at 1/4, 1/2 and full resolution (ids 0, 1, 2; 50 iterations each), a
+    quadratic-fit refinement before each level, bilinear x2 upsampling between levels, full fwd+bwd; the three lambda
+    gradients are all-reduced.  Metric counts the TV pixel-iterations of all levels."""
+    import torch
+    import torch.distributed as dist
+    from customnetworklayers_b200 import _lib
+    from customnetworklayers_b200.hierarchical import HierarchicalTV
+    from customnetworklayers_b200.synthetic import make_hierarchy_inputs
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    nb, ch, h, w, its = WORKLOADS[args.workload]
+    its_eff = 2 * (its // 2)
+    levels, grad = make_hierarchy_inputs(nb, h, w, seed=1237 + 1000 * rank)
+    D = [{k: v.to(dev).requires_grad_(k == "cost5") for k, v in I.items()} for I in levels]
+    grad = grad.to(dev)
+    model = HierarchicalTV(levels=3, its=its).to(dev)
+
+    def step():
+        model.zero_grad(set_to_none=True)
+        for d in D:
+            d["cost5"].grad = None
+        sols = model(D)
+        sols[-1].backward(grad)
+        model.allreduce_parameter_grads()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = _lib.load().cnl_launch_count()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    launches = _lib.load().cnl_launch_count() - l0
+    clocks = sampler.stop()
+    if rank == 0:
+        pixel_iters = world * nb * sum((h >> s) * (w >> s) for s in (2, 1, 0)) * its_eff
+        value = pixel_iters * args.steps / (ms * 1e-3) / 1e9
+        peak, kind = measured_peak_gbs()
+        fwd_b, rev_b = algorithmic_bytes_per_pixel_iter(ch)
+        ach = (fwd_b + rev_b) * pixel_iters / world * args.steps / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "hierarchical_tv_fwd_bwd_gpixel_iters_per_s", "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"cfg3: 3-level TV stack (ids 0,1,2), per-GPU batch {nb}, flow {ch}x{h}x{w}, {its} iterations per level, quadratic-fit refinement and bilinear upsampling between levels",
+                       "global_batch": nb * world, "parallelism": f"dp{world}"},
+            "roofline": {"bound": "hbm", "kernel": "whole step (TV pixel-iterations only)", "achieved": ach, "peak": peak,
+                         "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_kind": kind},
+            "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -458,6 +530,8 @@ def main():
         raise RuntimeError(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
+    elif args.workload == "cfg3":
+        run_hierarchy(args, rank, local_rank, world)
     elif args.workload.startswith("cfg2"):
         run_tgv(args, rank, local_rank, world)
     else:

@@ -100,3 +100,19 @@ def make_tgv_inputs(n: int, ch: int, h: int, w: int, seed: int = 1236, conf_p: f
     init[:, 0] = I["b"]
     grad = torch.randn(n, 3, ch, h, w, generator=gen).float()
     return {"dx": dx, "dy": dy, "c": I["c"], "b": I["b"], "init": init.contiguous(), "grad": grad.contiguous()}
+
+
+def make_hierarchy_inputs(n: int, h: int, w: int, levels: int = 3, seed: int = 1237):
+    """Inputs of the coarse-to-fine stack: per level (coarse to fine, each half the next one's size) edge weights,
+    confidence, integer match offsets uniform in +-64 px (scaled with the level) and 5-point cost stencils."""
+    out = []
+    for l in range(levels):
+        s = 2 ** (levels - 1 - l)
+        hl, wl = h // s, w // s
+        I = make_inputs(n, 2, hl, wl, seed=seed + 10 * l)
+        gen = torch.Generator().manual_seed(seed + 10 * l + 5)
+        offsets = torch.randint(-64 // s, 64 // s + 1, (n, 2, hl, wl), generator=gen).float()
+        cost5, _ = make_cost_patches(n, hl, wl, seed=seed + 10 * l + 7)
+        out.append({"wx": I["wx"], "wy": I["wy"], "c": I["c"], "offsets": offsets.contiguous(), "cost5": cost5})
+    grad = torch.randn(n, 2, h, w, generator=torch.Generator().manual_seed(seed + 99)).float()
+    return out, grad
