@@ -1,0 +1,265 @@
+// Learnable weighted-median filter for sm_100a, built around the reference's selection rule
+// (cudaMedian/cudaCode/medimax.cu:17-100): k x k window (replicate border), taps sorted by value (stable), the k*k
+// normalised weights permuted alike, sequential fp32 running sum, first rank with score < 0.5 <= score + p selected.
+// Output = value of the selected tap; the window, the sort and the pass-through input gradient have no counterpart in
+// the reference.
+//
+// One thread per (image, channel, pixel).  The K = k*k window values live in registers; the rank of every tap is
+// found by comparing it with all others (K*(K-1) compares, no data-dependent branches), which places its weight at
+// its sorted position in a thread-private column of shared memory; the scan then runs over that column in rank
+// order, i.e. in exactly the order the selection rule prescribes, so the selected index is bit-identical to the
+// CPU restatement.  The [N,H,W,K] weight volume of the reference layout is never materialised: HBM traffic is one
+// read and one write per pixel, the kernel is bound by the compares.
+#include "common.h"
+
+namespace cnl {
+namespace wmed {
+
+constexpr int NT = 128;
+constexpr int kMaxK = 49;
+
+// The k*k normalised weights (device memory) are copied to shared memory once per block; every thread then reads them
+// with compile-time indices (broadcast).
+template <int K>
+__device__ __forceinline__ void stage_weights(const float* __restrict__ weights, float* sp) {
+    if (threadIdx.x < K) sp[threadIdx.x] = weights[threadIdx.x];
+    __syncthreads();
+}
+
+template <int KS>
+__device__ __forceinline__ void load_window(const float* __restrict__ img, int h, int w, int H, int W, float (&v)[KS * KS]) {
+    constexpr int R = KS / 2;
+#pragma unroll
+    for (int dy = 0; dy < KS; ++dy) {
+        const int yy = min(max(h + dy - R, 0), H - 1);
+#pragma unroll
+        for (int dx = 0; dx < KS; ++dx) {
+            const int xx = min(max(w + dx - R, 0), W - 1);
+            v[dy * KS + dx] = __ldg(img + (size_t)yy * W + xx);
+        }
+    }
+}
+
+// rank of tap i in the stable ascending order
+template <int K>
+__device__ __forceinline__ int rank_of(const float (&v)[K], int i_static, float vi) {
+    int r = 0;
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+        if (j < i_static) r += (v[j] <= vi) ? 1 : 0;
+        else if (j > i_static) r += (v[j] < vi) ? 1 : 0;
+    }
+    return r;
+}
+
+struct Crossing {
+    int rank;          // -1: the weights never reach 0.5
+    float pmid, alpha;
+};
+
+template <int K>
+__device__ __forceinline__ Crossing scan_sorted(const float* __restrict__ sw) {
+    Crossing c;
+    c.rank = -1; c.pmid = 1.0f; c.alpha = 0.0f;
+    float score = 0.0f;
+    for (int r = 0; r < K; ++r) {
+        const float p = sw[r * NT];
+        const float nxt = score + p;
+        if (score < 0.5f && nxt >= 0.5f) {                       // medimax.cu:30
+            c.rank = r;
+            c.pmid = p;
+            c.alpha = (float)((1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p));     // :33
+            break;
+        }
+        score = nxt;
+    }
+    return c;
+}
+
+template <int KS>
+__global__ void __launch_bounds__(NT)
+wmedian_forward_kernel(const float* __restrict__ flow, const float* __restrict__ weights, float* __restrict__ out,
+                       int* __restrict__ tap, long long total, int H, int W) {
+    constexpr int K = KS * KS;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ float sp[K];
+    stage_weights<K>(weights, sp);
+    float* sw = reinterpret_cast<float*>(smem_raw) + threadIdx.x;                      // sw[r * NT]
+    unsigned char* sidx = smem_raw + (size_t)K * NT * sizeof(float) + threadIdx.x;     // sidx[r * NT]
+    const long long plane = (long long)H * W;
+    for (long long idx = (long long)blockIdx.x * NT + threadIdx.x; idx < total; idx += (long long)gridDim.x * NT) {
+        const long long img = idx / plane;
+        const int pix = (int)(idx - img * plane), h = pix / W, w = pix - h * W;
+        const float* src = flow + img * plane;
+        float v[K];
+        load_window<KS>(src, h, w, H, W, v);
+#pragma unroll
+        for (int i = 0; i < K; ++i) {
+            const int r = rank_of<K>(v, i, v[i]);
+            sw[r * NT] = sp[i];
+            sidx[r * NT] = (unsigned char)i;
+        }
+        const Crossing c = scan_sorted<K>(sw);
+        int t = -1;
+        float o = v[K / 2];                                      // no crossing: the centre value passes through
+        if (c.rank >= 0) {
+            t = sidx[c.rank * NT];
+            const int dy = t / KS - KS / 2, dx = t % KS - KS / 2;
+            o = __ldg(src + (size_t)min(max(h + dy, 0), H - 1) * W + min(max(w + dx, 0), W - 1));
+        }
+        out[idx] = o;
+        if (tap) tap[idx] = t;
+    }
+}
+
+// Weight gradient: per problem d/dp in sorted order (medimax.cu:73, :91-95 with the output gradient as g0, g1 = 0),
+// scattered back to the taps and accumulated per thread in shared memory, reduced per block in a fixed order.
+template <int KS>
+__global__ void __launch_bounds__(NT)
+wmedian_weight_grad_kernel(const float* __restrict__ flow, const float* __restrict__ weights, const float* __restrict__ grad,
+                           double* __restrict__ partial, long long total, int H, int W) {
+    constexpr int K = KS * KS;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ float sp[K];
+    stage_weights<K>(weights, sp);
+    float* sw = reinterpret_cast<float*>(smem_raw) + threadIdx.x;
+    float* sacc = reinterpret_cast<float*>(smem_raw) + (size_t)K * NT + threadIdx.x;
+    unsigned char* srank = smem_raw + (size_t)2 * K * NT * sizeof(float) + threadIdx.x;
+    const long long plane = (long long)H * W;
+#pragma unroll
+    for (int i = 0; i < K; ++i) sacc[i * NT] = 0.0f;
+    for (long long idx = (long long)blockIdx.x * NT + threadIdx.x; idx < total; idx += (long long)gridDim.x * NT) {
+        const long long img = idx / plane;
+        const int pix = (int)(idx - img * plane), h = pix / W, w = pix - h * W;
+        float v[K];
+        load_window<KS>(flow + img * plane, h, w, H, W, v);
+#pragma unroll
+        for (int i = 0; i < K; ++i) {
+            const int r = rank_of<K>(v, i, v[i]);
+            sw[r * NT] = sp[i];
+            srank[i * NT] = (unsigned char)r;
+        }
+        const Crossing c = scan_sorted<K>(sw);
+        const float g0 = grad[idx];
+        const float half = (float)((double)g0 / (2.0 * (double)c.pmid));
+        const float mid = __fdiv_rn(__fmul_rn(g0, c.alpha), -c.pmid);
+        const int j = c.rank < 0 ? K : c.rank;                   // no crossing: every bin counts as "before"
+#pragma unroll
+        for (int i = 0; i < K; ++i) {
+            const int r = srank[i * NT];
+            sacc[i * NT] += (r < j) ? -half : ((r > j) ? half : mid);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < K) {
+        const float* row = reinterpret_cast<float*>(smem_raw) + (size_t)K * NT + (size_t)threadIdx.x * NT;
+        double s = 0.0;
+        for (int t = 0; t < NT; ++t) s += (double)row[t];
+        partial[(size_t)blockIdx.x * K + threadIdx.x] = s;
+    }
+}
+
+__global__ void __launch_bounds__(64)
+wmedian_weight_grad_final_kernel(const double* __restrict__ partial, int nblocks, int K, float* __restrict__ g_p) {
+    const int i = threadIdx.x;
+    if (i >= K) return;
+    double s = 0.0;
+    for (int b = 0; b < nblocks; ++b) s += partial[(size_t)b * K + i];
+    g_p[i] = (float)s;
+}
+
+// Input gradient, gather form: pixel q collects the upstream gradient of every pixel p in its neighbourhood whose
+// selected tap lands on q (after the replicate-border clamp).  Fixed summation order, no atomics.
+template <int KS>
+__global__ void __launch_bounds__(256)
+wmedian_input_grad_kernel(const int* __restrict__ tap, const float* __restrict__ grad, float* __restrict__ g_flow,
+                          long long total, int H, int W) {
+    constexpr int R = KS / 2;
+    const long long plane = (long long)H * W;
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total) return;
+    const long long img = idx / plane;
+    const int pix = (int)(idx - img * plane), qh = pix / W, qw = pix - qh * W;
+    const int* tp = tap + img * plane;
+    const float* gp = grad + img * plane;
+    float s = 0.0f;
+    for (int ph = max(qh - R, 0); ph <= min(qh + R, H - 1); ++ph)
+        for (int pw = max(qw - R, 0); pw <= min(qw + R, W - 1); ++pw) {
+            int t = __ldg(tp + (size_t)ph * W + pw);
+            if (t < 0) t = (KS * KS - 1) / 2;                       // no crossing: the centre passed through
+            const int th = min(max(ph + t / KS - R, 0), H - 1), tw = min(max(pw + t % KS - R, 0), W - 1);
+            if (th == qh && tw == qw) s += __ldg(gp + (size_t)ph * W + pw);
+        }
+    g_flow[idx] = s;
+}
+
+constexpr int kGradBlocks = 592;
+
+template <int KS>
+static int run_forward(const float* flow, const float* wts, float* out, int* tap, long long total, int H, int W, cudaStream_t st) {
+    constexpr int K = KS * KS;
+    const int smem = K * NT * (int)sizeof(float) + K * NT;
+    CNL_TRY(check_cuda(cudaFuncSetAttribute(wmedian_forward_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"));
+    const unsigned blocks = (unsigned)std::min<long long>((total + NT - 1) / NT, 148LL * 64);
+    wmedian_forward_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, out, tap, total, H, W);
+    return after_launch("wmedian_forward_kernel");
+}
+
+template <int KS>
+static int run_backward(const float* flow, const float* wts, const int* tap, const float* grad, float* g_flow, float* g_p,
+                        double* scratch, long long total, int H, int W, cudaStream_t st) {
+    constexpr int K = KS * KS;
+    const int smem = 2 * K * NT * (int)sizeof(float) + K * NT;
+    CNL_TRY(check_cuda(cudaFuncSetAttribute(wmedian_weight_grad_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"));
+    const int blocks = (int)std::min<long long>((total + NT - 1) / NT, kGradBlocks);
+    wmedian_weight_grad_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, grad, scratch, total, H, W);
+    CNL_TRY(after_launch("wmedian_weight_grad_kernel"));
+    wmedian_weight_grad_final_kernel<<<1, 64, 0, st>>>(scratch, blocks, K, g_p);
+    CNL_TRY(after_launch("wmedian_weight_grad_final_kernel"));
+    wmedian_input_grad_kernel<KS><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(tap, grad, g_flow, total, H, W);
+    return after_launch("wmedian_input_grad_kernel");
+}
+
+static int check(int n, int c, int h, int w, int k) {
+    if (n < 1 || c < 1 || h < 1 || w < 1) return fail(CNL_ERR_BAD_SHAPE, "n, c, h, w must be >= 1 (got %d, %d, %d, %d)", n, c, h, w);
+    if ((long long)h * w > 0x3fffffffLL) return fail(CNL_ERR_BAD_SHAPE, "image beyond the supported range");
+    if (k != 3 && k != 5 && k != 7) return fail(CNL_ERR_BAD_SHAPE, "window size must be 3, 5 or 7 (got %d)", k);
+    return CNL_OK;
+}
+
+}  // namespace wmed
+}  // namespace cnl
+
+using namespace cnl;
+
+extern "C" long long cnl_wmedian_scratch_bytes(int k) { return (long long)wmed::kGradBlocks * k * k * (long long)sizeof(double); }
+
+extern "C" int cnl_wmedian_forward(const float* flow, const float* weights, float* out, int* tap, int n, int c, int h,
+                                   int w, int k, void* stream) {
+    if (!flow || !weights || !out) return fail(CNL_ERR_NULL, "null pointer argument");
+    CNL_TRY(wmed::check(n, c, h, w, k));
+    const float* wts = weights;
+    const long long total = (long long)n * c * h * w;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (k) {
+        case 3: return wmed::run_forward<3>(flow, wts, out, tap, total, h, w, st);
+        case 5: return wmed::run_forward<5>(flow, wts, out, tap, total, h, w, st);
+        default: return wmed::run_forward<7>(flow, wts, out, tap, total, h, w, st);
+    }
+}
+
+extern "C" int cnl_wmedian_backward(const float* flow, const float* weights, const int* tap, const float* grad,
+                                    float* g_flow, float* g_weights, void* scratch, int n, int c, int h, int w, int k,
+                                    void* stream) {
+    if (!flow || !weights || !tap || !grad || !g_flow || !g_weights || !scratch) return fail(CNL_ERR_NULL, "null pointer argument");
+    CNL_TRY(wmed::check(n, c, h, w, k));
+    const float* wts = weights;
+    const long long total = (long long)n * c * h * w;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    double* sc = static_cast<double*>(scratch);
+    switch (k) {
+        case 3: return wmed::run_backward<3>(flow, wts, tap, grad, g_flow, g_weights, sc, total, h, w, st);
+        case 5: return wmed::run_backward<5>(flow, wts, tap, grad, g_flow, g_weights, sc, total, h, w, st);
+        default: return wmed::run_backward<7>(flow, wts, tap, grad, g_flow, g_weights, sc, total, h, w, st);
+    }
+}

@@ -116,3 +116,15 @@ def make_hierarchy_inputs(n: int, h: int, w: int, levels: int = 3, seed: int = 1
         out.append({"wx": I["wx"], "wy": I["wy"], "c": I["c"], "offsets": offsets.contiguous(), "cost5": cost5})
     grad = torch.randn(n, 2, h, w, generator=torch.Generator().manual_seed(seed + 99)).float()
     return out, grad
+
+
+def make_median_filter_inputs(n: int, c: int, h: int, w: int, k: int = 7, seed: int = 1238):
+    """Flow ~ U(-20,20) with 5 % of the pixels replaced by outliers ~ U(-200,200); k*k raw weights ~ U(0.5,1.5);
+    upstream gradient ~ N(0,1).  Returns (flow, raw_weights, grad) as fp32 CPU tensors."""
+    gen = torch.Generator().manual_seed(seed)
+    flow = torch.rand(n, c, h, w, generator=gen) * 40.0 - 20.0
+    outlier = torch.rand(n, c, h, w, generator=gen) < 0.05
+    flow = torch.where(outlier, torch.rand(n, c, h, w, generator=gen) * 400.0 - 200.0, flow)
+    weights = torch.rand(k * k, generator=gen) + 0.5
+    grad = torch.randn(n, c, h, w, generator=gen)
+    return flow.float().contiguous(), weights.float(), grad.float().contiguous()

@@ -1,0 +1,88 @@
+"""Learnable weighted-median filter: oracle self-checks on CPU, GPU parity (selected tap bit-exact) through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from customnetworklayers_b200.synthetic import make_median_filter_inputs
+from oracle import median_ref as M
+from oracle import wmedian_ref as W
+from tests.parity import assert_close
+
+
+def test_uniform_weights_give_the_plain_median():
+    flow, _, _ = make_median_filter_inputs(1, 2, 9, 11, seed=1)
+    for k in (3, 5, 7):
+        p = np.full(k * k, 1.0 / (k * k), np.float32)
+        out, tap, _ = W.wmedian_forward(flow.numpy(), p, k)
+        win, _, _ = W._windows(flow.numpy(), k)
+        assert np.array_equal(out, np.sort(win, axis=-1)[..., (k * k) // 2])
+
+
+def test_selection_equals_the_reference_rule_on_the_materialised_volume():
+    """Permuting the weights by the sort and running the reference layer's oracle gives the same crossing rank."""
+    flow, wts, _ = make_median_filter_inputs(1, 1, 6, 7, seed=2)
+    p = (wts / wts.sum()).numpy()
+    out, tap, aux = W.wmedian_forward(flow.numpy(), p, 7)
+    vol = p[aux["order"]][0]                      # [C=1,H,W,K] -> treat C as batch
+    _, idx = M.median_forward(vol)
+    assert np.array_equal(idx, aux["rank"][0])
+
+
+def test_weight_gradient_sums_reference_dp_through_the_permutation():
+    flow, wts, grad = make_median_filter_inputs(1, 1, 5, 6, seed=3)
+    p = (wts / wts.sum()).numpy()
+    _, _, aux = W.wmedian_forward(flow.numpy(), p, 7)
+    g_flow, g_p = W.wmedian_backward(flow.numpy(), p, grad.numpy(), 7)
+    vol = p[aux["order"]][0]
+    g2 = np.zeros((1, 2, 5, 6), np.float32); g2[0, 0] = grad.numpy()[0, 0]
+    dvol = M.median_backward(vol, g2)              # reference d/dp in sorted order
+    ref = np.zeros(49)
+    np.add.at(ref, aux["order"][0].reshape(-1), dvol.astype(np.float64).reshape(-1))
+    assert np.allclose(g_p, ref, rtol=1e-6, atol=1e-6)
+    assert abs(float(g_flow.sum()) - float(grad.sum())) < 1e-3       # pass-through conserves the gradient mass
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [(1, 1, 1, 1, 7), (1, 2, 9, 11, 3), (2, 2, 17, 33, 5), (1, 2, 40, 56, 7), (3, 1, 8, 64, 7)],
+                         ids=lambda c: "n%d_c%d_%dx%d_k%d" % c)
+def test_cuda_matches_oracle(case):
+    from customnetworklayers_b200 import wmedian as wm
+    n, c, h, w, k = case
+    flow, wts, grad = make_median_filter_inputs(n, c, h, w, k=k, seed=10 + k)
+    if h * w > 4:
+        flow[0, 0, 1, :3] = 5.0                    # ties: the stable order decides
+    p = (wts / wts.sum()).float()
+    out, tap = wm.forward(flow.cuda(), p.cuda(), k)
+    g_flow, g_p = wm.backward(flow.cuda(), p.cuda(), tap, grad.cuda(), k)
+    o_ref, t_ref, _ = W.wmedian_forward(flow.numpy(), p.numpy(), k)
+    gf_ref, gp_ref = W.wmedian_backward(flow.numpy(), p.numpy(), grad.numpy(), k)
+    assert np.array_equal(tap.cpu().numpy(), t_ref), "selected tap must be bit-exact"
+    assert np.array_equal(out.cpu().numpy(), o_ref)
+    assert_close(g_flow, torch.from_numpy(gf_ref), "g_flow", tol=1e-5)
+    assert_close(g_p, torch.from_numpy(gp_ref), "g_weights")
+
+
+@pytest.mark.gpu
+def test_filter_module_learns_through_normalisation():
+    from customnetworklayers_b200.wmedian import WeightedMedianFilter
+    flow, wts, grad = make_median_filter_inputs(2, 2, 24, 32, seed=5)
+    m = WeightedMedianFilter(7).cuda()
+    with torch.no_grad():
+        m.weight.copy_(wts)
+    x = flow.cuda().requires_grad_(True)
+    y = m(x)
+    y.backward(grad.cuda())
+    m.allreduce_parameter_grads()
+    p = (wts / wts.sum()).float()
+    _, gp_ref = W.wmedian_backward(flow.numpy(), p.numpy(), grad.numpy(), 7)
+    # chain rule through p = w / sum(w)
+    s = float(wts.sum())
+    gp = torch.from_numpy(gp_ref)
+    ref_w = (gp - (gp * p.double()).sum()) / s
+    assert_close(m.weight.grad, ref_w, "weight gradient", tol=2e-4)
+    assert x.grad.shape == x.shape
+    # twice: deterministic
+    m.weight.grad = None
+    x2 = flow.cuda().requires_grad_(True)
+    m(x2).backward(grad.cuda())
+    assert torch.equal(x2.grad, x.grad)
