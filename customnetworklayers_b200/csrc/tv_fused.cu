@@ -1,6 +1,9 @@
 // Register-tiled, temporally blocked TV-FISTA kernels for sm_100a (geometry: see tv_fused.cuh).
 #include "tv_fused.cuh"
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.h"
 #include "tv_math.cuh"
 
@@ -21,14 +24,58 @@ __device__ __forceinline__ void st4(float* p, const float4& v) { *reinterpret_ca
 __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
 __device__ __forceinline__ void add4(float4& a, const float4& b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
 
-// Fluxes of the four triangles anchored at one lane's pixels of a row.  `yd` is the row below.
+// 16-byte asynchronous global->shared copy; with ok == false nothing is read and the destination is zero-filled.
+__device__ __forceinline__ void cp_async16(float4* smem_dst, const float* gsrc, bool ok) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Fire-and-forget vector accumulation into global memory: the addition happens in L2, so no load round trip is
+// exposed to the SM.  Each address is touched by exactly one thread per launch, which keeps the sum order fixed.
+__device__ __forceinline__ void red_add4(float* p, const float4& v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+__device__ __forceinline__ float2 lo2(const float4& v) { return make_float2(v.x, v.y); }
+__device__ __forceinline__ float2 hi2(const float4& v) { return make_float2(v.z, v.w); }
+__device__ __forceinline__ float4 join4(float2 a, float2 b) { return make_float4(a.x, a.y, b.x, b.y); }
+
+// Fluxes of the four triangles anchored at one lane's pixels of a row.  `yd` is the row below.  The pixel quad is
+// processed as two register pairs with packed fp32x2 arithmetic.
 __device__ __forceinline__ void flux_row(const float4& y, const float4& yd, const float4& wx, const float4& wy,
                                          float4& fx, float4& fy) {
     const float yr3 = __shfl_down_sync(kFull, y.x, 1);      // first pixel of the lane to the right
-    tri_flux_fast(y.x, y.y, yd.x, wx.x, wy.x, fx.x, fy.x);
-    tri_flux_fast(y.y, y.z, yd.y, wx.y, wy.y, fx.y, fy.y);
-    tri_flux_fast(y.z, y.w, yd.z, wx.z, wy.z, fx.z, fy.z);
-    tri_flux_fast(y.w, yr3, yd.w, wx.w, wy.w, fx.w, fy.w);
+    const float2 d1a = make_float2(y.x - y.y, y.y - y.z), d1b = make_float2(y.z - y.w, y.w - yr3);
+    const float2 d2a = sub2(lo2(y), lo2(yd)), d2b = sub2(hi2(y), hi2(yd));
+    float2 fxa, fya, fxb, fyb;
+    tri_flux2(d1a, d2a, lo2(wx), lo2(wy), fxa, fya);
+    tri_flux2(d1b, d2b, hi2(wx), hi2(wy), fxb, fyb);
+    fx = join4(fxa, fxb);
+    fy = join4(fya, fyb);
+}
+
+// v - f1 - f2 + f1[left neighbour] + f2[row above]: the divergence both sweeps end with
+__device__ __forceinline__ float4 divergence_row(const float4& v, const float4& f1, const float4& f2v, float f1_left,
+                                                 const float4& f2_above) {
+    float2 a = add2(sub2(sub2(lo2(v), lo2(f1)), lo2(f2v)), lo2(f2_above));
+    float2 b = add2(sub2(sub2(hi2(v), hi2(f1)), hi2(f2v)), hi2(f2_above));
+    a.x += f1_left; a.y += f1.x;
+    b.x += f1.y;    b.y += f1.z;
+    return join4(a, b);
+}
+
+// prox + momentum extrapolation of one row: updates x (primal) and y (momentum variable)
+__device__ __forceinline__ void prox_extrapolate_row(const float4& x05, const float4& b, const float4& c, float t,
+                                                     float4& x, float4& y) {
+    const float2 xa = prox_huber2(lo2(x05), lo2(b), lo2(c));
+    const float2 xb = prox_huber2(hi2(x05), hi2(b), hi2(c));
+    const float2 ya = fma2(f2(t), sub2(xa, lo2(x)), xa);
+    const float2 yb = fma2(f2(t), sub2(xb, hi2(x)), xb);
+    x = join4(xa, xb);
+    y = join4(ya, yb);
 }
 
 struct TileGeom {
@@ -40,18 +87,26 @@ struct TileGeom {
 };
 
 template <int K>
+__device__ __forceinline__ TileGeom make_geom_at(int tx, int ty, int H, int W);
+
+template <int K>
 __device__ __forceinline__ TileGeom make_geom(int H, int W) {
+    return make_geom_at<K>(blockIdx.x, blockIdx.y, H, W);
+}
+
+template <int K>
+__device__ __forceinline__ TileGeom make_geom_at(int tx, int ty, int H, int W) {
     TileGeom g;
     g.lane = threadIdx.x & 31;
     g.warp = threadIdx.x >> 5;
     constexpr int TH = kRegionH - 2 * K;
-    g.gx = blockIdx.x * kTileW - kHaloX + 4 * g.lane;
+    g.gx = tx * kTileW - kHaloX + 4 * g.lane;
     const bool col_ok = g.gx >= 0 && g.gx < W;
     const bool col_int = g.lane >= 1 && g.lane <= 30;
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
         const int lr = g.warp * kRows + r;
-        g.gy[r] = blockIdx.y * TH - K + lr;
+        g.gy[r] = ty * TH - K + lr;
         g.ok[r] = col_ok && g.gy[r] >= 0 && g.gy[r] < H;
         g.store[r] = g.ok[r] && col_int && lr >= K && lr < kRegionH - K;
     }
@@ -82,6 +137,40 @@ __device__ __forceinline__ void load_maps(const P& p, const TileGeom& g, size_t 
     }
 }
 
+// After fused step j only rows j+1 .. 30-j of the region can still influence what the CTA stores, so a warp whose
+// two rows lie outside that band skips the update of step j (it still publishes its rows and its last-row flux,
+// which its neighbours read).  The condition is uniform per warp.
+__device__ __forceinline__ bool rows_needed(int warp, int j) {
+    return (warp * kRows + kRows - 1 >= j + 1) && (warp * kRows <= kRegionH - 2 - j);
+}
+
+// Scales / masks edge weights that were fetched raw (see load_maps).
+__device__ __forceinline__ void finish_maps(const TileGeom& g, int H, int W, float4 (&wx)[kRows], float4 (&wy)[kRows]) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const int last = W - 1 - g.gx;
+        wx[r].x = (last == 0) ? 0.f : kLip * wx[r].x;
+        wx[r].y = (last == 1) ? 0.f : kLip * wx[r].y;
+        wx[r].z = (last == 2) ? 0.f : kLip * wx[r].z;
+        wx[r].w = (last == 3) ? 0.f : kLip * wx[r].w;
+        const float sy = (g.gy[r] == H - 1) ? 0.f : kLip;
+        wy[r].x *= sy; wy[r].y *= sy; wy[r].z *= sy; wy[r].w *= sy;
+    }
+}
+
+struct TileCoord {
+    int tx, ty;
+    size_t n;
+};
+__device__ __forceinline__ TileCoord tile_coord(long long tile, int tiles_x, int tiles_y) {
+    TileCoord t;
+    t.tx = (int)(tile % tiles_x);
+    const long long q = tile / tiles_x;
+    t.ty = (int)(q % tiles_y);
+    t.n = (size_t)(q / tiles_y);
+    return t;
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -95,15 +184,8 @@ tv_fwd_fused_kernel(const __grid_constant__ FwdFusedParams p) {
     const TileGeom g = make_geom<K>(p.H, p.W);
     const size_t n = blockIdx.z;
     const size_t plane = (size_t)p.H * p.W;
-    float4 c[kRows], wx[kRows], wy[kRows], inv[kRows];
+    float4 c[kRows], wx[kRows], wy[kRows];
     load_maps(p, g, n, c, wx, wy);
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-        inv[r].x = rcp_approx(1.0f + c[r].x);
-        inv[r].y = rcp_approx(1.0f + c[r].y);
-        inv[r].z = rcp_approx(1.0f + c[r].z);
-        inv[r].w = rcp_approx(1.0f + c[r].w);
-    }
     for (int ch = 0; ch < p.C; ++ch) {
         float4 y[kRows], x[kRows], b[kRows];
         size_t off[kRows];
@@ -130,29 +212,17 @@ tv_fwd_fused_kernel(const __grid_constant__ FwdFusedParams p) {
             sh_f[g.warp][g.lane] = fyl;
             __syncthreads();
             float4 fyc = (g.warp > 0) ? sh_f[g.warp - 1][g.lane] : zero4();    // vertical flux arriving from above
+            if (!rows_needed(g.warp, j)) continue;           // pure halo rows at this step: only their fluxes were needed
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
                 float4 fx, fy;
                 if (r == kRows - 1) { fx = fxl; fy = fyl; }
                 else flux_row(y[r], y[r + 1], wx[r], wy[r], fx, fy);
                 const float fx_left = __shfl_up_sync(kFull, fx.w, 1);          // last pixel of the lane to the left
-                float4 x05;
-                x05.x = y[r].x - fx.x - fy.x + fx_left + fyc.x;
-                x05.y = y[r].y - fx.y - fy.y + fx.x + fyc.y;
-                x05.z = y[r].z - fx.z - fy.z + fx.y + fyc.z;
-                x05.w = y[r].w - fx.w - fy.w + fx.z + fyc.w;
+                const float4 x05 = divergence_row(y[r], fx, fy, fx_left, fyc);
                 fyc = fy;
                 if (g.store[r]) st4(p.hist[j] + off[r], x05);
-                float4 xn;
-                xn.x = prox_huber_fast(x05.x, b[r].x, c[r].x, inv[r].x);
-                xn.y = prox_huber_fast(x05.y, b[r].y, c[r].y, inv[r].y);
-                xn.z = prox_huber_fast(x05.z, b[r].z, c[r].z, inv[r].z);
-                xn.w = prox_huber_fast(x05.w, b[r].w, c[r].w, inv[r].w);
-                y[r].x = fmaf(t, xn.x - x[r].x, xn.x);
-                y[r].y = fmaf(t, xn.y - x[r].y, xn.y);
-                y[r].z = fmaf(t, xn.z - x[r].z, xn.z);
-                y[r].w = fmaf(t, xn.w - x[r].w, xn.w);
-                x[r] = xn;
+                prox_extrapolate_row(x05, b[r], c[r], t, x[r], y[r]);
             }
         }
 #pragma unroll
@@ -163,6 +233,127 @@ tv_fwd_fused_kernel(const __grid_constant__ FwdFusedParams p) {
             }
         __syncthreads();      // the next channel reuses the exchange rows
     }
+}
+
+// Persistent, software-pipelined variant: one CTA per SM walks over the tiles; while it iterates on one (tile, channel)
+// item, the operands of the next item are already on their way into shared memory (cp.async, one private 16-byte
+// slot per thread, plane and row), so the load phase of every item overlaps the arithmetic of the previous one.
+constexpr int kFwdPipeSmemBytes = (2 * kWarps * 32 + 6 * kRows * kThreads) * (int)sizeof(float4);
+
+template <int K>
+__global__ void __launch_bounds__(kThreads, 1)
+tv_fwd_pipe_kernel(const __grid_constant__ FwdFusedParams p, int tiles_x, int tiles_y) {
+    extern __shared__ float4 smem4[];
+    float4(*sh_y)[32] = reinterpret_cast<float4(*)[32]>(smem4);
+    float4(*sh_f)[32] = sh_y + kWarps;
+    float4* buf_item = smem4 + 2 * kWarps * 32;                 // y, x, b of the next item
+    float4* buf_maps = buf_item + 3 * kRows * kThreads;         // c, wx, wy of the next tile
+    const int tid = threadIdx.x;
+    const long long ntiles = (long long)tiles_x * tiles_y * p.N;
+    const size_t plane = (size_t)p.H * p.W;
+
+    auto issue = [&](long long tile, int ch) {
+        const TileCoord tc = tile_coord(tile, tiles_x, tiles_y);
+        const TileGeom gg = make_geom_at<K>(tc.tx, tc.ty, p.H, p.W);
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const size_t pix = gg.ok[r] ? (size_t)gg.gy[r] * p.W + gg.gx : 0;
+            const size_t o = gg.ok[r] ? (tc.n * p.C + ch) * plane + pix : 0;
+            cp_async16(buf_item + (0 * kRows + r) * kThreads + tid, p.y_in + o, gg.ok[r]);
+            cp_async16(buf_item + (1 * kRows + r) * kThreads + tid, p.x_in + o, gg.ok[r]);
+            cp_async16(buf_item + (2 * kRows + r) * kThreads + tid, p.b + o, gg.ok[r]);
+            if (ch == 0) {
+                const size_t o2 = gg.ok[r] ? tc.n * plane + pix : 0;
+                cp_async16(buf_maps + (0 * kRows + r) * kThreads + tid, p.c + o2, gg.ok[r]);
+                cp_async16(buf_maps + (1 * kRows + r) * kThreads + tid, p.wx + o2, gg.ok[r]);
+                cp_async16(buf_maps + (2 * kRows + r) * kThreads + tid, p.wy + o2, gg.ok[r]);
+            }
+        }
+        cp_async_commit();
+    };
+
+    long long tile = blockIdx.x;
+    if (tile >= ntiles) return;
+    issue(tile, 0);
+    for (; tile < ntiles; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, tiles_x, tiles_y);
+        const TileGeom g = make_geom_at<K>(tc.tx, tc.ty, p.H, p.W);
+        float4 c[kRows], wx[kRows], wy[kRows];
+        for (int ch = 0; ch < p.C; ++ch) {
+            cp_async_wait_all();
+            if (ch == 0) {
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) {
+                    c[r] = buf_maps[(0 * kRows + r) * kThreads + tid];
+                    wx[r] = buf_maps[(1 * kRows + r) * kThreads + tid];
+                    wy[r] = buf_maps[(2 * kRows + r) * kThreads + tid];
+                }
+                finish_maps(g, p.H, p.W, wx, wy);
+            }
+            float4 y[kRows], x[kRows], b[kRows];
+            size_t off[kRows];
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                off[r] = (tc.n * p.C + ch) * plane + (size_t)g.gy[r] * p.W + g.gx;
+                y[r] = buf_item[(0 * kRows + r) * kThreads + tid];
+                x[r] = buf_item[(1 * kRows + r) * kThreads + tid];
+                b[r] = buf_item[(2 * kRows + r) * kThreads + tid];
+            }
+            // the private slots are free again: start fetching the next item
+            if (ch + 1 < p.C) issue(tile, ch + 1);
+            else if (tile + gridDim.x < ntiles) issue(tile + gridDim.x, 0);
+#pragma unroll
+            for (int j = 0; j < K; ++j) {
+                const float t = p.t[j];
+                sh_y[g.warp][g.lane] = y[0];
+                __syncthreads();
+                const float4 ybelow = (g.warp + 1 < kWarps) ? sh_y[g.warp + 1][g.lane] : zero4();
+                if (p.ckpt[j]) {
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r)
+                        if (g.store[r]) st4(p.ckpt[j] + off[r], y[r]);
+                }
+                float4 fxl, fyl;
+                flux_row(y[kRows - 1], ybelow, wx[kRows - 1], wy[kRows - 1], fxl, fyl);
+                sh_f[g.warp][g.lane] = fyl;
+                __syncthreads();
+                float4 fyc = (g.warp > 0) ? sh_f[g.warp - 1][g.lane] : zero4();
+                if (!rows_needed(g.warp, j)) continue;       // pure halo rows at this step: only their fluxes were needed
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) {
+                    float4 fx, fy;
+                    if (r == kRows - 1) { fx = fxl; fy = fyl; }
+                    else flux_row(y[r], y[r + 1], wx[r], wy[r], fx, fy);
+                    const float fx_left = __shfl_up_sync(kFull, fx.w, 1);
+                    const float4 x05 = divergence_row(y[r], fx, fy, fx_left, fyc);
+                    fyc = fy;
+                    if (g.store[r]) st4(p.hist[j] + off[r], x05);
+                    prox_extrapolate_row(x05, b[r], c[r], t, x[r], y[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kRows; ++r)
+                if (g.store[r]) {
+                    st4(p.y_out + off[r], y[r]);
+                    st4(p.x_out + off[r], x[r]);
+                }
+        }
+    }
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+static bool pipeline_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = std::getenv("CNL_TV_NO_PIPELINE"); v = (e && e[0] == '1') ? 0 : 1; }
+    return v == 1;
 }
 
 bool fused_supported(int W, const void* const* ptrs, int nptr) {
@@ -176,6 +367,25 @@ int launch_tv_fwd_fused(const FwdFusedParams& p, int K, cudaStream_t st) {
     if (K < 1 || K > kFuseMax) return fail(CNL_ERR_BAD_OPTION, "fuse factor %d is outside 1..%d", K, kFuseMax);
     const int TH = kRegionH - 2 * K;
     const dim3 grid((p.W + kTileW - 1) / kTileW, (p.H + TH - 1) / TH, p.N);
+    if (pipeline_enabled()) {
+        static bool attr_set[kFuseMax + 1] = {};
+        const long long ntiles = (long long)grid.x * grid.y * grid.z;
+        const unsigned ctas = (unsigned)std::min<long long>(ntiles, sm_count());
+        auto go = [&](auto kern) -> int {
+            if (!attr_set[K]) {
+                CNL_TRY(check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdPipeSmemBytes), "cudaFuncSetAttribute"));
+                attr_set[K] = true;
+            }
+            kern<<<ctas, kThreads, kFwdPipeSmemBytes, st>>>(p, (int)grid.x, (int)grid.y);
+            return after_launch("tv_fwd_pipe_kernel");
+        };
+        switch (K) {
+            case 1: return go(tv_fwd_pipe_kernel<1>);
+            case 2: return go(tv_fwd_pipe_kernel<2>);
+            case 3: return go(tv_fwd_pipe_kernel<3>);
+            default: return go(tv_fwd_pipe_kernel<4>);
+        }
+    }
     switch (K) {
         case 1: tv_fwd_fused_kernel<1><<<grid, kThreads, 0, st>>>(p); break;
         case 2: tv_fwd_fused_kernel<2><<<grid, kThreads, 0, st>>>(p); break;
@@ -196,34 +406,40 @@ __device__ __forceinline__ void adjoint_row(const float4& y, const float4& yd, c
                                             float4& dwx, float4& dwy) {
     const float yr3 = __shfl_down_sync(kFull, y.x, 1);
     const float gr3 = __shfl_down_sync(kFull, g.x, 1);
-    tri_adjoint_fast(y.x, y.y, yd.x, g.x, g.y, gd.x, wx.x, wy.x, p1.x, p2.x, dwx.x, dwy.x);
-    tri_adjoint_fast(y.y, y.z, yd.y, g.y, g.z, gd.y, wx.y, wy.y, p1.y, p2.y, dwx.y, dwy.y);
-    tri_adjoint_fast(y.z, y.w, yd.z, g.z, g.w, gd.z, wx.z, wy.z, p1.z, p2.z, dwx.z, dwy.z);
-    tri_adjoint_fast(y.w, yr3, yd.w, g.w, gr3, gd.w, wx.w, wy.w, p1.w, p2.w, dwx.w, dwy.w);
+    const float2 d1a = make_float2(y.x - y.y, y.y - y.z), d1b = make_float2(y.z - y.w, y.w - yr3);
+    const float2 e1a = make_float2(g.x - g.y, g.y - g.z), e1b = make_float2(g.z - g.w, g.w - gr3);
+    const float2 d2a = sub2(lo2(y), lo2(yd)), d2b = sub2(hi2(y), hi2(yd));
+    const float2 e2a = sub2(lo2(g), lo2(gd)), e2b = sub2(hi2(g), hi2(gd));
+    float2 p1a, p2a, ax, ay, p1b, p2b, bx, by;
+    tri_adjoint2(d1a, d2a, e1a, e2a, lo2(wx), lo2(wy), p1a, p2a, ax, ay);
+    tri_adjoint2(d1b, d2b, e1b, e2b, hi2(wx), hi2(wy), p1b, p2b, bx, by);
+    p1 = join4(p1a, p1b);
+    p2 = join4(p2a, p2b);
+    dwx = join4(ax, bx);
+    dwy = join4(ay, by);
 }
 
-// Momentum reverse + prox Jacobian for one pixel (TVInpaintFista.cu:796-828); returns dL/dx^{g+1/2}.
-__device__ __forceinline__ float reverse_point(float ybar, float& acc, float x05, float b, float c, float t,
-                                               float& dgc, float& dgb, float& xbar_out) {
-    const float xbar = clampf(fmaf(1.0f + t, ybar, acc), -kClipLocal, kClipLocal);
-    acc = -t * ybar;
-    xbar_out = xbar;
-    const float diff = b - x05;
-    const float inv = rcp_approx(1.0f + c);
-    if (1.0f + c >= fabsf(diff)) {
-        // d/dc of (c b + x05)/(1+c) = (b - x)/(1+c) with x the prox output
-        const float xq = fmaf(c, b, x05) * inv;
-        dgc = fmaf(xbar * kLocalGC, (b - xq) * inv, dgc);
-        dgb = fmaf(xbar * kLocalGB, c * inv, dgb);
-        return xbar * inv;
-    }
-    dgc = fmaf(copysignf(kLocalGC, diff), xbar, dgc);
-    return xbar;
+// y_{g+1} of one row rebuilt from two stored pre-prox iterates
+__device__ __forceinline__ float4 rederive_row(const float4& xh, const float4& xhm, const float4& b, const float4& c, float t) {
+    return join4(rederive_y2(lo2(xh), lo2(xhm), lo2(b), lo2(c), t), rederive_y2(hi2(xh), hi2(xhm), hi2(b), hi2(c), t));
+}
+
+// momentum reverse + prox Jacobian of one row; returns dL/dx^{g+1/2}
+__device__ __forceinline__ float4 reverse_row(const float4& ybar, float4& acc, const float4& xh, const float4& b,
+                                              const float4& c, float t, float4& dc, float4& db, float4& xbar) {
+    float2 acca = lo2(acc), accb = hi2(acc), dca = lo2(dc), dcb = hi2(dc), dba = lo2(db), dbb = hi2(db), xa, xb;
+    const float2 ga = reverse_point2(lo2(ybar), acca, lo2(xh), lo2(b), lo2(c), t, dca, dba, xa);
+    const float2 gb = reverse_point2(hi2(ybar), accb, hi2(xh), hi2(b), hi2(c), t, dcb, dbb, xb);
+    acc = join4(acca, accb);
+    dc = join4(dca, dcb);
+    db = join4(dba, dbb);
+    xbar = join4(xa, xb);
+    return join4(ga, gb);
 }
 
 }  // namespace
 
-constexpr int kRevSmemBytes = (4 * kRows * kThreads + 3 * kWarps * 32) * (int)sizeof(float4);
+constexpr int kRevSmemBytes = (5 * kRows * kThreads + 3 * kWarps * 32) * (int)sizeof(float4);
 
 template <int K>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -233,7 +449,8 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
     float4* sh_dwx = sh_dc + kRows * kThreads;
     float4* sh_dwy = sh_dwx + kRows * kThreads;
     float4* sh_db = sh_dwy + kRows * kThreads;             // per channel
-    float4(*sh_y)[32] = reinterpret_cast<float4(*)[32]>(sh_db + kRows * kThreads);    // first rows of y
+    float4* sh_xn = sh_db + kRows * kThreads;              // private landing slots of the prefetched pre-prox iterate
+    float4(*sh_y)[32] = reinterpret_cast<float4(*)[32]>(sh_xn + kRows * kThreads);    // first rows of y
     float4(*sh_g)[32] = sh_y + kWarps;                                               // first rows of g
     float4(*sh_p)[32] = sh_g + kWarps;                                               // last-row vertical adjoint flux
     const TileGeom g = make_geom<K>(p.H, p.W);
@@ -264,23 +481,22 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
         for (int j = 0; j < K; ++j) {
             const float t = p.t[j];
             // prefetch the pre-prox iterate the next fused step needs
-            float4 xnext[kRows];
+            if (j + 2 <= K) {
+                const float* src = p.hist[j + 2 <= K ? j + 2 : K];
 #pragma unroll
-            for (int r = 0; r < kRows; ++r)
-                xnext[r] = (j + 2 <= K) ? ld4(p.hist[j + 2 <= K ? j + 2 : K] + off[r], g.ok[r] && p.hist[j + 2 <= K ? j + 2 : K] != nullptr)
-                                        : zero4();
+                for (int r = 0; r < kRows; ++r) {
+                    const bool okr = g.ok[r] && src != nullptr;
+                    cp_async16(sh_xn + r * kThreads + threadIdx.x, okr ? src + off[r] : p.b, okr);
+                }
+                cp_async_commit();
+            }
             float4 y[kRows];
             if (p.ckpt[j]) {
 #pragma unroll
                 for (int r = 0; r < kRows; ++r) y[r] = ld4(p.ckpt[j] + off[r], g.ok[r]);
             } else {
 #pragma unroll
-                for (int r = 0; r < kRows; ++r) {
-                    y[r].x = rederive_y_fast(xh[r].x, xhm[r].x, b[r].x, c[r].x, rcp_approx(1.0f + c[r].x), t);
-                    y[r].y = rederive_y_fast(xh[r].y, xhm[r].y, b[r].y, c[r].y, rcp_approx(1.0f + c[r].y), t);
-                    y[r].z = rederive_y_fast(xh[r].z, xhm[r].z, b[r].z, c[r].z, rcp_approx(1.0f + c[r].z), t);
-                    y[r].w = rederive_y_fast(xh[r].w, xhm[r].w, b[r].w, c[r].w, rcp_approx(1.0f + c[r].w), t);
-                }
+                for (int r = 0; r < kRows; ++r) y[r] = rederive_row(xh[r], xhm[r], b[r], c[r], t);
             }
             sh_y[g.warp][g.lane] = y[0];
             sh_g[g.warp][g.lane] = gq[0];
@@ -295,6 +511,12 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
             add4(sh_dwy[(kRows - 1) * kThreads + threadIdx.x], dwyl);
             __syncthreads();
             float4 p2c = (g.warp > 0) ? sh_p[g.warp - 1][g.lane] : zero4();
+            if (!rows_needed(g.warp, j)) {                   // pure halo rows at this step: keep the history pipeline moving only
+                cp_async_wait_all();
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) { xh[r] = xhm[r]; xhm[r] = (j + 2 <= K) ? sh_xn[r * kThreads + threadIdx.x] : zero4(); }
+                continue;
+            }
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
                 float4 p1, p2;
@@ -306,27 +528,21 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
                     add4(sh_dwy[r * kThreads + threadIdx.x], ay);
                 }
                 const float p1_left = __shfl_up_sync(kFull, p1.w, 1);
-                float4 ybar;
-                ybar.x = gq[r].x - p1.x - p2.x + p1_left + p2c.x;
-                ybar.y = gq[r].y - p1.y - p2.y + p1.x + p2c.y;
-                ybar.z = gq[r].z - p1.z - p2.z + p1.y + p2c.z;
-                ybar.w = gq[r].w - p1.w - p2.w + p1.z + p2c.w;
+                const float4 ybar = divergence_row(gq[r], p1, p2, p1_left, p2c);
                 p2c = p2;
                 float4 xb;
                 float4 dc = sh_dc[r * kThreads + threadIdx.x];
                 float4 db = sh_db[r * kThreads + threadIdx.x];
-                gq[r].x = reverse_point(ybar.x, acc[r].x, xh[r].x, b[r].x, c[r].x, t, dc.x, db.x, xb.x);
-                gq[r].y = reverse_point(ybar.y, acc[r].y, xh[r].y, b[r].y, c[r].y, t, dc.y, db.y, xb.y);
-                gq[r].z = reverse_point(ybar.z, acc[r].z, xh[r].z, b[r].z, c[r].z, t, dc.z, db.z, xb.z);
-                gq[r].w = reverse_point(ybar.w, acc[r].w, xh[r].w, b[r].w, c[r].w, t, dc.w, db.w, xb.w);
+                gq[r] = reverse_row(ybar, acc[r], xh[r], b[r], c[r], t, dc, db, xb);
                 sh_dc[r * kThreads + threadIdx.x] = dc;
                 sh_db[r * kThreads + threadIdx.x] = db;
                 if (j == K - 1 && p.x1bar != nullptr && g.store[r]) st4(p.x1bar + off[r], xb);
             }
+            cp_async_wait_all();
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
                 xh[r] = xhm[r];
-                xhm[r] = xnext[r];
+                xhm[r] = (j + 2 <= K) ? sh_xn[r * kThreads + threadIdx.x] : zero4();
             }
         }
 #pragma unroll
@@ -334,9 +550,7 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
             if (g.store[r]) {
                 st4(p.g_out + off[r], gq[r]);
                 st4(p.acc_out + off[r], acc[r]);
-                float4 v = *reinterpret_cast<const float4*>(p.g_b + off[r]);
-                add4(v, sh_db[r * kThreads + threadIdx.x]);
-                st4(p.g_b + off[r], v);
+                red_add4(p.g_b + off[r], sh_db[r * kThreads + threadIdx.x]);
             }
         }
     }
@@ -354,17 +568,12 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
         if (last == 2) ax.z = 0.f;
         if (last == 3) ax.w = 0.f;
         if (g.gy[r] == p.H - 1) ay = zero4();
-        float4 v = *reinterpret_cast<const float4*>(p.g_c + o);
-        v.x += dc.x; v.y += dc.y; v.z += dc.z; v.w += dc.w;
-        st4(p.g_c + o, v);
-        v = *reinterpret_cast<const float4*>(p.g_wx + o);
-        v.x += ax.x; v.y += ax.y; v.z += ax.z; v.w += ax.w;
-        st4(p.g_wx + o, v);
-        v = *reinterpret_cast<const float4*>(p.g_wy + o);
-        v.x += ay.x; v.y += ay.y; v.z += ay.z; v.w += ay.w;
-        st4(p.g_wy + o, v);
+        red_add4(p.g_c + o, dc);
+        red_add4(p.g_wx + o, ax);
+        red_add4(p.g_wy + o, ay);
     }
 }
+
 
 int launch_tv_rev_fused(const RevFusedParams& p, int K, cudaStream_t st) {
     if (K < 1 || K > kFuseMax) return fail(CNL_ERR_BAD_OPTION, "fuse factor %d is outside 1..%d", K, kFuseMax);

@@ -185,3 +185,127 @@ __device__ __forceinline__ void tri_adjoint_fast(float yc, float yr, float yd, f
 }
 
 }  // namespace cnl
+
+// ---------------------------------------------------------------------------------------------------------------
+// Packed fp32x2 variants (Blackwell FFMA2 / FADD2 / FMUL2: one issue slot for two pixels).  The temporally blocked
+// kernels are bound by instruction issue, not by FP32 throughput, so pairing the two halves of a lane's pixel quad
+// roughly halves the issue slots of the add / multiply / fma part of the per-pixel math.  Differences whose operands
+// are not register-pair aligned (right neighbours) are formed with scalar subtractions by the caller.
+// ---------------------------------------------------------------------------------------------------------------
+namespace cnl {
+
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ float2 f2(float a) { return make_float2(a, a); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(b, f2(-1.0f), a); }
+__device__ __forceinline__ float2 neg2(float2 a) { return make_float2(-a.x, -a.y); }
+
+// fluxes of two triangles given their differences d1 = y - y_right, d2 = y - y_down
+__device__ __forceinline__ void tri_flux2(float2 d1, float2 d2, float2 wx, float2 wy, float2& fx, float2& fy) {
+    const float2 wd1 = mul2(wx, d1);
+    const float2 wd2 = mul2(wy, d2);
+    const float2 A = fma2(wd1, d1, mul2(wd2, d2));
+    const float2 dr = mul2(f2(kDelta), f2(rsqrt_approx(A.x), rsqrt_approx(A.y)));
+    const float2 s = f2(fminf(1.0f, dr.x), fminf(1.0f, dr.y));
+    fx = mul2(s, wd1);
+    fy = mul2(s, wd2);
+}
+
+__device__ __forceinline__ float2 prox_huber2(float2 x05, float2 b, float2 c) {
+    const float2 opc = add2(c, f2(1.0f));
+    const float2 inv = f2(rcp_approx(opc.x), rcp_approx(opc.y));
+    float2 x = mul2(fma2(c, b, x05), inv);
+    const float2 lo = sub2(x05, c);
+    const float2 hi = add2(x05, c);
+    const float2 bp = add2(b, f2(1.0f));
+    const float2 bm = add2(b, f2(-1.0f));
+    if (lo.x > bp.x) x.x = lo.x;
+    if (lo.y > bp.y) x.y = lo.y;
+    if (hi.x < bm.x) x.x = hi.x;
+    if (hi.y < bm.y) x.y = hi.y;
+    return x;
+}
+
+// y_{k+1} rebuilt from two stored pre-prox iterates for two pixels (see rederive_y_fast)
+__device__ __forceinline__ float2 rederive_y2(float2 x05, float2 x05m, float2 b, float2 c, float t) {
+    const float2 opc = add2(c, f2(1.0f));
+    const float2 inv = f2(rcp_approx(opc.x), rcp_approx(opc.y));
+    const float2 cb = mul2(c, b);
+    const float2 diff = sub2(b, x05);
+    const float2 diff2 = sub2(b, x05m);
+    const float2 xq = mul2(add2(cb, x05), inv);
+    const float2 xqm = mul2(add2(cb, x05m), inv);
+    float2 xk, xkm;
+    {
+        const bool quad = opc.x >= fabsf(diff.x);
+        const float xl = x05.x + copysignf(c.x, diff.x);
+        const float xlm = (c.x <= fabsf(diff2.x)) ? x05m.x + copysignf(c.x, diff2.x) : b.x;
+        xk.x = quad ? xq.x : xl;
+        xkm.x = quad ? xqm.x : xlm;
+    }
+    {
+        const bool quad = opc.y >= fabsf(diff.y);
+        const float xl = x05.y + copysignf(c.y, diff.y);
+        const float xlm = (c.y <= fabsf(diff2.y)) ? x05m.y + copysignf(c.y, diff2.y) : b.y;
+        xk.y = quad ? xq.y : xl;
+        xkm.y = quad ? xqm.y : xlm;
+    }
+    return fma2(f2(t), sub2(xk, xkm), xk);
+}
+
+// adjoint fluxes and edge-weight gradients of two triangles given d1, d2 (y differences) and e1, e2 (g differences)
+__device__ __forceinline__ void tri_adjoint2(float2 d1, float2 d2, float2 e1, float2 e2, float2 wx, float2 wy,
+                                             float2& phi1, float2& phi2, float2& dwx, float2& dwy) {
+    const float2 wd1 = mul2(wx, d1);
+    const float2 wd2 = mul2(wy, d2);
+    const float2 A = fma2(wd1, d1, mul2(wd2, d2));
+    const float2 r = f2(rsqrt_approx(A.x), rsqrt_approx(A.y));
+    const float2 dr = mul2(f2(kDelta), r);
+    const bool bx = dr.x < 1.0f, by = dr.y < 1.0f;
+    const float2 nom = f2(bx ? dr.x : 1.0f, by ? dr.y : 1.0f);
+    const float2 hr = mul2(mul2(f2(0.5f), nom), mul2(r, r));
+    const float2 den = f2(bx ? hr.x : 0.0f, by ? hr.y : 0.0f);
+    const float2 S = fma2(wd1, e1, mul2(wd2, e2));
+    const float2 dS = mul2(den, S);
+    const float2 k2n = mul2(dS, f2(-2.0f));
+    phi1 = mul2(wx, fma2(nom, e1, mul2(k2n, d1)));
+    phi2 = mul2(wy, fma2(nom, e2, mul2(k2n, d2)));
+    const float2 ndS = neg2(dS);
+    dwx = mul2(mul2(f2(-kLocalGX), d1), fma2(nom, e1, mul2(ndS, d1)));
+    dwy = mul2(mul2(f2(-kLocalGX), d2), fma2(nom, e2, mul2(ndS, d2)));
+}
+
+// momentum reverse + prox Jacobian for two pixels (see reverse_point in the kernels' source)
+__device__ __forceinline__ float2 reverse_point2(float2 ybar, float2& acc, float2 x05, float2 b, float2 c, float t,
+                                                 float2& dgc, float2& dgb, float2& xbar_out) {
+    float2 xbar = fma2(f2(1.0f + t), ybar, acc);
+    xbar = f2(clampf(xbar.x, -kClipLocal, kClipLocal), clampf(xbar.y, -kClipLocal, kClipLocal));
+    acc = mul2(f2(-t), ybar);
+    xbar_out = xbar;
+    const float2 opc = add2(c, f2(1.0f));
+    const float2 inv = f2(rcp_approx(opc.x), rcp_approx(opc.y));
+    const float2 diff = sub2(b, x05);
+    const float2 xq = mul2(fma2(c, b, x05), inv);
+    const float2 xi = mul2(xbar, inv);
+    // quadratic zone: d/dc = xbar (b - xq)/(1+c) * kLocalGC, d/db = xbar c/(1+c) * kLocalGB
+    const float2 gc_q = mul2(mul2(xi, f2(kLocalGC)), sub2(b, xq));
+    const float2 gb_q = mul2(mul2(xi, f2(kLocalGB)), c);
+    float2 out;
+    {
+        const bool quad = opc.x >= fabsf(diff.x);
+        dgc.x += quad ? gc_q.x : copysignf(kLocalGC, diff.x) * xbar.x;
+        dgb.x += quad ? gb_q.x : 0.0f;
+        out.x = quad ? xi.x : xbar.x;
+    }
+    {
+        const bool quad = opc.y >= fabsf(diff.y);
+        dgc.y += quad ? gc_q.y : copysignf(kLocalGC, diff.y) * xbar.y;
+        dgb.y += quad ? gb_q.y : 0.0f;
+        out.y = quad ? xi.y : xbar.y;
+    }
+    return out;
+}
+
+}  // namespace cnl
