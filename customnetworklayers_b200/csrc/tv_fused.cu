@@ -162,11 +162,11 @@ struct TileCoord {
     int tx, ty;
     size_t n;
 };
-__device__ __forceinline__ TileCoord tile_coord(long long tile, int tiles_x, int tiles_y) {
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_x, int tiles_y) {
     TileCoord t;
-    t.tx = (int)(tile % tiles_x);
-    const long long q = tile / tiles_x;
-    t.ty = (int)(q % tiles_y);
+    t.tx = tile % tiles_x;
+    const int q = tile / tiles_x;
+    t.ty = q % tiles_y;
     t.n = (size_t)(q / tiles_y);
     return t;
 }
@@ -249,10 +249,10 @@ tv_fwd_pipe_kernel(const __grid_constant__ FwdFusedParams p, int tiles_x, int ti
     float4* buf_item = smem4 + 2 * kWarps * 32;                 // y, x, b of the next item
     float4* buf_maps = buf_item + 3 * kRows * kThreads;         // c, wx, wy of the next tile
     const int tid = threadIdx.x;
-    const long long ntiles = (long long)tiles_x * tiles_y * p.N;
+    const int ntiles = tiles_x * tiles_y * p.N;
     const size_t plane = (size_t)p.H * p.W;
 
-    auto issue = [&](long long tile, int ch) {
+    auto issue = [&](int tile, int ch) {
         const TileCoord tc = tile_coord(tile, tiles_x, tiles_y);
         const TileGeom gg = make_geom_at<K>(tc.tx, tc.ty, p.H, p.W);
 #pragma unroll
@@ -272,7 +272,7 @@ tv_fwd_pipe_kernel(const __grid_constant__ FwdFusedParams p, int tiles_x, int ti
         cp_async_commit();
     };
 
-    long long tile = blockIdx.x;
+    int tile = blockIdx.x;
     if (tile >= ntiles) return;
     issue(tile, 0);
     for (; tile < ntiles; tile += gridDim.x) {
@@ -367,7 +367,7 @@ int launch_tv_fwd_fused(const FwdFusedParams& p, int K, cudaStream_t st) {
     if (K < 1 || K > kFuseMax) return fail(CNL_ERR_BAD_OPTION, "fuse factor %d is outside 1..%d", K, kFuseMax);
     const int TH = kRegionH - 2 * K;
     const dim3 grid((p.W + kTileW - 1) / kTileW, (p.H + TH - 1) / TH, p.N);
-    if (pipeline_enabled()) {
+    if (pipeline_enabled() && (long long)grid.x * grid.y * grid.z < (1ll << 30)) {
         static bool attr_set[kFuseMax + 1] = {};
         const long long ntiles = (long long)grid.x * grid.y * grid.z;
         const unsigned ctas = (unsigned)std::min<long long>(ntiles, sm_count());
