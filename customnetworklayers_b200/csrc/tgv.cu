@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "common.h"
+#include "tgv_vec.cuh"
 #include "tv_math.cuh"
 
 namespace cnl {
@@ -603,6 +604,14 @@ static int ensure_arena(Slot& s, size_t floats) {
     return CNL_OK;
 }
 
+// The register-tiled kernels serve every shape with W % 4 == 0 and 16-byte aligned planes; CNL_TGV_NO_VEC=1 forces
+// the scalar shared-memory kernels.
+static bool vec_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = std::getenv("CNL_TGV_NO_VEC"); v = (e && e[0] == '1') ? 0 : 1; }
+    return v == 1;
+}
+
 static int lipschitz(const float* dx, const float* dy, float* Lbuf, int* lip_bits, int n, int h, int w, cudaStream_t st) {
     tgv_lipschitz_init_kernel<<<(n + 127) / 128, 128, 0, st>>>(lip_bits, n);
     CNL_TRY(after_launch("tgv_lipschitz_init_kernel"));
@@ -636,14 +645,25 @@ static int forward_impl(const float* dx, const float* dy, const float* c, const 
     CNL_TRY(check_cuda(cudaMemcpyAsync(out, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->x"));
     CNL_TRY(check_cuda(cudaMemcpyAsync(y0, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->y"));
     const dim3 grid((w + TW - 1) / TW, (h + TH - 1) / TH, n);
+    const void* planes[] = {dx, dy, c, b, out, s.arena};
+    const bool vec = vec_enabled() && tgv_vec_supported(w, planes, 6);
     size_t next = 0;
     for (int g = 0; g < its_eff; ++g) {
         float* yin = (g & 1) ? y1 : y0;
         float* yout = (g & 1) ? y0 : y1;
+        float* ck = nullptr;
         if (next < s.sched.size() && s.sched[next] == g) {
-            CNL_TRY(check_cuda(cudaMemcpyAsync(s.arena + l.ckpt + next * l.vol, yin, vol_bytes, cudaMemcpyDeviceToDevice, st), "checkpoint y"));
+            ck = s.arena + l.ckpt + next * l.vol;
             ++next;
         }
+        if (vec) {
+            FwdVecParams q{};
+            q.y_in = yin; q.y_out = yout; q.x = out; q.hist = s.arena + l.hist + (size_t)g * l.vol; q.ckpt = ck;
+            q.b = b; q.c = c; q.dx = dx; q.dy = dy; q.L = Lbuf; q.N = n; q.C = ch; q.H = h; q.W = w; q.t = s.steps[g];
+            CNL_TRY(launch_tgv_fwd_vec(q, st));
+            continue;
+        }
+        if (ck) CNL_TRY(check_cuda(cudaMemcpyAsync(ck, yin, vol_bytes, cudaMemcpyDeviceToDevice, st), "checkpoint y"));
         tgv_fwd_kernel<<<grid, NT, 0, st>>>(yin, yout, out, b, c, dx, dy, Lbuf, s.arena + l.hist + (size_t)g * l.vol, ch, h, w, s.steps[g]);
         CNL_TRY(after_launch("tgv_fwd_kernel"));
     }
@@ -700,6 +720,8 @@ static int backward_impl(const float* dx, const float* dy, const float* c, const
     const float* hist = s.arena + l.hist;
     CNL_TRY(check_cuda(cudaMemsetAsync(acc, 0, vol * sizeof(float), st), "zero acc"));
     const dim3 grid((w + TW - 1) / TW, (h + TH - 1) / TH, n);
+    const void* planes[] = {dx, dy, c, b, g_dx, g_dy, g_c, g_b, g_init, s.arena};
+    const bool vec = vec_enabled() && tgv_vec_supported(w, planes, 10);
     static bool attr = false;
     if (!attr) {
         CNL_TRY(check_cuda(cudaFuncSetAttribute(tgv_rev_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -716,6 +738,15 @@ static int backward_impl(const float* dx, const float* dy, const float* c, const
         for (size_t i = 0; i < s.sched.size(); ++i) if (s.sched[i] == g) ck = s.arena + l.ckpt + i * l.vol;
         float* gout = (g & 1) ? gb : ga;
         const float* gin = (g & 1) ? ga : gb;
+        if (vec) {
+            RevVecParams q{};
+            q.hist_g = hist + (size_t)g * l.vol; q.hist_gm1 = g > 0 ? hist + (size_t)(g - 1) * l.vol : nullptr; q.ckpt = ck;
+            q.g_in = gin; q.g_out = gout; q.acc = acc; q.b = b; q.c = c; q.dx = dx; q.dy = dy; q.L = Lbuf;
+            q.g_c = g_c; q.g_b = g_b; q.g_dx = g_dx; q.g_dy = g_dy; q.x1bar = g == 0 ? g_init : nullptr;
+            q.N = n; q.C = ch; q.H = h; q.W = w; q.t = s.steps[g]; q.typo = ck ? 0 : 1;
+            CNL_TRY(launch_tgv_rev_vec(q, st));
+            continue;
+        }
         tgv_rev_kernel<<<grid, NT, kRevSmemFloats * sizeof(float), st>>>(
             hist + (size_t)g * l.vol, g > 0 ? hist + (size_t)(g - 1) * l.vol : nullptr, ck, gin, gout, acc, b, c, dx, dy, Lbuf,
             g_c, g_b, g_dx, g_dy, g == 0 ? g_init : nullptr, ch, h, w, s.steps[g], ck ? 0 : 1);

@@ -1,0 +1,370 @@
+// Register-tiled TGV-FISTA iteration kernels for sm_100a (geometry: see tgv_vec.cuh; math: the divergence form of
+// cudaTGV/cudaCode/TGVInpaintFistaBetas.cu:1546-1776 forward and :224-644 / :1061-1473 reverse, as in tgv.cu).
+#include "tgv_vec.cuh"
+
+#include "common.h"
+#include "tv_math.cuh"
+
+namespace cnl {
+namespace tgv {
+
+namespace {
+
+constexpr int kNT = kTgvWarps * 32;
+constexpr unsigned kFull = 0xffffffffu;
+constexpr float kDeltaU = 0.2f, kDeltaV1 = 0.2f, kDeltaV2 = 0.2f;     // __HDelta2__, __HDeltaY1__, __HDeltaY2__ (:58-60)
+constexpr float kClip = 2000.0f;                                      // clipLocalGrad (:78)
+
+__device__ __forceinline__ float4 ld4(const float* p, bool ok) {
+    return ok ? __ldg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+// plain (coherent) load for planes this launch also writes
+__device__ __forceinline__ float4 ld4c(const float* p, bool ok) {
+    return ok ? *reinterpret_cast<const float4*>(p) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+__device__ __forceinline__ void st4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ void red_add4(float* p, const float4& v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void unpack(const float4& v, float (&a)[4]) { a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
+__device__ __forceinline__ float4 pack(const float (&a)[4]) { return make_float4(a[0], a[1], a[2], a[3]); }
+
+struct Geom {
+    int lane, warp, gx, gy;
+    bool ok;          // the lane's vector lies inside the image
+    bool okb;         // ... and so does the vector one row below
+    bool store;       // inside the interior this CTA writes
+    bool my;          // a vertical edge leaves this row
+    bool mx[4];       // a horizontal edge leaves pixel k
+    size_t pix;       // gy * W + gx (0 when !ok)
+};
+
+__device__ __forceinline__ Geom make_geom(int H, int W) {
+    Geom g;
+    g.lane = threadIdx.x & 31;
+    g.warp = threadIdx.x >> 5;
+    g.gx = blockIdx.x * kTgvTileW - 4 + 4 * g.lane;
+    g.gy = blockIdx.y * kTgvTileH - 1 + g.warp;
+    const bool col = g.gx >= 0 && g.gx < W;
+    g.ok = col && g.gy >= 0 && g.gy < H;
+    g.okb = col && g.gy + 1 >= 0 && g.gy + 1 < H;
+    g.store = g.ok && g.warp >= 1 && g.lane >= 1 && g.lane <= 30;
+    g.my = g.ok && g.gy < H - 1;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) g.mx[k] = g.ok && g.gx + k < W - 1;
+    g.pix = g.ok ? (size_t)g.gy * W + g.gx : 0;
+    return g;
+}
+
+// Edge weights of the lane's four triangles, scaled by 1/Lipschitz and zero where no edge leaves the pixel.
+struct Weights {
+    float wx[4], wy[4], b0[4], b1[4];
+};
+__device__ __forceinline__ Weights load_weights(const float* dx, const float* dy, size_t n, size_t plane, const Geom& g, float L) {
+    Weights w;
+    float a[4];
+    unpack(ld4(dx + (n * 2 + 0) * plane + g.pix, g.ok), a);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w.wx[k] = g.mx[k] ? __fmul_rn(L, a[k]) : 0.f;
+    unpack(ld4(dy + (n * 2 + 0) * plane + g.pix, g.ok), a);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w.wy[k] = g.my ? __fmul_rn(L, a[k]) : 0.f;
+    unpack(ld4(dx + (n * 2 + 1) * plane + g.pix, g.ok), a);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w.b0[k] = g.ok ? __fmul_rn(L, a[k]) : 0.f;
+    unpack(ld4(dy + (n * 2 + 1) * plane + g.pix, g.ok), a);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w.b1[k] = g.ok ? __fmul_rn(L, a[k]) : 0.f;
+    return w;
+}
+
+// Differences and Huber factors of the triangle anchored at one pixel (c = centre, r = right, d = below).
+struct TriQ {
+    float z1, z2, Hu, r_u;
+    float a1[2], a2[2], H[2], r[2];
+};
+__device__ __forceinline__ TriQ tri_quantities(float uc, float ur, float ud, float v1c, float v1r, float v1d, float v2c,
+                                               float v2r, float v2d, float wx, float wy, float b0, float b1, bool mx, bool my) {
+    TriQ t;
+    t.z1 = mx ? (ur - uc - v1c) : 0.f;
+    t.z2 = my ? (ud - uc - v2c) : 0.f;
+    t.r_u = rsqrtf(wy * t.z2 * t.z2 + wx * t.z1 * t.z1);
+    t.Hu = fminf(1.f, t.r_u * kDeltaU);
+    t.a1[0] = mx ? (v1r - v1c) : 0.f;
+    t.a2[0] = my ? (v1d - v1c) : 0.f;
+    t.r[0] = rsqrtf(b0 * (t.a1[0] * t.a1[0] + t.a2[0] * t.a2[0]));
+    t.H[0] = fminf(1.f, t.r[0] * kDeltaV1);
+    t.a1[1] = mx ? (v2r - v2c) : 0.f;
+    t.a2[1] = my ? (v2d - v2c) : 0.f;
+    t.r[1] = rsqrtf(b1 * (t.a1[1] * t.a1[1] + t.a2[1] * t.a2[1]));
+    t.H[1] = fminf(1.f, t.r[1] * kDeltaV2);
+    return t;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------
+// forward iteration
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kNT, 2)
+tgv_fwd_vec_kernel(const __grid_constant__ FwdVecParams p) {
+    __shared__ float4 sh[2][3][kTgvWarps][32];        // per channel parity: Fy, G1y, G2y of each warp's row
+    const Geom g = make_geom(p.H, p.W);
+    const size_t plane = (size_t)p.H * p.W;
+    const size_t n = blockIdx.z;
+    const float L = p.L[n];
+    const Weights w = load_weights(p.dx, p.dy, n, plane, g, L);
+    float cf[4];
+    unpack(ld4(p.c + n * plane + g.pix, g.store), cf);
+    const size_t cstride = (size_t)p.C * plane;         // distance between the u, v1, v2 planes of a channel
+    for (int ch = 0; ch < p.C; ++ch) {
+        const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
+        const float4 yu4 = ld4(p.y_in + o, g.ok), y14 = ld4(p.y_in + o + cstride, g.ok), y24 = ld4(p.y_in + o + 2 * cstride, g.ok);
+        const float4 du4 = ld4(p.y_in + o + p.W, g.okb), d14 = ld4(p.y_in + o + cstride + p.W, g.okb),
+                     d24 = ld4(p.y_in + o + 2 * cstride + p.W, g.okb);
+        // pointwise operands are only needed where the CTA stores
+        const float4 xu4 = ld4c(p.x + o, g.store), x14 = ld4c(p.x + o + cstride, g.store), x24 = ld4c(p.x + o + 2 * cstride, g.store);
+        const float4 b4 = ld4(p.b + (n * p.C + ch) * plane + g.pix, g.store);
+        if (p.ckpt && g.store) {
+            st4(p.ckpt + o, yu4); st4(p.ckpt + o + cstride, y14); st4(p.ckpt + o + 2 * cstride, y24);
+        }
+        float yu[5], y1[5], y2[5], du[4], d1[4], d2[4];
+        {
+            float a[4];
+            unpack(yu4, a); for (int k = 0; k < 4; ++k) yu[k] = a[k];
+            unpack(y14, a); for (int k = 0; k < 4; ++k) y1[k] = a[k];
+            unpack(y24, a); for (int k = 0; k < 4; ++k) y2[k] = a[k];
+        }
+        unpack(du4, du); unpack(d14, d1); unpack(d24, d2);
+        yu[4] = __shfl_down_sync(kFull, yu4.x, 1);
+        y1[4] = __shfl_down_sync(kFull, y14.x, 1);
+        y2[4] = __shfl_down_sync(kFull, y24.x, 1);
+        float fx[4], fy[4], g1x[4], g1y[4], g2x[4], g2y[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const TriQ t = tri_quantities(yu[k], yu[k + 1], du[k], y1[k], y1[k + 1], d1[k], y2[k], y2[k + 1], d2[k],
+                                          w.wx[k], w.wy[k], w.b0[k], w.b1[k], g.mx[k], g.my);
+            fx[k] = w.wx[k] * t.z1 * t.Hu;
+            fy[k] = w.wy[k] * t.z2 * t.Hu;
+            g1x[k] = w.b0[k] * t.a1[0] * t.H[0];
+            g1y[k] = w.b0[k] * t.a2[0] * t.H[0];
+            g2x[k] = w.b1[k] * t.a1[1] * t.H[1];
+            g2y[k] = w.b1[k] * t.a2[1] * t.H[1];
+        }
+        float4(*ex)[kTgvWarps][32] = sh[ch & 1];
+        ex[0][g.warp][g.lane] = pack(fy);
+        ex[1][g.warp][g.lane] = pack(g1y);
+        ex[2][g.warp][g.lane] = pack(g2y);
+        __syncthreads();
+        float fya[4], g1ya[4], g2ya[4];                  // vertical fluxes of the row above
+        unpack(g.warp > 0 ? ex[0][g.warp - 1][g.lane] : zero4(), fya);
+        unpack(g.warp > 0 ? ex[1][g.warp - 1][g.lane] : zero4(), g1ya);
+        unpack(g.warp > 0 ? ex[2][g.warp - 1][g.lane] : zero4(), g2ya);
+        const float fxl = __shfl_up_sync(kFull, fx[3], 1);      // horizontal fluxes of the pixel to the left
+        const float g1xl = __shfl_up_sync(kFull, g1x[3], 1);
+        const float g2xl = __shfl_up_sync(kFull, g2x[3], 1);
+        float xu[4], x1[4], x2[4], bq[4];
+        unpack(xu4, xu); unpack(x14, x1); unpack(x24, x2); unpack(b4, bq);
+        float hu[4], h1[4], h2[4], nu[4], ou[4], o1[4], o2[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float fx_l = k == 0 ? fxl : fx[k - 1];
+            const float g1x_l = k == 0 ? g1xl : g1x[k - 1];
+            const float g2x_l = k == 0 ? g2xl : g2x[k - 1];
+            hu[k] = yu[k] + fx[k] + fy[k] - fx_l - fya[k];
+            h1[k] = y1[k] + g1x[k] + g1y[k] - g1x_l - g1ya[k] + fx[k];
+            h2[k] = y2[k] + g2x[k] + g2y[k] - g2x_l - g2ya[k] + fy[k];
+            nu[k] = prox_huber(hu[k], bq[k], cf[k]);
+            ou[k] = nu[k] + p.t * (nu[k] - xu[k]);
+            o1[k] = h1[k] + p.t * (h1[k] - x1[k]);
+            o2[k] = h2[k] + p.t * (h2[k] - x2[k]);
+        }
+        if (g.store) {
+            st4(p.hist + o, pack(hu)); st4(p.hist + o + cstride, pack(h1)); st4(p.hist + o + 2 * cstride, pack(h2));
+            st4(p.x + o, pack(nu));    st4(p.x + o + cstride, pack(h1));    st4(p.x + o + 2 * cstride, pack(h2));
+            st4(p.y_out + o, pack(ou)); st4(p.y_out + o + cstride, pack(o1)); st4(p.y_out + o + 2 * cstride, pack(o2));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// reverse iteration
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+// y (momentum variable) and incoming adjoint of one row of the lane's pixels.  u of y is rebuilt from the stored
+// pre-prox iterates of iterations g and g-1 unless a checkpoint supplies all three planes (:1478-1541).
+struct RowState {
+    float4 yu, y1, y2, gu, g1, g2;
+};
+__device__ __forceinline__ RowState load_row(const RevVecParams& p, size_t o, size_t ob, size_t oc, size_t cstride, bool ok) {
+    RowState r;
+    const float* ysrc = p.ckpt ? p.ckpt : p.hist_g;
+    r.yu = ld4(ysrc + o, ok);
+    r.y1 = ld4(ysrc + o + cstride, ok);
+    r.y2 = ld4(ysrc + o + 2 * cstride, ok);
+    r.gu = ld4(p.g_in + o, ok);
+    r.g1 = ld4(p.g_in + o + cstride, ok);
+    r.g2 = ld4(p.g_in + o + 2 * cstride, ok);
+    if (!p.ckpt) {
+        const float4 hm = ld4(p.hist_gm1 + o, ok && p.hist_gm1 != nullptr);
+        const float4 b = ld4(p.b + ob, ok);
+        const float4 c = ld4(p.c + oc, ok);
+        if (ok) {
+            r.yu.x = rederive_y(r.yu.x, hm.x, b.x, c.x, p.t);
+            r.yu.y = rederive_y(r.yu.y, hm.y, b.y, c.y, p.t);
+            r.yu.z = rederive_y(r.yu.z, hm.z, b.z, c.z, p.t);
+            r.yu.w = rederive_y(r.yu.w, hm.w, b.w, c.w, p.t);
+        }
+    }
+    return r;
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kNT, 2)
+tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
+    __shared__ float4 sh_row[6][kTgvWarps][32];       // y (u, v1, v2) and g (u, v1, v2) of each warp's row
+    __shared__ float4 sh_flux[3][kTgvWarps][32];      // psi2, chi1y and the down-going chi2y of each warp's row
+    const Geom g = make_geom(p.H, p.W);
+    const size_t plane = (size_t)p.H * p.W;
+    const size_t n = blockIdx.z;
+    const float L = p.L[n];
+    const Weights w = load_weights(p.dx, p.dy, n, plane, g, L);
+    const size_t cstride = (size_t)p.C * plane;
+    const size_t oc = n * plane + g.pix;
+    for (int ch = 0; ch < p.C; ++ch) {
+        const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
+        const size_t ob = (n * p.C + ch) * plane + g.pix;
+        const RowState own = load_row(p, o, ob, oc, cstride, g.ok);
+        // pointwise operands of the lane's own pixels (only where the CTA stores)
+        const float4 hu_raw = ld4(p.hist_g + o, g.store);                     // x^{g+1/2}, primary plane
+        const float4 b4 = ld4(p.b + ob, g.store);
+        const float4 c4 = ld4(p.c + oc, g.store);
+        const float4 au4 = ld4c(p.acc + o, g.store), a14 = ld4c(p.acc + o + cstride, g.store), a24 = ld4c(p.acc + o + 2 * cstride, g.store);
+        sh_row[0][g.warp][g.lane] = own.yu; sh_row[1][g.warp][g.lane] = own.y1; sh_row[2][g.warp][g.lane] = own.y2;
+        sh_row[3][g.warp][g.lane] = own.gu; sh_row[4][g.warp][g.lane] = own.g1; sh_row[5][g.warp][g.lane] = own.g2;
+        RowState below;
+        if (g.warp == kTgvWarps - 1) below = load_row(p, o + p.W, ob + p.W, oc + p.W, cstride, g.okb);   // row under the region
+        __syncthreads();
+        if (g.warp < kTgvWarps - 1) {
+            below.yu = sh_row[0][g.warp + 1][g.lane]; below.y1 = sh_row[1][g.warp + 1][g.lane]; below.y2 = sh_row[2][g.warp + 1][g.lane];
+            below.gu = sh_row[3][g.warp + 1][g.lane]; below.g1 = sh_row[4][g.warp + 1][g.lane]; below.g2 = sh_row[5][g.warp + 1][g.lane];
+        }
+        float yu[5], y1[5], y2[5], gu[5], g1[5], g2[5], du[4], d1[4], d2[4], eu[4], e1[4], e2[4];
+        {
+            float a[4];
+            unpack(own.yu, a); for (int k = 0; k < 4; ++k) yu[k] = a[k];
+            unpack(own.y1, a); for (int k = 0; k < 4; ++k) y1[k] = a[k];
+            unpack(own.y2, a); for (int k = 0; k < 4; ++k) y2[k] = a[k];
+            unpack(own.gu, a); for (int k = 0; k < 4; ++k) gu[k] = a[k];
+            unpack(own.g1, a); for (int k = 0; k < 4; ++k) g1[k] = a[k];
+            unpack(own.g2, a); for (int k = 0; k < 4; ++k) g2[k] = a[k];
+        }
+        unpack(below.yu, du); unpack(below.y1, d1); unpack(below.y2, d2);
+        unpack(below.gu, eu); unpack(below.g1, e1); unpack(below.g2, e2);
+        yu[4] = __shfl_down_sync(kFull, own.yu.x, 1); y1[4] = __shfl_down_sync(kFull, own.y1.x, 1); y2[4] = __shfl_down_sync(kFull, own.y2.x, 1);
+        gu[4] = __shfl_down_sync(kFull, own.gu.x, 1); g1[4] = __shfl_down_sync(kFull, own.g1.x, 1); g2[4] = __shfl_down_sync(kFull, own.g2.x, 1);
+        // adjoint fluxes of the lane's four triangles and their edge-weight gradients
+        float P1[4], P2[4], C1x[4], C1y[4], C2x[4], C2y[4], C2d[4], gw0[4], gw1[4], gw2[4], gw3[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const TriQ tr = tri_quantities(yu[k], yu[k + 1], du[k], y1[k], y1[k + 1], d1[k], y2[k], y2[k + 1], d2[k],
+                                           w.wx[k], w.wy[k], w.b0[k], w.b1[k], g.mx[k], g.my);
+            const float Ex = gu[k] - gu[k + 1] + g1[k];
+            const float Ey = gu[k] - eu[k] + g2[k];
+            const float a1 = tr.z1 * w.wx[k], a2 = tr.z2 * w.wy[k];
+            const float S = a1 * Ex + a2 * Ey;
+            const float dW = tr.Hu < 1.f ? tr.Hu * tr.r_u * tr.r_u : 0.f;
+            P1[k] = w.wx[k] * tr.Hu * Ex - dW * a1 * S;
+            P2[k] = w.wy[k] * tr.Hu * Ey - dW * a2 * S;
+            gw0[k] = kLocalGX * (Ex * tr.z1 * tr.Hu - 0.5f * tr.z1 * tr.z1 * dW * S);
+            gw2[k] = kLocalGX * (Ey * tr.z2 * tr.Hu - 0.5f * tr.z2 * tr.z2 * dW * S);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float gc = j == 0 ? g1[k] : g2[k], gr = j == 0 ? g1[k + 1] : g2[k + 1], gd = j == 0 ? e1[k] : e2[k];
+                const float E1 = g.mx[k] ? gc - gr : 0.f;
+                const float E2 = g.my ? gc - gd : 0.f;
+                const float b1 = tr.a1[j], b2 = tr.a2[j], beta = j == 0 ? w.b0[k] : w.b1[k], Hj = tr.H[j];
+                const float Sj = b1 * E1 + b2 * E2;
+                const bool act = Hj < 1.f;
+                const float dWj = act ? Hj * tr.r[j] * tr.r[j] : 0.f;
+                const float chx = beta * (Hj * E1 - dWj * beta * b1 * Sj);
+                const float chy = beta * (Hj * E2 - dWj * beta * b2 * Sj);
+                const float gbeta = kLocalGX * (Sj * Hj - 0.5f * (b1 * b1 + b2 * b2) * dWj * beta * Sj);
+                if (j == 0) { C1x[k] = chx; C1y[k] = chy; gw1[k] = gbeta; }
+                else {
+                    C2x[k] = chx; C2y[k] = chy; gw3[k] = gbeta;
+                    float down = chy;
+                    if (p.typo && act) down = beta * (Hj * E2 - (Hj * beta * (b1 * b1 + b2 * b2)) * beta * b2 * Sj);
+                    C2d[k] = down;
+                }
+            }
+        }
+        sh_flux[0][g.warp][g.lane] = pack(P2);
+        sh_flux[1][g.warp][g.lane] = pack(C1y);
+        sh_flux[2][g.warp][g.lane] = pack(C2d);
+        if (g.store) {      // every triangle's weight gradient is accumulated by the pixel that anchors it
+            red_add4(p.g_dx + (n * 2 + 0) * plane + g.pix, pack(gw0));
+            red_add4(p.g_dx + (n * 2 + 1) * plane + g.pix, pack(gw1));
+            red_add4(p.g_dy + (n * 2 + 0) * plane + g.pix, pack(gw2));
+            red_add4(p.g_dy + (n * 2 + 1) * plane + g.pix, pack(gw3));
+        }
+        __syncthreads();
+        float P2a[4], C1ya[4], C2da[4];
+        unpack(g.warp > 0 ? sh_flux[0][g.warp - 1][g.lane] : zero4(), P2a);
+        unpack(g.warp > 0 ? sh_flux[1][g.warp - 1][g.lane] : zero4(), C1ya);
+        unpack(g.warp > 0 ? sh_flux[2][g.warp - 1][g.lane] : zero4(), C2da);
+        const float P1l = __shfl_up_sync(kFull, P1[3], 1);
+        const float C1xl = __shfl_up_sync(kFull, C1x[3], 1);
+        const float C2xl = __shfl_up_sync(kFull, C2x[3], 1);
+        float au[4], a1v[4], a2v[4], hu[4], bq[4], cq[4];
+        unpack(au4, au); unpack(a14, a1v); unpack(a24, a2v); unpack(hu_raw, hu); unpack(b4, bq); unpack(c4, cq);
+        float xb0[4], xb1[4], xb2[4], na0[4], na1[4], na2[4], go[4], dgc[4], dgb[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float P1_l = k == 0 ? P1l : P1[k - 1];
+            const float C1x_l = k == 0 ? C1xl : C1x[k - 1];
+            const float C2x_l = k == 0 ? C2xl : C2x[k - 1];
+            const float yb0 = gu[k] - P1[k] - P2[k] + P1_l + P2a[k];
+            const float yb1 = g1[k] - P1[k] - C1x[k] - C1y[k] + C1x_l + C1ya[k];
+            const float yb2 = g2[k] - P2[k] - C2x[k] - C2y[k] + C2x_l + C2da[k];
+            xb0[k] = clampf(au[k] + (1.0f + p.t) * yb0, -kClip, kClip);
+            xb1[k] = clampf(a1v[k] + (1.0f + p.t) * yb1, -kClip, kClip);
+            xb2[k] = clampf(a2v[k] + (1.0f + p.t) * yb2, -kClip, kClip);
+            na0[k] = -p.t * yb0; na1[k] = -p.t * yb1; na2[k] = -p.t * yb2;
+            dgc[k] = 0.f; dgb[k] = 0.f;
+            go[k] = prox_reverse(xb0[k], hu[k], bq[k], cq[k], dgc[k], dgb[k]);
+        }
+        if (g.store) {
+            st4(p.acc + o, pack(na0)); st4(p.acc + o + cstride, pack(na1)); st4(p.acc + o + 2 * cstride, pack(na2));
+            if (p.x1bar) { st4(p.x1bar + o, pack(xb0)); st4(p.x1bar + o + cstride, pack(xb1)); st4(p.x1bar + o + 2 * cstride, pack(xb2)); }
+            st4(p.g_out + o, pack(go)); st4(p.g_out + o + cstride, pack(xb1)); st4(p.g_out + o + 2 * cstride, pack(xb2));
+            red_add4(p.g_b + ob, pack(dgb));
+            red_add4(p.g_c + oc, pack(dgc));
+        }
+    }
+}
+
+int launch_tgv_rev_vec(const RevVecParams& p, cudaStream_t st) {
+    const dim3 grid((p.W + kTgvTileW - 1) / kTgvTileW, (p.H + kTgvTileH - 1) / kTgvTileH, p.N);
+    tgv_rev_vec_kernel<<<grid, kNT, 0, st>>>(p);
+    return after_launch("tgv_rev_vec_kernel");
+}
+
+bool tgv_vec_supported(int W, const void* const* ptrs, int nptr) {
+    if (W % 4 != 0) return false;
+    for (int i = 0; i < nptr; ++i)
+        if ((reinterpret_cast<size_t>(ptrs[i]) & 15) != 0) return false;
+    return true;
+}
+
+int launch_tgv_fwd_vec(const FwdVecParams& p, cudaStream_t st) {
+    const dim3 grid((p.W + kTgvTileW - 1) / kTgvTileW, (p.H + kTgvTileH - 1) / kTgvTileH, p.N);
+    tgv_fwd_vec_kernel<<<grid, kNT, 0, st>>>(p);
+    return after_launch("tgv_fwd_vec_kernel");
+}
+
+}  // namespace tgv
+}  // namespace cnl
