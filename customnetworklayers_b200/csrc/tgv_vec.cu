@@ -89,15 +89,15 @@ __device__ __forceinline__ TriQ tri_quantities(float uc, float ur, float ud, flo
     TriQ t;
     t.z1 = mx ? (ur - uc - v1c) : 0.f;
     t.z2 = my ? (ud - uc - v2c) : 0.f;
-    t.r_u = rsqrtf(wy * t.z2 * t.z2 + wx * t.z1 * t.z1);
+    t.r_u = rsqrt_approx(wy * t.z2 * t.z2 + wx * t.z1 * t.z1);
     t.Hu = fminf(1.f, t.r_u * kDeltaU);
     t.a1[0] = mx ? (v1r - v1c) : 0.f;
     t.a2[0] = my ? (v1d - v1c) : 0.f;
-    t.r[0] = rsqrtf(b0 * (t.a1[0] * t.a1[0] + t.a2[0] * t.a2[0]));
+    t.r[0] = rsqrt_approx(b0 * (t.a1[0] * t.a1[0] + t.a2[0] * t.a2[0]));
     t.H[0] = fminf(1.f, t.r[0] * kDeltaV1);
     t.a1[1] = mx ? (v2r - v2c) : 0.f;
     t.a2[1] = my ? (v2d - v2c) : 0.f;
-    t.r[1] = rsqrtf(b1 * (t.a1[1] * t.a1[1] + t.a2[1] * t.a2[1]));
+    t.r[1] = rsqrt_approx(b1 * (t.a1[1] * t.a1[1] + t.a2[1] * t.a2[1]));
     t.H[1] = fminf(1.f, t.r[1] * kDeltaV2);
     return t;
 }
@@ -175,7 +175,7 @@ tgv_fwd_vec_kernel(const __grid_constant__ FwdVecParams p) {
             hu[k] = yu[k] + fx[k] + fy[k] - fx_l - fya[k];
             h1[k] = y1[k] + g1x[k] + g1y[k] - g1x_l - g1ya[k] + fx[k];
             h2[k] = y2[k] + g2x[k] + g2y[k] - g2x_l - g2ya[k] + fy[k];
-            nu[k] = prox_huber(hu[k], bq[k], cf[k]);
+            nu[k] = prox_huber_fast(hu[k], bq[k], cf[k], rcp_approx(1.0f + cf[k]));
             ou[k] = nu[k] + p.t * (nu[k] - xu[k]);
             o1[k] = h1[k] + p.t * (h1[k] - x1[k]);
             o2[k] = h2[k] + p.t * (h2[k] - x2[k]);
@@ -212,10 +212,10 @@ __device__ __forceinline__ RowState load_row(const RevVecParams& p, size_t o, si
         const float4 b = ld4(p.b + ob, ok);
         const float4 c = ld4(p.c + oc, ok);
         if (ok) {
-            r.yu.x = rederive_y(r.yu.x, hm.x, b.x, c.x, p.t);
-            r.yu.y = rederive_y(r.yu.y, hm.y, b.y, c.y, p.t);
-            r.yu.z = rederive_y(r.yu.z, hm.z, b.z, c.z, p.t);
-            r.yu.w = rederive_y(r.yu.w, hm.w, b.w, c.w, p.t);
+            r.yu.x = rederive_y_fast(r.yu.x, hm.x, b.x, c.x, rcp_approx(1.0f + c.x), p.t);
+            r.yu.y = rederive_y_fast(r.yu.y, hm.y, b.y, c.y, rcp_approx(1.0f + c.y), p.t);
+            r.yu.z = rederive_y_fast(r.yu.z, hm.z, b.z, c.z, rcp_approx(1.0f + c.z), p.t);
+            r.yu.w = rederive_y_fast(r.yu.w, hm.w, b.w, c.w, rcp_approx(1.0f + c.w), p.t);
         }
     }
     return r;
@@ -335,7 +335,7 @@ tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
             xb2[k] = clampf(a2v[k] + (1.0f + p.t) * yb2, -kClip, kClip);
             na0[k] = -p.t * yb0; na1[k] = -p.t * yb1; na2[k] = -p.t * yb2;
             dgc[k] = 0.f; dgb[k] = 0.f;
-            go[k] = prox_reverse(xb0[k], hu[k], bq[k], cq[k], dgc[k], dgb[k]);
+            go[k] = prox_reverse_fast(xb0[k], hu[k], bq[k], cq[k], rcp_approx(1.0f + cq[k]), dgc[k], dgb[k]);
         }
         if (g.store) {
             st4(p.acc + o, pack(na0)); st4(p.acc + o + cstride, pack(na1)); st4(p.acc + o + 2 * cstride, pack(na2));

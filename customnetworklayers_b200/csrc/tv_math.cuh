@@ -161,6 +161,19 @@ __device__ __forceinline__ float rederive_y_fast(float x05, float x05m, float b,
     return fmaf(t, xk - xkm, xk);
 }
 
+// prox Jacobian with the reciprocal of (1 + c) supplied by the caller (see prox_reverse)
+__device__ __forceinline__ float prox_reverse_fast(float df_dxk, float x05, float b, float c, float inv1pc, float& dgc, float& dgb) {
+    const float diff = b - x05;
+    const float xi = df_dxk * inv1pc;
+    if (1.0f + c >= fabsf(diff)) {
+        dgc += xi * kLocalGC * (b - fmaf(c, b, x05) * inv1pc);
+        dgb += xi * c * kLocalGB;
+        return xi;
+    }
+    dgc += copysignf(kLocalGC, diff) * df_dxk;
+    return df_dxk;
+}
+
 __device__ __forceinline__ void tri_adjoint_fast(float yc, float yr, float yd, float gc, float gr, float gd,
                                                  float wx, float wy, float& phi1, float& phi2, float& dwx, float& dwy) {
     const float d1 = yc - yr;

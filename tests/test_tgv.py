@@ -101,8 +101,9 @@ def _run_cuda(ext, D, its, pid, n, ch, h, w):
     return five(sol), five(hist), five(cky), L, grads[:4] + [five(grads[4])]
 
 
+# widths divisible by 4 run the register-tiled kernels (tiles of 7 x 120 pixels), the others the scalar ones
 GPU_CASES = [(1, 1, 1, 1, 2), (1, 2, 5, 37, 4), (1, 1, 29, 3, 6), (2, 2, 40, 72, 20), (1, 3, 17, 33, 21), (1, 2, 96, 320, 20),
-             (1, 2, 64, 96, 50)]
+             (1, 2, 64, 96, 50), (1, 1, 3, 4, 2), (2, 3, 9, 124, 5), (1, 1, 15, 244, 6)]
 
 
 @pytest.mark.gpu
