@@ -27,6 +27,14 @@ __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.
 __device__ __forceinline__ void red_add4(float* p, const float4& v) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+// 16-byte asynchronous global->shared copy; with ok == false nothing is read and the destination is zero-filled
+__device__ __forceinline__ void cp_async16(float4* smem_dst, const float* gsrc, bool ok) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void unpack(const float4& v, float (&a)[4]) { a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w; }
 __device__ __forceinline__ float4 pack(const float (&a)[4]) { return make_float4(a[0], a[1], a[2], a[3]); }
 
@@ -110,22 +118,27 @@ __device__ __forceinline__ TriQ tri_quantities(float uc, float ur, float ud, flo
 __global__ void __launch_bounds__(kNT, 2)
 tgv_fwd_vec_kernel(const __grid_constant__ FwdVecParams p) {
     __shared__ float4 sh[2][3][kTgvWarps][32];        // per channel parity: Fy, G1y, G2y of each warp's row
+    __shared__ float4 slots[5][kNT];                  // private landing slots of the pointwise operands
+    float4* slot = &slots[0][threadIdx.x];
     const Geom g = make_geom(p.H, p.W);
     const size_t plane = (size_t)p.H * p.W;
     const size_t n = blockIdx.z;
     const float L = p.L[n];
     const Weights w = load_weights(p.dx, p.dy, n, plane, g, L);
-    float cf[4];
-    unpack(ld4(p.c + n * plane + g.pix, g.store), cf);
     const size_t cstride = (size_t)p.C * plane;         // distance between the u, v1, v2 planes of a channel
     for (int ch = 0; ch < p.C; ++ch) {
         const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
         const float4 yu4 = ld4(p.y_in + o, g.ok), y14 = ld4(p.y_in + o + cstride, g.ok), y24 = ld4(p.y_in + o + 2 * cstride, g.ok);
         const float4 du4 = ld4(p.y_in + o + p.W, g.okb), d14 = ld4(p.y_in + o + cstride + p.W, g.okb),
                      d24 = ld4(p.y_in + o + 2 * cstride + p.W, g.okb);
-        // pointwise operands are only needed where the CTA stores
-        const float4 xu4 = ld4c(p.x + o, g.store), x14 = ld4c(p.x + o + cstride, g.store), x24 = ld4c(p.x + o + 2 * cstride, g.store);
-        const float4 b4 = ld4(p.b + (n * p.C + ch) * plane + g.pix, g.store);
+        // pointwise operands are only needed where the CTA stores and not before the divergence: fetched
+        // asynchronously so that they hold no registers meanwhile
+        cp_async16(slot + 0 * kNT, p.x + o, g.store);
+        cp_async16(slot + 1 * kNT, p.x + o + cstride, g.store);
+        cp_async16(slot + 2 * kNT, p.x + o + 2 * cstride, g.store);
+        cp_async16(slot + 3 * kNT, p.b + (n * p.C + ch) * plane + g.pix, g.store);
+        cp_async16(slot + 4 * kNT, p.c + n * plane + g.pix, g.store);
+        cp_async_commit();
         if (p.ckpt && g.store) {
             st4(p.ckpt + o, yu4); st4(p.ckpt + o + cstride, y14); st4(p.ckpt + o + 2 * cstride, y24);
         }
@@ -164,8 +177,9 @@ tgv_fwd_vec_kernel(const __grid_constant__ FwdVecParams p) {
         const float fxl = __shfl_up_sync(kFull, fx[3], 1);      // horizontal fluxes of the pixel to the left
         const float g1xl = __shfl_up_sync(kFull, g1x[3], 1);
         const float g2xl = __shfl_up_sync(kFull, g2x[3], 1);
-        float xu[4], x1[4], x2[4], bq[4];
-        unpack(xu4, xu); unpack(x14, x1); unpack(x24, x2); unpack(b4, bq);
+        float xu[4], x1[4], x2[4], bq[4], cf[4];
+        cp_async_wait_all();
+        unpack(slot[0 * kNT], xu); unpack(slot[1 * kNT], x1); unpack(slot[2 * kNT], x2); unpack(slot[3 * kNT], bq); unpack(slot[4 * kNT], cf);
         float hu[4], h1[4], h2[4], nu[4], ou[4], o1[4], o2[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -225,8 +239,10 @@ __device__ __forceinline__ RowState load_row(const RevVecParams& p, size_t o, si
 
 __global__ void __launch_bounds__(kNT, 2)
 tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
-    __shared__ float4 sh_row[6][kTgvWarps][32];       // y (u, v1, v2) and g (u, v1, v2) of each warp's row
-    __shared__ float4 sh_flux[3][kTgvWarps][32];      // psi2, chi1y and the down-going chi2y of each warp's row
+    extern __shared__ float4 rev_smem[];
+    float4(*sh_row)[kTgvWarps][32] = reinterpret_cast<float4(*)[kTgvWarps][32]>(rev_smem);             // [6]: y and g planes of each warp's row
+    float4(*sh_flux)[kTgvWarps][32] = reinterpret_cast<float4(*)[kTgvWarps][32]>(rev_smem + 6 * kNT);  // [3]: psi2, chi1y, down-going chi2y
+    float4* slot = rev_smem + 9 * kNT + threadIdx.x;   // [6][kNT] private landing slots of the pointwise operands
     const Geom g = make_geom(p.H, p.W);
     const size_t plane = (size_t)p.H * p.W;
     const size_t n = blockIdx.z;
@@ -239,10 +255,14 @@ tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
         const size_t ob = (n * p.C + ch) * plane + g.pix;
         const RowState own = load_row(p, o, ob, oc, cstride, g.ok);
         // pointwise operands of the lane's own pixels (only where the CTA stores)
-        const float4 hu_raw = ld4(p.hist_g + o, g.store);                     // x^{g+1/2}, primary plane
-        const float4 b4 = ld4(p.b + ob, g.store);
-        const float4 c4 = ld4(p.c + oc, g.store);
-        const float4 au4 = ld4c(p.acc + o, g.store), a14 = ld4c(p.acc + o + cstride, g.store), a24 = ld4c(p.acc + o + 2 * cstride, g.store);
+        // they are not needed before the divergence: fetched asynchronously so that they hold no registers meanwhile
+        cp_async16(slot + 0 * kNT, p.hist_g + o, g.store);                    // x^{g+1/2}, primary plane
+        cp_async16(slot + 1 * kNT, p.b + ob, g.store);
+        cp_async16(slot + 2 * kNT, p.c + oc, g.store);
+        cp_async16(slot + 3 * kNT, p.acc + o, g.store);
+        cp_async16(slot + 4 * kNT, p.acc + o + cstride, g.store);
+        cp_async16(slot + 5 * kNT, p.acc + o + 2 * cstride, g.store);
+        cp_async_commit();
         sh_row[0][g.warp][g.lane] = own.yu; sh_row[1][g.warp][g.lane] = own.y1; sh_row[2][g.warp][g.lane] = own.y2;
         sh_row[3][g.warp][g.lane] = own.gu; sh_row[4][g.warp][g.lane] = own.g1; sh_row[5][g.warp][g.lane] = own.g2;
         RowState below;
@@ -320,7 +340,9 @@ tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
         const float C1xl = __shfl_up_sync(kFull, C1x[3], 1);
         const float C2xl = __shfl_up_sync(kFull, C2x[3], 1);
         float au[4], a1v[4], a2v[4], hu[4], bq[4], cq[4];
-        unpack(au4, au); unpack(a14, a1v); unpack(a24, a2v); unpack(hu_raw, hu); unpack(b4, bq); unpack(c4, cq);
+        cp_async_wait_all();
+        unpack(slot[0 * kNT], hu); unpack(slot[1 * kNT], bq); unpack(slot[2 * kNT], cq);
+        unpack(slot[3 * kNT], au); unpack(slot[4 * kNT], a1v); unpack(slot[5 * kNT], a2v);
         float xb0[4], xb1[4], xb2[4], na0[4], na1[4], na2[4], go[4], dgc[4], dgb[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -349,7 +371,13 @@ tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
 
 int launch_tgv_rev_vec(const RevVecParams& p, cudaStream_t st) {
     const dim3 grid((p.W + kTgvTileW - 1) / kTgvTileW, (p.H + kTgvTileH - 1) / kTgvTileH, p.N);
-    tgv_rev_vec_kernel<<<grid, kNT, 0, st>>>(p);
+    constexpr int smem_bytes = 15 * kNT * (int)sizeof(float4);
+    static bool attr_set = false;
+    if (!attr_set) {
+        CNL_TRY(check_cuda(cudaFuncSetAttribute(tgv_rev_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes), "cudaFuncSetAttribute"));
+        attr_set = true;
+    }
+    tgv_rev_vec_kernel<<<grid, kNT, smem_bytes, st>>>(p);
     return after_launch("tgv_rev_vec_kernel");
 }
 
