@@ -47,19 +47,29 @@ def tv_fwd_bwd_from_host(pipe: HostPipeline, host_in: Dict[str, torch.Tensor], h
     for lo in range(0, n, chunk):
         hi = min(n, lo + chunk)
         with torch.cuda.stream(pipe.s_in):
-            d = {k: host_in[k][lo:hi].to(dev, non_blocking=True) for k in IN_KEYS}
+            # what the forward pass needs first; the upstream gradient follows behind it
+            d = {k: host_in[k][lo:hi].to(dev, non_blocking=True) for k in IN_KEYS if k != "grad"}
             ev_in = torch.cuda.Event()
             ev_in.record(pipe.s_in)
+            d["grad"] = host_in["grad"][lo:hi].to(dev, non_blocking=True)
+            ev_grad = torch.cuda.Event()
+            ev_grad.record(pipe.s_in)
         comp.wait_event(ev_in)
         c = d["c"] * lam if lam is not None else d["c"]
         sol = ext.forward(d["wx"], d["wy"], c, d["b"], d["init"], its, pid)[0]
+        ev_f = torch.cuda.Event()
+        ev_f.record(comp)
+        pipe.s_out.wait_event(ev_f)
+        with torch.cuda.stream(pipe.s_out):          # the solution goes back while the backward pass runs
+            host_out["sol"][lo:hi].copy_(sol, non_blocking=True)
+        comp.wait_event(ev_grad)
         grads = ext.backward(d["grad"], d["wx"], d["wy"], c, d["b"], its, pid)
         g_lam += ext.lambda_grad(grads[2], d["c"])
         ev_c = torch.cuda.Event()
         ev_c.record(comp)
         pipe.s_out.wait_event(ev_c)
         with torch.cuda.stream(pipe.s_out):
-            for key, t in zip(OUT_KEYS, [sol] + list(grads)):
+            for key, t in zip(OUT_KEYS[1:], grads):
                 host_out[key][lo:hi].copy_(t, non_blocking=True)
         keep.append((d, c, sol, grads))
     allreduce_scalar_grads(g_lam)
