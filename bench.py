@@ -257,6 +257,7 @@ def run_ours(args, rank, local_rank, world):
     its_eff = 2 * (its // 2)
     pid = 0
     ext.set_option(pid, _lib.OPT_FUSE, args.fuse)
+    ext.set_option(pid, _lib.OPT_RECOMPUTE, 1 if args.recompute else 0)
     ext.set_option(pid, _lib.OPT_CONDITIONER, 1)
 
     # seeded synthetic inputs; every rank draws its own shard
@@ -351,6 +352,7 @@ def run_ours(args, rank, local_rank, world):
             "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{args.workload}: TV-FISTA fwd+bwd, per-GPU batch {nb}, flow {ch}x{h}x{w}, {its} iterations, lambda gradient all-reduced",
                        "global_batch": nb * world, "parallelism": f"dp{world}", "fuse": args.fuse,
+                       "history": "checkpoints only, segments recomputed in the backward pass" if args.recompute else "every iterate resident",
                        "l2": "per-step working set (iterate history) is far larger than the 126 MB L2; no flush"},
             "roofline": {"bound": "hbm", "kernel": "reverse iteration", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "traffic": ncu_traffic["reverse"] if ncu_traffic else None,
@@ -600,6 +602,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
     ap.add_argument("--fuse", type=int, default=0)
+    ap.add_argument("--recompute", action="store_true",
+                    help="keep only checkpoints on the device and rebuild the iterate history segment by segment in the backward pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunk", type=int, default=4, help="images per chunk of the host-buffer pipeline")
     args = ap.parse_args()

@@ -48,6 +48,7 @@ SIGNATURES = {
 OPT_CONDITIONER = 1
 OPT_FUSE = 2
 OPT_TIMING = 3
+OPT_RECOMPUTE = 4
 
 _lib = None
 

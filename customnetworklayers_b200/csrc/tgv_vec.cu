@@ -18,10 +18,6 @@ constexpr float kClip = 2000.0f;                                      // clipLoc
 __device__ __forceinline__ float4 ld4(const float* p, bool ok) {
     return ok ? __ldg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
 }
-// plain (coherent) load for planes this launch also writes
-__device__ __forceinline__ float4 ld4c(const float* p, bool ok) {
-    return ok ? *reinterpret_cast<const float4*>(p) : make_float4(0.f, 0.f, 0.f, 0.f);
-}
 __device__ __forceinline__ void st4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
 __device__ __forceinline__ float4 zero4() { return make_float4(0.f, 0.f, 0.f, 0.f); }
 __device__ __forceinline__ void red_add4(float* p, const float4& v) {

@@ -305,6 +305,9 @@ struct Slot {
     int opt_conditioner = 1;
     int opt_fuse = 0;
     int opt_timing = 0;
+    int opt_recompute = 0;           // 1: keep only checkpoints and rebuild each segment's history in the backward pass
+    bool recompute = false;          // mode the stored forward pass was run in
+    bool window_valid = false;       // recompute mode: the history window holds the LAST segment (left by the forward)
     // timing ring: per recorded call one (start, stop) event pair around the iteration loop and its launch count
     static constexpr int kRing = 64;
     cudaEvent_t ev_fwd[kRing][2] = {}, ev_rev[kRing][2] = {};
@@ -355,10 +358,12 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 // Layout of a slot's arena, in floats.  Every sub-buffer starts on a 256-byte boundary.
 struct ArenaLayout {
     size_t vol;       // n*ch*h*w rounded up to 64 floats
-    size_t y0, y1, xbuf, hist, ckpt, ga, gb, acc, acc2, ybuf, total;
+    size_t y0, y1, xbuf, hist, ckpt, xck, ga, gb, acc, acc2, ybuf, total;
 };
 
-static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t its_eff, size_t nckpt) {
+// hist_planes: its_eff when every iterate is kept, the longest segment in recompute mode; xck_planes: primal iterate
+// at every checkpoint (recompute mode only, needed to restart the iteration there).
+static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t hist_planes, size_t nckpt, size_t xck_planes = 0) {
     ArenaLayout L;
     L.vol = align_up(n * ch * h * w, 64);
     size_t o = 0;
@@ -371,7 +376,8 @@ static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t i
     L.xbuf = o; o += L.vol;
     L.ybuf = o; o += L.vol;
     L.ckpt = o; o += L.vol * nckpt;
-    L.hist = o; o += L.vol * its_eff;
+    L.xck = o; o += L.vol * xck_planes;
+    L.hist = o; o += L.vol * hist_planes;
     L.total = o;
     return L;
 }
@@ -388,6 +394,21 @@ static void compute_schedule(int its, std::vector<int>& sched, std::vector<float
         t = (1.0 + std::sqrt(1.0 + 4.0 * t * t)) / 2.0;
         steps[i] = (float)std::max(0.0, (t_ - 1.0) / t);
     }
+}
+
+// Segment i of the iteration runs from checkpoint iteration sched[i] up to (excluding) the next checkpoint.
+static inline int seg_begin(const std::vector<int>& sched, int i) { return sched[i]; }
+static inline int seg_end(const std::vector<int>& sched, int i, int its_eff) {
+    return i + 1 < (int)sched.size() ? sched[i + 1] : its_eff;
+}
+static int longest_segment(const std::vector<int>& sched, int its_eff) {
+    int m = 0;
+    for (int i = 0; i < (int)sched.size(); ++i) m = std::max(m, seg_end(sched, i, its_eff) - seg_begin(sched, i));
+    return m;
+}
+static ArenaLayout slot_layout(size_t n, size_t ch, size_t h, size_t w, int its_eff, const std::vector<int>& sched, bool recompute) {
+    if (recompute) return make_layout(n, ch, h, w, (size_t)longest_segment(sched, its_eff), sched.size(), sched.size());
+    return make_layout(n, ch, h, w, (size_t)its_eff, sched.size());
 }
 
 static int check_common(const void* const* ptrs, int nptr, int n, int ch, int h, int w, int its, int id) {
@@ -452,29 +473,49 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
     s.have_forward = false;
     compute_schedule(its, s.sched, s.steps);
     const int its_eff = 2 * (its / 2);
-    const ArenaLayout L = make_layout(n, ch, h, w, its_eff, s.sched.size());
+    const void* aligned[] = {wx, wy, c, b, init, out};          // the arena itself is 256-byte aligned
+    const int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
+    const bool fused = fuse > 1 && fused_supported(w, aligned, 6);
+    ArenaLayout L = slot_layout(n, ch, h, w, its_eff, s.sched, false);
+    // Keeping every iterate costs its_eff volumes.  When that exceeds the budget (or on request) only the checkpoints
+    // are kept and the backward pass rebuilds the history segment by segment, like the reference does
+    // (TVInpaintFista.cu:1690-1760); the temporally blocked kernels are needed for that.
+    const bool recompute = fused && (s.opt_recompute || L.total > arena_budget_floats());
+    if (recompute) L = slot_layout(n, ch, h, w, its_eff, s.sched, true);
     CNL_TRY(ensure_arena(s, L.total));
+    s.recompute = recompute;
+    s.window_valid = false;
     const size_t vol_bytes = (size_t)n * ch * h * w * sizeof(float);
     float* y0 = s.arena + L.y0;
     float* y1 = s.arena + L.y1;
-    const void* aligned[] = {wx, wy, c, b, init, out, s.arena};
-    int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
-    if (fuse > 1 && fused_supported(w, aligned, 7)) {
-        // temporally blocked path: `fuse` iterations per launch; x and y ping-pong between launches so that no CTA
-        // reads a halo another CTA is writing, and the last launch writes x into the caller's buffer
+    if (fused) {
+        // temporally blocked path: up to `fuse` iterations per launch; x and y ping-pong between launches so that no
+        // CTA reads a halo another CTA is writing, and the last launch writes x into the caller's buffer.  In
+        // recompute mode launches do not straddle checkpoints, the primal iterate is saved beside every checkpoint
+        // and only the last segment's history is written (the backward pass starts there).
         const bool timing = s.opt_timing && s.n_fwd < Slot::kRing;
         const unsigned long long launches0 = g_launches.load();
         if (timing) {
             CNL_TRY(ensure_events(s));
             CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][0], st), "cudaEventRecord"));
         }
-        const int nlaunch = (its_eff + fuse - 1) / fuse;
+        struct Launch { int g0, K; };
+        std::vector<Launch> plan;
+        if (recompute) {
+            for (int i = 0; i < (int)s.sched.size(); ++i)
+                for (int g0 = seg_begin(s.sched, i), e = seg_end(s.sched, i, its_eff); g0 < e; g0 += fuse)
+                    plan.push_back({g0, std::min(fuse, e - g0)});
+        } else {
+            for (int g0 = 0; g0 < its_eff; g0 += fuse) plan.push_back({g0, std::min(fuse, its_eff - g0)});
+        }
+        const int nlaunch = (int)plan.size();
+        const int last_seg = (int)s.sched.size() - 1;
         float* xbuf = s.arena + L.xbuf;
         const float* y_in = init;
         const float* x_in = init;
         size_t next_ckpt = 0;
-        for (int i = 0, g0 = 0; i < nlaunch; ++i) {
-            const int K = std::min(fuse, its_eff - g0);
+        for (int i = 0; i < nlaunch; ++i) {
+            const int g0 = plan[i].g0, K = plan[i].K;
             FwdFusedParams fp{};
             fp.y_in = y_in; fp.x_in = x_in;
             fp.y_out = (i & 1) ? y1 : y0;
@@ -483,18 +524,21 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
             fp.N = n; fp.C = ch; fp.H = h; fp.W = w;
             for (int j = 0; j < K; ++j) {
                 const int g = g0 + j;
-                fp.hist[j] = s.arena + L.hist + (size_t)g * L.vol;
                 fp.t[j] = s.steps[g];
                 fp.ckpt[j] = nullptr;
                 if (next_ckpt < s.sched.size() && s.sched[next_ckpt] == g) {
                     fp.ckpt[j] = s.arena + L.ckpt + next_ckpt * L.vol;
+                    if (recompute)      // j == 0 here: x at the checkpoint is this launch's input
+                        CNL_TRY(check_cuda(cudaMemcpyAsync(s.arena + L.xck + next_ckpt * L.vol, x_in, vol_bytes,
+                                                           cudaMemcpyDeviceToDevice, st), "checkpoint x"));
                     ++next_ckpt;
                 }
+                if (!recompute) fp.hist[j] = s.arena + L.hist + (size_t)g * L.vol;
+                else fp.hist[j] = g >= s.sched[last_seg] ? s.arena + L.hist + (size_t)(g - s.sched[last_seg]) * L.vol : nullptr;
             }
             CNL_TRY(launch_tv_fwd_fused(fp, K, st));
             y_in = fp.y_out;
             x_in = fp.x_out;
-            g0 += K;
         }
         if (timing) {
             CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][1], st), "cudaEventRecord"));
@@ -502,6 +546,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
             s.n_fwd += 1;
         }
         s.n = n; s.ch = ch; s.h = h; s.w = w; s.its = its;
+        s.window_valid = recompute;
         s.have_forward = true;
         return CNL_OK;
     }
@@ -553,7 +598,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
                     id, id);
     CNL_TRY(ensure_cond(s));
     const int its_eff = 2 * (its / 2);
-    const ArenaLayout L = make_layout(n, ch, h, w, its_eff, s.sched.size());
+    const ArenaLayout L = slot_layout(n, ch, h, w, its_eff, s.sched, s.recompute);
     const size_t plane = (size_t)h * w;
     const size_t vol_bytes = (size_t)n * ch * plane * sizeof(float);
     const size_t map_bytes = (size_t)n * plane * sizeof(float);
@@ -580,21 +625,68 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
             if (s.sched[i] == g) return s.arena + L.ckpt + i * L.vol;      // segment start: the checkpointed y_g (:1724-1727)
         return nullptr;
     };
+    const void* aligned[] = {wx, wy, c, b, g_wx, g_wy, g_c, g_b, g_init, s.arena};
+    const int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
+    const bool fused = fuse > 1 && fused_supported(w, aligned, 10);
+    if (s.recompute && !fused)
+        return fail(CNL_ERR_BAD_SHAPE, "the forward pass kept checkpoints only; the backward pass then needs 16-byte aligned tensors");
+    const int nseg = (int)s.sched.size();
+    // Recompute mode: rebuilds the history window of segment i from the y and x saved at its checkpoint.
+    auto rebuild_segment = [&](int i) -> int {
+        const int g_begin = seg_begin(s.sched, i), g_end = seg_end(s.sched, i, its_eff);
+        const float* y_in = s.arena + L.ckpt + (size_t)i * L.vol;
+        const float* x_in = s.arena + L.xck + (size_t)i * L.vol;
+        int k = 0;
+        for (int g0 = g_begin; g0 < g_end; g0 += fuse, ++k) {
+            const int K = std::min(fuse, g_end - g0);
+            FwdFusedParams fp{};
+            fp.y_in = y_in; fp.x_in = x_in;
+            fp.y_out = s.arena + ((k & 1) ? L.y1 : L.y0);        // iterates beyond the window are scratch
+            fp.x_out = s.arena + ((k & 1) ? L.ybuf : L.xbuf);
+            fp.b = b; fp.c = c; fp.wx = wx; fp.wy = wy;
+            fp.N = n; fp.C = ch; fp.H = h; fp.W = w;
+            for (int j = 0; j < K; ++j) {
+                fp.t[j] = s.steps[g0 + j];
+                fp.ckpt[j] = nullptr;
+                fp.hist[j] = s.arena + L.hist + (size_t)(g0 + j - g_begin) * L.vol;
+            }
+            CNL_TRY(launch_tv_fwd_fused(fp, K, st));
+            y_in = fp.y_out;
+            x_in = fp.x_out;
+        }
+        return CNL_OK;
+    };
+    // x^{g+1/2} of iteration g inside the segment whose history is resident (every iteration without recomputation)
+    const float* hist_base = hist;
+    int hist_first = 0;
+    auto hist_of = [&](int g) -> const float* { return g >= hist_first ? hist_base + (size_t)(g - hist_first) * L.vol : nullptr; };
+    if (s.recompute) {
+        hist_first = s.sched[nseg - 1];
+        if (!s.window_valid) CNL_TRY(rebuild_segment(nseg - 1));
+        s.window_valid = false;
+    }
     // seed at the last iteration (its_eff - 1 is odd, so the seed lands in the "odd" buffer like the reference's)
     {
         const int g = its_eff - 1;
-        tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hist + (size_t)g * L.vol, b, c, gb, g_c, g_b, ch, plane);
+        tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hist_of(g), b, c, gb, g_c, g_b, ch, plane);
         CNL_TRY(after_launch("tv_rev_seed_kernel"));
     }
-    const void* aligned[] = {wx, wy, c, b, g_wx, g_wy, g_c, g_b, g_init, s.arena};
-    const int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
-    if (fuse > 1 && fused_supported(w, aligned, 10)) {
+    if (fused) {
         float* acc2 = s.arena + L.acc2;
         const float* g_cur = gb;
         const float* acc_cur = acc;
         int flip = 0;
+        int seg = nseg - 1;                       // segment the sweep is in (recompute mode)
         for (int g0 = its_eff - 2; g0 >= 0;) {
-            const int K = std::min(fuse, g0 + 1);
+            int K = std::min(fuse, g0 + 1);
+            if (s.recompute) {
+                if (g0 < seg_begin(s.sched, seg)) {          // entering the next older segment: rebuild its history
+                    --seg;
+                    hist_first = seg_begin(s.sched, seg);
+                    CNL_TRY(rebuild_segment(seg));
+                }
+                K = std::min(K, g0 - seg_begin(s.sched, seg) + 1);      // launches do not straddle checkpoints
+            }
             RevFusedParams rp{};
             rp.g_in = g_cur; rp.acc_in = acc_cur;
             rp.g_out = flip ? gb : ga;
@@ -604,7 +696,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
             rp.N = n; rp.C = ch; rp.H = h; rp.W = w;
             for (int j = 0; j <= K; ++j) {
                 const int g = g0 - j;
-                rp.hist[j] = g >= 0 ? hist + (size_t)g * L.vol : nullptr;
+                rp.hist[j] = g >= 0 ? hist_of(g) : nullptr;
                 if (j < K) {
                     rp.t[j] = s.steps[g];
                     rp.ckpt[j] = ckpt_of(g);
@@ -692,10 +784,11 @@ extern "C" int cnl_tv_release(int id) {
     if (sp->events_ready)
         for (int i = 0; i < Slot::kRing; ++i)
             for (int j = 0; j < 2; ++j) { cudaEventDestroy(sp->ev_fwd[i][j]); cudaEventDestroy(sp->ev_rev[i][j]); }
-    const int keep_cond = sp->opt_conditioner, keep_fuse = sp->opt_fuse;
+    const int keep_cond = sp->opt_conditioner, keep_fuse = sp->opt_fuse, keep_rec = sp->opt_recompute;
     *sp = Slot();
     sp->opt_conditioner = keep_cond;
     sp->opt_fuse = keep_fuse;
+    sp->opt_recompute = keep_rec;
     return CNL_OK;
 }
 
@@ -710,7 +803,13 @@ static int read_iterate(int id, int idx, bool checkpoint, float* dst, void* stre
     const int its_eff = 2 * (sp->its / 2);
     const int limit = checkpoint ? (int)sp->sched.size() : its_eff;
     if (idx < 0 || idx >= limit) return fail(CNL_ERR_BAD_SHAPE, "index %d is outside 0..%d", idx, limit - 1);
-    const ArenaLayout L = make_layout(sp->n, sp->ch, sp->h, sp->w, its_eff, sp->sched.size());
+    const ArenaLayout L = slot_layout(sp->n, sp->ch, sp->h, sp->w, its_eff, sp->sched, sp->recompute);
+    if (!checkpoint && sp->recompute) {
+        const int first = sp->sched.back();
+        if (!sp->window_valid || idx < first)
+            return fail(CNL_ERR_NO_FORWARD, "iteration %d is not resident: this forward pass kept checkpoints only", idx);
+        idx -= first;
+    }
     const float* src = sp->arena + (checkpoint ? L.ckpt : L.hist) + (size_t)idx * L.vol;
     const size_t bytes = (size_t)sp->n * sp->ch * sp->h * sp->w * sizeof(float);
     return check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)),
@@ -746,6 +845,7 @@ extern "C" int cnl_tv_set_option(int id, int option, int value) {
             sp->opt_timing = value ? 1 : 0;
             sp->n_fwd = sp->n_rev = 0;
             return CNL_OK;
+        case CNL_OPT_RECOMPUTE: sp->opt_recompute = value ? 1 : 0; return CNL_OK;
         case CNL_OPT_FUSE:
             if (value < 0 || value > 4) return fail(CNL_ERR_BAD_OPTION, "fuse factor %d is outside 0..4", value);
             sp->opt_fuse = value;

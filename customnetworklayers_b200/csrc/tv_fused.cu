@@ -221,7 +221,7 @@ tv_fwd_fused_kernel(const __grid_constant__ FwdFusedParams p) {
                 const float fx_left = __shfl_up_sync(kFull, fx.w, 1);          // last pixel of the lane to the left
                 const float4 x05 = divergence_row(y[r], fx, fy, fx_left, fyc);
                 fyc = fy;
-                if (g.store[r]) st4(p.hist[j] + off[r], x05);
+                if (g.store[r] && p.hist[j]) st4(p.hist[j] + off[r], x05);
                 prox_extrapolate_row(x05, b[r], c[r], t, x[r], y[r]);
             }
         }
@@ -327,7 +327,7 @@ tv_fwd_pipe_kernel(const __grid_constant__ FwdFusedParams p, int tiles_x, int ti
                     const float fx_left = __shfl_up_sync(kFull, fx.w, 1);
                     const float4 x05 = divergence_row(y[r], fx, fy, fx_left, fyc);
                     fyc = fy;
-                    if (g.store[r]) st4(p.hist[j] + off[r], x05);
+                    if (g.store[r] && p.hist[j]) st4(p.hist[j] + off[r], x05);
                     prox_extrapolate_row(x05, b[r], c[r], t, x[r], y[r]);
                 }
             }

@@ -27,7 +27,7 @@ struct FwdFusedParams {
     const float* c;
     const float* wx;
     const float* wy;
-    float* hist[kFuseMax];      // destination of x^{g+1/2} for each fused iteration
+    float* hist[kFuseMax];      // destination of x^{g+1/2} for each fused iteration (null: not stored)
     float* ckpt[kFuseMax];      // if non-null: y before fused iteration j is stored here (checkpoint)
     float t[kFuseMax];          // momentum factors
     int N, C, H, W;

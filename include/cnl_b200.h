@@ -38,6 +38,12 @@ extern "C" {
 
 #define CNL_OPT_TIMING 3        /* 1: bracket the forward and the reverse iteration loop of every call with CUDA events on
                                    the caller's stream (up to 64 calls are kept); setting the option clears the records */
+#define CNL_OPT_RECOMPUTE 4     /* 0 (default): every pre-prox iterate is kept on the device (2*floor(its/2) volumes) unless
+                                   that exceeds the CNL_MAX_ARENA_GB budget; 1: always keep only the floor(sqrt(its))
+                                   checkpoints (y and x) and let the backward pass rebuild the history one checkpoint
+                                   segment at a time, as the reference does (cudaTV/cudaCode/TVInpaintFista.cu:1690-1760).
+                                   Costs one extra forward sweep per backward pass; needs widths divisible by 4 and
+                                   16-byte aligned tensors */
 
 /*
  * Forward pass of the unrolled FISTA TV-inpainting layer: 2*floor(its/2) iterations starting from x = y = init.
