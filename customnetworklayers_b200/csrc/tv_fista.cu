@@ -186,11 +186,23 @@ tv_grad_stats_kernel(FinalizeArgs a, double* __restrict__ partial) {
     const float* p = a.ptr[o];
     const unsigned long long cnt = a.count[o];
     double s = 0.0, bad = 0.0;
-    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < cnt;
-         i += (unsigned long long)gridDim.x * blockDim.x) {
-        const float v = p[i];
-        if (finite_f(v)) s += fabs((double)v); else bad += 1.0;
+    auto take = [&](float v) { if (finite_f(v)) s += fabs((double)v); else bad += 1.0; };
+    const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned long long nthreads = (unsigned long long)gridDim.x * blockDim.x;
+    // 16-byte vectors where the plane allows it (two in flight per thread), scalars for the tail
+    const unsigned long long nvec = (reinterpret_cast<size_t>(p) & 15) == 0 ? cnt / 4 : 0;
+    const float4* p4 = reinterpret_cast<const float4*>(p);
+    unsigned long long i = tid;
+    for (; i + nthreads < nvec; i += 2 * nthreads) {
+        const float4 a0 = p4[i], a1 = p4[i + nthreads];
+        take(a0.x); take(a0.y); take(a0.z); take(a0.w);
+        take(a1.x); take(a1.y); take(a1.z); take(a1.w);
     }
+    for (; i < nvec; i += nthreads) {
+        const float4 a0 = p4[i];
+        take(a0.x); take(a0.y); take(a0.z); take(a0.w);
+    }
+    for (i = nvec * 4 + tid; i < cnt; i += nthreads) take(p[i]);
     for (int off = 16; off > 0; off >>= 1) {
         s += __shfl_down_sync(0xffffffffu, s, off);
         bad += __shfl_down_sync(0xffffffffu, bad, off);
@@ -252,12 +264,24 @@ tv_grad_apply_kernel(FinalizeArgs a, const float* __restrict__ factor) {
     const unsigned long long cnt = a.count[o];
     const float f = (factor ? factor[o] : 1.0f);
     const float sc = a.scale[o];
-    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < cnt;
-         i += (unsigned long long)gridDim.x * blockDim.x) {
-        float v = p[i];
-        if (!finite_f(v) || fabsf(v) > 10000000.0f) v = 0.0f;
-        p[i] = v * f * sc;
+    auto fix = [&](float v) { return (!finite_f(v) || fabsf(v) > 10000000.0f) ? 0.0f : v * f * sc; };
+    const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned long long nthreads = (unsigned long long)gridDim.x * blockDim.x;
+    const unsigned long long nvec = (reinterpret_cast<size_t>(p) & 15) == 0 ? cnt / 4 : 0;
+    float4* p4 = reinterpret_cast<float4*>(p);
+    unsigned long long i = tid;
+    for (; i + nthreads < nvec; i += 2 * nthreads) {
+        float4 a0 = p4[i], a1 = p4[i + nthreads];
+        a0.x = fix(a0.x); a0.y = fix(a0.y); a0.z = fix(a0.z); a0.w = fix(a0.w);
+        a1.x = fix(a1.x); a1.y = fix(a1.y); a1.z = fix(a1.z); a1.w = fix(a1.w);
+        p4[i] = a0; p4[i + nthreads] = a1;
     }
+    for (; i < nvec; i += nthreads) {
+        float4 a0 = p4[i];
+        a0.x = fix(a0.x); a0.y = fix(a0.y); a0.z = fix(a0.z); a0.w = fix(a0.w);
+        p4[i] = a0;
+    }
+    for (i = nvec * 4 + tid; i < cnt; i += nthreads) p[i] = fix(p[i]);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
