@@ -184,3 +184,35 @@ def test_tgv_layer_api():
     assert all(t.grad is not None and torch.isfinite(t.grad).all() for t in leaves)
     r_sol, *_ = G.tgv_forward_history(I["dx"], I["dy"], I["c"], I["b"], I["init"], its)
     assert_close(out.permute(2, 0, 1).reshape(1, 3, ch, h, w), r_sol, "layer output")
+
+
+@pytest.mark.gpu
+def test_full_size_properties():
+    """Size-independent properties at the secondary benchmark's full size (batch 8, 2x436x1024, 100 iterations):
+    batch independence and linearity of the reverse sweep in the upstream gradient."""
+    from customnetworklayers_b200 import tgvInpaint_cuda_ext as ext
+    n, ch, h, w, its = 8, 2, 436, 1024, 100
+    D = {k: v.cuda() for k, v in make_tgv_inputs(n, ch, h, w, seed=99).items()}
+    flat = lambda t: t.reshape(t.shape[0], 3 * ch, h, w)
+    for pid in (7, 8):
+        ext.release(pid)
+        ext.set_option(pid, 1, 0)
+    try:
+        sol = ext.forward(D["dx"], D["dy"], D["c"], D["b"], flat(D["init"]), its, 7)[0]
+        g1 = ext.backward(flat(D["grad"]), D["dx"], D["dy"], D["c"], D["b"], its, 7)
+        assert all(bool(torch.isfinite(t).all()) for t in (sol,) + tuple(g1))
+        g2 = ext.backward(2.0 * flat(D["grad"]), D["dx"], D["dy"], D["c"], D["b"], its, 7)
+        for name, a, b in zip(NAMES, g1, g2):
+            assert float((2.0 * a - b).abs().max()) <= 1e-30, name + ": backward(2 g) != 2 backward(g)"
+        k = 3
+        one = {key: D[key][k:k + 1].contiguous() for key in D}
+        sol_k = ext.forward(one["dx"], one["dy"], one["c"], one["b"], flat(one["init"]), its, 8)[0]
+        gk = ext.backward(flat(one["grad"]), one["dx"], one["dy"], one["c"], one["b"], its, 8)
+        torch.cuda.synchronize()
+        assert torch.equal(sol_k[0], sol[k])
+        for name, a, b in zip(NAMES, g1, gk):
+            assert torch.equal(a[k], b[0]), name + ": batch member differs from the single call"
+    finally:
+        for pid in (7, 8):
+            ext.set_option(pid, 1, 1)
+            ext.release(pid)

@@ -348,3 +348,50 @@ def test_history_budget_switches_to_recomputation(ext, monkeypatch):
         monkeypatch.delenv("CNL_MAX_ARENA_GB", raising=False)
         ext.set_option(pid, _lib.OPT_CONDITIONER, 1)
         ext.release(pid)
+
+
+def test_full_size_properties(ext):
+    """Size-independent properties at the benchmark's full size (batch 8, 2x384x1280, 100 iterations), where the
+    oracle would take minutes: fixed point, batch independence, linearity of the reverse sweep, storage modes."""
+    from customnetworklayers_b200 import _lib
+    from customnetworklayers_b200.synthetic import make_inputs
+    n, ch, h, w, its = 8, 2, 384, 1280, 100
+    D = _dev(make_inputs(n, ch, h, w, seed=4321))
+    pid, pid1 = 7, 8
+    for p in (pid, pid1):
+        ext.release(p)
+        ext.set_option(p, _lib.OPT_CONDITIONER, 0)
+    try:
+        # a constant image is a fixed point of the smoothing step when c = 0
+        const = torch.full_like(D["b"], -1.75)
+        out = ext.forward(D["wx"], D["wy"], torch.zeros_like(D["c"]), D["b"], const, its, pid)[0]
+        assert torch.equal(out, const)
+        sol = ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, pid)[0]
+        g1 = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, pid)
+        assert all(bool(torch.isfinite(t).all()) for t in (sol,) + tuple(g1))
+        # the reverse sweep is linear in the upstream gradient; a factor of two is exact in binary floating point
+        g2 = ext.backward(2.0 * D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, pid)
+        for name, a, b2 in zip(GRAD_NAMES, g1, g2):
+            assert float((2.0 * a - b2).abs().max()) <= 1e-30, name + ": backward(2 g) != 2 backward(g)"
+        # images of a batch do not interact: image 5 alone gives the same bits
+        k = 5
+        one = {key: D[key][k:k + 1].contiguous() for key in D}
+        sol_k = ext.forward(one["wx"], one["wy"], one["c"], one["b"], one["init"], its, pid1)[0]
+        gk = ext.backward(one["grad"], one["wx"], one["wy"], one["c"], one["b"], its, pid1)
+        assert torch.equal(sol_k[0], sol[k])
+        for name, a, b2 in zip(GRAD_NAMES, g1, gk):
+            assert torch.equal(a[k], b2[0]), name + ": batch member differs from the single call"
+        # checkpoint-only storage gives the same solution and the same gradients up to the association of sums
+        ext.release(pid1)
+        ext.set_option(pid1, _lib.OPT_RECOMPUTE, 1)
+        sol_r = ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, pid1)[0]
+        gr = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, pid1)
+        torch.cuda.synchronize()
+        assert torch.equal(sol_r, sol)
+        for name, a, b2 in zip(GRAD_NAMES, g1, gr):
+            assert_close(b2, a, name, tol=1e-5)
+    finally:
+        ext.set_option(pid1, _lib.OPT_RECOMPUTE, 0)
+        for p in (pid, pid1):
+            ext.set_option(p, _lib.OPT_CONDITIONER, 1)
+            ext.release(p)
