@@ -38,8 +38,8 @@ SIGNATURES = {
     "cnl_tgv_set_option": (c_int, [c_int, c_int, c_int]),
     "cnl_tgv_read_state": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p]),
     "cnl_tgv_num_checkpoints": (c_int, [c_int]),
-    "cnl_wmedian_forward": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
-    "cnl_wmedian_backward": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_void_p]),
+    "cnl_wmedian_forward": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p]),
+    "cnl_wmedian_backward": (c_int, [c_void_p] * 8 + [c_int] * 5 + [c_void_p]),
     "cnl_wmedian_scratch_bytes": (c_longlong, [c_int]),
     "cnl_last_error": (c_char_p, []),
     "cnl_version": (c_char_p, []),

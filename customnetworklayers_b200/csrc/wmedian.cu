@@ -16,7 +16,6 @@ namespace cnl {
 namespace wmed {
 
 constexpr int NT = 128;
-constexpr int kMaxK = 49;
 
 // The k*k normalised weights (device memory) are copied to shared memory once per block; every thread then reads them
 // with compile-time indices (broadcast).
@@ -79,7 +78,7 @@ __device__ __forceinline__ Crossing scan_sorted(const float* __restrict__ sw) {
 template <int KS>
 __global__ void __launch_bounds__(NT)
 wmedian_forward_kernel(const float* __restrict__ flow, const float* __restrict__ weights, float* __restrict__ out,
-                       int* __restrict__ tap, long long total, int H, int W) {
+                       int* __restrict__ tap, float* __restrict__ alpha, long long total, int H, int W) {
     constexpr int K = KS * KS;
     extern __shared__ unsigned char smem_raw[];
     __shared__ float sp[K];
@@ -109,22 +108,25 @@ wmedian_forward_kernel(const float* __restrict__ flow, const float* __restrict__
         }
         out[idx] = o;
         if (tap) tap[idx] = t;
+        if (alpha) alpha[idx] = c.alpha;
     }
 }
 
 // Weight gradient: per problem d/dp in sorted order (medimax.cu:73, :91-95 with the output gradient as g0, g1 = 0),
 // scattered back to the taps and accumulated per thread in shared memory, reduced per block in a fixed order.
+// The sort is not repeated: a tap precedes the selected one in the stable ascending order exactly when its value is
+// smaller, or equal with a smaller window index; the selected tap and the interpolation factor alpha come from the
+// forward pass, the weight at the crossing is the selected tap's own weight.
 template <int KS>
 __global__ void __launch_bounds__(NT)
-wmedian_weight_grad_kernel(const float* __restrict__ flow, const float* __restrict__ weights, const float* __restrict__ grad,
-                           double* __restrict__ partial, long long total, int H, int W) {
+wmedian_weight_grad_kernel(const float* __restrict__ flow, const float* __restrict__ weights, const int* __restrict__ tap,
+                           const float* __restrict__ alpha, const float* __restrict__ grad, double* __restrict__ partial,
+                           long long total, int H, int W) {
     constexpr int K = KS * KS;
     extern __shared__ unsigned char smem_raw[];
     __shared__ float sp[K];
     stage_weights<K>(weights, sp);
-    float* sw = reinterpret_cast<float*>(smem_raw) + threadIdx.x;
-    float* sacc = reinterpret_cast<float*>(smem_raw) + (size_t)K * NT + threadIdx.x;
-    unsigned char* srank = smem_raw + (size_t)2 * K * NT * sizeof(float) + threadIdx.x;
+    float* sacc = reinterpret_cast<float*>(smem_raw) + threadIdx.x;            // sacc[i * NT]
     const long long plane = (long long)H * W;
 #pragma unroll
     for (int i = 0; i < K; ++i) sacc[i * NT] = 0.0f;
@@ -133,26 +135,24 @@ wmedian_weight_grad_kernel(const float* __restrict__ flow, const float* __restri
         const int pix = (int)(idx - img * plane), h = pix / W, w = pix - h * W;
         float v[K];
         load_window<KS>(flow + img * plane, h, w, H, W, v);
-#pragma unroll
-        for (int i = 0; i < K; ++i) {
-            const int r = rank_of<K>(v, i, v[i]);
-            sw[r * NT] = sp[i];
-            srank[i * NT] = (unsigned char)r;
-        }
-        const Crossing c = scan_sorted<K>(sw);
+        const int t = tap[idx];
         const float g0 = grad[idx];
-        const float half = (float)((double)g0 / (2.0 * (double)c.pmid));
-        const float mid = __fdiv_rn(__fmul_rn(g0, c.alpha), -c.pmid);
-        const int j = c.rank < 0 ? K : c.rank;                   // no crossing: every bin counts as "before"
+        const float pmid = t >= 0 ? sp[t] : 1.0f;
+        const float half = (float)((double)g0 / (2.0 * (double)pmid));
+        const float mid = __fdiv_rn(__fmul_rn(g0, alpha[idx]), -pmid);
+        float vsel = 0.0f;
+#pragma unroll
+        for (int i = 0; i < K; ++i) vsel = (i == t) ? v[i] : vsel;
 #pragma unroll
         for (int i = 0; i < K; ++i) {
-            const int r = srank[i * NT];
-            sacc[i * NT] += (r < j) ? -half : ((r > j) ? half : mid);
+            // no crossing (t < 0): every bin counts as "before"
+            const bool before = t < 0 || v[i] < vsel || (v[i] == vsel && i < t);
+            sacc[i * NT] += before ? -half : ((i == t) ? mid : half);
         }
     }
     __syncthreads();
     if (threadIdx.x < K) {
-        const float* row = reinterpret_cast<float*>(smem_raw) + (size_t)K * NT + (size_t)threadIdx.x * NT;
+        const float* row = reinterpret_cast<float*>(smem_raw) + (size_t)threadIdx.x * NT;
         double s = 0.0;
         for (int t = 0; t < NT; ++t) s += (double)row[t];
         partial[(size_t)blockIdx.x * K + threadIdx.x] = s;
@@ -196,23 +196,24 @@ wmedian_input_grad_kernel(const int* __restrict__ tap, const float* __restrict__
 constexpr int kGradBlocks = 592;
 
 template <int KS>
-static int run_forward(const float* flow, const float* wts, float* out, int* tap, long long total, int H, int W, cudaStream_t st) {
+static int run_forward(const float* flow, const float* wts, float* out, int* tap, float* alpha, long long total, int H, int W,
+                       cudaStream_t st) {
     constexpr int K = KS * KS;
     const int smem = K * NT * (int)sizeof(float) + K * NT;
     CNL_TRY(check_cuda(cudaFuncSetAttribute(wmedian_forward_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"));
     const unsigned blocks = (unsigned)std::min<long long>((total + NT - 1) / NT, 148LL * 64);
-    wmedian_forward_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, out, tap, total, H, W);
+    wmedian_forward_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, out, tap, alpha, total, H, W);
     return after_launch("wmedian_forward_kernel");
 }
 
 template <int KS>
-static int run_backward(const float* flow, const float* wts, const int* tap, const float* grad, float* g_flow, float* g_p,
-                        double* scratch, long long total, int H, int W, cudaStream_t st) {
+static int run_backward(const float* flow, const float* wts, const int* tap, const float* alpha, const float* grad,
+                        float* g_flow, float* g_p, double* scratch, long long total, int H, int W, cudaStream_t st) {
     constexpr int K = KS * KS;
-    const int smem = 2 * K * NT * (int)sizeof(float) + K * NT;
+    const int smem = K * NT * (int)sizeof(float);
     CNL_TRY(check_cuda(cudaFuncSetAttribute(wmedian_weight_grad_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"));
     const int blocks = (int)std::min<long long>((total + NT - 1) / NT, kGradBlocks);
-    wmedian_weight_grad_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, grad, scratch, total, H, W);
+    wmedian_weight_grad_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, tap, alpha, grad, scratch, total, H, W);
     CNL_TRY(after_launch("wmedian_weight_grad_kernel"));
     wmedian_weight_grad_final_kernel<<<1, 64, 0, st>>>(scratch, blocks, K, g_p);
     CNL_TRY(after_launch("wmedian_weight_grad_final_kernel"));
@@ -234,32 +235,32 @@ using namespace cnl;
 
 extern "C" long long cnl_wmedian_scratch_bytes(int k) { return (long long)wmed::kGradBlocks * k * k * (long long)sizeof(double); }
 
-extern "C" int cnl_wmedian_forward(const float* flow, const float* weights, float* out, int* tap, int n, int c, int h,
-                                   int w, int k, void* stream) {
+extern "C" int cnl_wmedian_forward(const float* flow, const float* weights, float* out, int* tap, float* alpha, int n,
+                                   int c, int h, int w, int k, void* stream) {
     if (!flow || !weights || !out) return fail(CNL_ERR_NULL, "null pointer argument");
     CNL_TRY(wmed::check(n, c, h, w, k));
     const float* wts = weights;
     const long long total = (long long)n * c * h * w;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (k) {
-        case 3: return wmed::run_forward<3>(flow, wts, out, tap, total, h, w, st);
-        case 5: return wmed::run_forward<5>(flow, wts, out, tap, total, h, w, st);
-        default: return wmed::run_forward<7>(flow, wts, out, tap, total, h, w, st);
+        case 3: return wmed::run_forward<3>(flow, wts, out, tap, alpha, total, h, w, st);
+        case 5: return wmed::run_forward<5>(flow, wts, out, tap, alpha, total, h, w, st);
+        default: return wmed::run_forward<7>(flow, wts, out, tap, alpha, total, h, w, st);
     }
 }
 
-extern "C" int cnl_wmedian_backward(const float* flow, const float* weights, const int* tap, const float* grad,
-                                    float* g_flow, float* g_weights, void* scratch, int n, int c, int h, int w, int k,
-                                    void* stream) {
-    if (!flow || !weights || !tap || !grad || !g_flow || !g_weights || !scratch) return fail(CNL_ERR_NULL, "null pointer argument");
+extern "C" int cnl_wmedian_backward(const float* flow, const float* weights, const int* tap, const float* alpha,
+                                    const float* grad, float* g_flow, float* g_weights, void* scratch, int n, int c, int h,
+                                    int w, int k, void* stream) {
+    if (!flow || !weights || !tap || !alpha || !grad || !g_flow || !g_weights || !scratch) return fail(CNL_ERR_NULL, "null pointer argument");
     CNL_TRY(wmed::check(n, c, h, w, k));
     const float* wts = weights;
     const long long total = (long long)n * c * h * w;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     double* sc = static_cast<double*>(scratch);
     switch (k) {
-        case 3: return wmed::run_backward<3>(flow, wts, tap, grad, g_flow, g_weights, sc, total, h, w, st);
-        case 5: return wmed::run_backward<5>(flow, wts, tap, grad, g_flow, g_weights, sc, total, h, w, st);
-        default: return wmed::run_backward<7>(flow, wts, tap, grad, g_flow, g_weights, sc, total, h, w, st);
+        case 3: return wmed::run_backward<3>(flow, wts, tap, alpha, grad, g_flow, g_weights, sc, total, h, w, st);
+        case 5: return wmed::run_backward<5>(flow, wts, tap, alpha, grad, g_flow, g_weights, sc, total, h, w, st);
+        default: return wmed::run_backward<7>(flow, wts, tap, alpha, grad, g_flow, g_weights, sc, total, h, w, st);
     }
 }

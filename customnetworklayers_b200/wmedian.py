@@ -14,7 +14,8 @@ from .tvInpaint_cuda_ext import _check_input, _stream_ptr
 
 
 def forward(flow: torch.Tensor, p: torch.Tensor, k: int):
-    """flow [N,C,H,W], p [k*k] normalised weights (CUDA fp32) -> (out [N,C,H,W], tap [N,C,H,W] int32)."""
+    """flow [N,C,H,W], p [k*k] normalised weights (CUDA fp32) -> (out [N,C,H,W], tap [N,C,H,W] int32,
+    alpha [N,C,H,W] = interpolation factor of the selection rule at the crossing, kept for the backward pass)."""
     _check_input(flow, "flow")
     _check_input(p, "p")
     if p.numel() != k * k:
@@ -22,16 +23,17 @@ def forward(flow: torch.Tensor, p: torch.Tensor, k: int):
     n, c, h, w = flow.shape
     out = torch.empty_like(flow)
     tap = torch.empty((n, c, h, w), dtype=torch.int32, device=flow.device)
+    alpha = torch.empty_like(flow)
     with torch.cuda.device(flow.device):
-        rc = _lib.load().cnl_wmedian_forward(flow.data_ptr(), p.data_ptr(), out.data_ptr(), tap.data_ptr(), n, c, h, w, k,
-                                             _stream_ptr(flow.device))
+        rc = _lib.load().cnl_wmedian_forward(flow.data_ptr(), p.data_ptr(), out.data_ptr(), tap.data_ptr(), alpha.data_ptr(),
+                                             n, c, h, w, k, _stream_ptr(flow.device))
     _lib.check(rc, "weighted median forward")
-    return out, tap
+    return out, tap, alpha
 
 
-def backward(flow, p, tap, grad, k: int):
+def backward(flow, p, tap, alpha, grad, k: int):
     """Returns (g_flow [N,C,H,W], g_p [k*k])."""
-    for t, nm in ((flow, "flow"), (p, "p"), (grad, "grad")):
+    for t, nm in ((flow, "flow"), (p, "p"), (alpha, "alpha"), (grad, "grad")):
         _check_input(t, nm)
     n, c, h, w = flow.shape
     lib = _lib.load()
@@ -39,8 +41,9 @@ def backward(flow, p, tap, grad, k: int):
     g_p = torch.empty(k * k, dtype=torch.float32, device=flow.device)
     scratch = torch.empty(lib.cnl_wmedian_scratch_bytes(k) // 8, dtype=torch.float64, device=flow.device)
     with torch.cuda.device(flow.device):
-        rc = lib.cnl_wmedian_backward(flow.data_ptr(), p.data_ptr(), tap.data_ptr(), grad.data_ptr(), g_flow.data_ptr(),
-                                      g_p.data_ptr(), scratch.data_ptr(), n, c, h, w, k, _stream_ptr(flow.device))
+        rc = lib.cnl_wmedian_backward(flow.data_ptr(), p.data_ptr(), tap.data_ptr(), alpha.data_ptr(), grad.data_ptr(),
+                                      g_flow.data_ptr(), g_p.data_ptr(), scratch.data_ptr(), n, c, h, w, k,
+                                      _stream_ptr(flow.device))
     _lib.check(rc, "weighted median backward")
     return g_flow, g_p
 
@@ -49,15 +52,15 @@ class WeightedMedianFunction(Function):
     @staticmethod
     def forward(ctx, flow, p, k):
         flow, p = flow.contiguous(), p.contiguous()
-        out, tap = forward(flow, p, k)
-        ctx.save_for_backward(flow, p, tap)
+        out, tap, alpha = forward(flow, p, k)
+        ctx.save_for_backward(flow, p, tap, alpha)
         ctx.k = k
         return out
 
     @staticmethod
     def backward(ctx, grad):
-        flow, p, tap = ctx.saved_tensors
-        g_flow, g_p = backward(flow, p, tap, grad.contiguous(), ctx.k)
+        flow, p, tap, alpha = ctx.saved_tensors
+        g_flow, g_p = backward(flow, p, tap, alpha, grad.contiguous(), ctx.k)
         return g_flow, g_p, None
 
 

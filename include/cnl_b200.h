@@ -197,15 +197,17 @@ int cnl_tgv_num_checkpoints(int id);
  * k*k normalised weights (device memory, must sum to 1) permuted alike, then the reference's selection rule
  * (sequential fp32 running sum, first rank with score < 0.5 <= score + p; cudaMedian/cudaCode/medimax.cu:27-40).
  *   flow, out, grad, g_flow [n][c][h][w]; tap [n][c][h][w] int = selected window offset index (row-major, -1: none);
+ *   alpha [n][c][h][w] = the rule's interpolation factor (1 - 2 score - p) / (2 p) at the crossing (medimax.cu:33),
+ *   which the backward pass needs; tap and alpha may be null in a forward call that no backward call follows;
  *   g_weights [k*k] = the reference's d/dp (medimax.cu:55-98, output gradient in the role of the position gradient)
  *   scattered back through the sort and summed over all pixels in a fixed order; g_flow = pass-through to the selected
  *   tap.  scratch: cnl_wmedian_scratch_bytes(k) bytes of device memory.
  * Only the selection rule and d/dp have a reference counterpart; the window, the sort and the input gradient do not.
  */
-int cnl_wmedian_forward(const float* flow, const float* weights, float* out, int* tap, int n, int c, int h, int w, int k,
-                        void* stream);
-int cnl_wmedian_backward(const float* flow, const float* weights, const int* tap, const float* grad, float* g_flow,
-                         float* g_weights, void* scratch, int n, int c, int h, int w, int k, void* stream);
+int cnl_wmedian_forward(const float* flow, const float* weights, float* out, int* tap, float* alpha, int n, int c, int h,
+                        int w, int k, void* stream);
+int cnl_wmedian_backward(const float* flow, const float* weights, const int* tap, const float* alpha, const float* grad,
+                         float* g_flow, float* g_weights, void* scratch, int n, int c, int h, int w, int k, void* stream);
 long long cnl_wmedian_scratch_bytes(int k);
 
 /* Message for the last error on the calling thread ("" if none). */

@@ -52,8 +52,8 @@ def test_cuda_matches_oracle(case):
     if h * w > 4:
         flow[0, 0, 1, :3] = 5.0                    # ties: the stable order decides
     p = (wts / wts.sum()).float()
-    out, tap = wm.forward(flow.cuda(), p.cuda(), k)
-    g_flow, g_p = wm.backward(flow.cuda(), p.cuda(), tap, grad.cuda(), k)
+    out, tap, alpha = wm.forward(flow.cuda(), p.cuda(), k)
+    g_flow, g_p = wm.backward(flow.cuda(), p.cuda(), tap, alpha, grad.cuda(), k)
     o_ref, t_ref, _ = W.wmedian_forward(flow.numpy(), p.numpy(), k)
     gf_ref, gp_ref = W.wmedian_backward(flow.numpy(), p.numpy(), grad.numpy(), k)
     assert np.array_equal(tap.cpu().numpy(), t_ref), "selected tap must be bit-exact"
