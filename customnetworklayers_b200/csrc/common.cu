@@ -1,6 +1,10 @@
 // Error reporting and launch accounting of the C-ABI library.
 #include "common.h"
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 namespace cnl {
 
 std::atomic<unsigned long long> g_launches{0};
@@ -18,6 +22,19 @@ int fail(int code, const char* fmt, ...) {
     va_end(ap);
     last_error_ref() = buf;
     return code;
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, int> done;      // (kernel, device) -> bytes granted
+    int dev = 0;
+    CNL_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
+    std::lock_guard<std::mutex> lock(mu);
+    int& granted = done[{kernel, dev}];
+    if (granted >= bytes) return CNL_OK;
+    CNL_TRY(check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "cudaFuncSetAttribute"));
+    granted = bytes;
+    return CNL_OK;
 }
 
 }  // namespace cnl

@@ -20,6 +20,12 @@ inline int check_cuda(cudaError_t e, const char* what) {
     return fail(CNL_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
+// Opts a kernel in to `bytes` of dynamic shared memory once per (kernel, device); the attribute belongs to the device's
+// context, so a process that drives several GPUs needs it on each.
+int ensure_dynamic_smem(const void* kernel, int bytes);
+template <typename K>
+inline int ensure_dynamic_smem(K* kernel, int bytes) { return ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), bytes); }
+
 // Counts a launch and turns a launch-configuration error into an error code.
 inline int after_launch(const char* kernel) {
     g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -133,8 +133,7 @@ static int median_smem(int k) { return kMedWarps * 32 * (k | 1) * (int)sizeof(fl
 template <typename Kern>
 static int median_prepare(Kern kern, int k) {
     const int bytes = median_smem(k);
-    if (bytes > 48 * 1024)
-        return check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "cudaFuncSetAttribute");
+    if (bytes > 48 * 1024) return ensure_dynamic_smem(kern, bytes);
     return CNL_OK;
 }
 

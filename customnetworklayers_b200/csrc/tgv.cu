@@ -722,12 +722,7 @@ static int backward_impl(const float* dx, const float* dy, const float* c, const
     const dim3 grid((w + TW - 1) / TW, (h + TH - 1) / TH, n);
     const void* planes[] = {dx, dy, c, b, g_dx, g_dy, g_c, g_b, g_init, s.arena};
     const bool vec = vec_enabled() && tgv_vec_supported(w, planes, 10);
-    static bool attr = false;
-    if (!attr) {
-        CNL_TRY(check_cuda(cudaFuncSetAttribute(tgv_rev_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                kRevSmemFloats * (int)sizeof(float)), "cudaFuncSetAttribute"));
-        attr = true;
-    }
+    CNL_TRY(ensure_dynamic_smem(tgv_rev_kernel, kRevSmemFloats * (int)sizeof(float)));
     {
         const int g = its_eff - 1;
         tgv_seed_kernel<<<dim3((unsigned)((plane + NT - 1) / NT), n), NT, 0, st>>>(grad, hist + (size_t)g * l.vol, b, c, gb, g_c, g_b, ch, plane);

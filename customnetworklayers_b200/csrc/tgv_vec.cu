@@ -368,11 +368,7 @@ tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
 int launch_tgv_rev_vec(const RevVecParams& p, cudaStream_t st) {
     const dim3 grid((p.W + kTgvTileW - 1) / kTgvTileW, (p.H + kTgvTileH - 1) / kTgvTileH, p.N);
     constexpr int smem_bytes = 15 * kNT * (int)sizeof(float4);
-    static bool attr_set = false;
-    if (!attr_set) {
-        CNL_TRY(check_cuda(cudaFuncSetAttribute(tgv_rev_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes), "cudaFuncSetAttribute"));
-        attr_set = true;
-    }
+    CNL_TRY(ensure_dynamic_smem(tgv_rev_vec_kernel, smem_bytes));
     tgv_rev_vec_kernel<<<grid, kNT, smem_bytes, st>>>(p);
     return after_launch("tgv_rev_vec_kernel");
 }

@@ -368,14 +368,10 @@ int launch_tv_fwd_fused(const FwdFusedParams& p, int K, cudaStream_t st) {
     const int TH = kRegionH - 2 * K;
     const dim3 grid((p.W + kTileW - 1) / kTileW, (p.H + TH - 1) / TH, p.N);
     if (pipeline_enabled() && (long long)grid.x * grid.y * grid.z < (1ll << 30)) {
-        static bool attr_set[kFuseMax + 1] = {};
         const long long ntiles = (long long)grid.x * grid.y * grid.z;
         const unsigned ctas = (unsigned)std::min<long long>(ntiles, sm_count());
         auto go = [&](auto kern) -> int {
-            if (!attr_set[K]) {
-                CNL_TRY(check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdPipeSmemBytes), "cudaFuncSetAttribute"));
-                attr_set[K] = true;
-            }
+            CNL_TRY(ensure_dynamic_smem(kern, kFwdPipeSmemBytes));
             kern<<<ctas, kThreads, kFwdPipeSmemBytes, st>>>(p, (int)grid.x, (int)grid.y);
             return after_launch("tv_fwd_pipe_kernel");
         };
@@ -577,32 +573,18 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
 
 int launch_tv_rev_fused(const RevFusedParams& p, int K, cudaStream_t st) {
     if (K < 1 || K > kFuseMax) return fail(CNL_ERR_BAD_OPTION, "fuse factor %d is outside 1..%d", K, kFuseMax);
-    static bool attr_set[kFuseMax + 1] = {};
     const int TH = kRegionH - 2 * K;
     const dim3 grid((p.W + kTileW - 1) / kTileW, (p.H + TH - 1) / TH, p.N);
-    auto set_attr = [&](const void* fn) -> int {
-        if (attr_set[K]) return CNL_OK;
-        attr_set[K] = true;
-        return check_cuda(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kRevSmemBytes),
-                          "cudaFuncSetAttribute");
+    auto go = [&](auto kern) -> int {
+        CNL_TRY(ensure_dynamic_smem(kern, kRevSmemBytes));
+        kern<<<grid, kThreads, kRevSmemBytes, st>>>(p);
+        return CNL_OK;
     };
     switch (K) {
-        case 1:
-            CNL_TRY(set_attr(reinterpret_cast<const void*>(tv_rev_fused_kernel<1>)));
-            tv_rev_fused_kernel<1><<<grid, kThreads, kRevSmemBytes, st>>>(p);
-            break;
-        case 2:
-            CNL_TRY(set_attr(reinterpret_cast<const void*>(tv_rev_fused_kernel<2>)));
-            tv_rev_fused_kernel<2><<<grid, kThreads, kRevSmemBytes, st>>>(p);
-            break;
-        case 3:
-            CNL_TRY(set_attr(reinterpret_cast<const void*>(tv_rev_fused_kernel<3>)));
-            tv_rev_fused_kernel<3><<<grid, kThreads, kRevSmemBytes, st>>>(p);
-            break;
-        default:
-            CNL_TRY(set_attr(reinterpret_cast<const void*>(tv_rev_fused_kernel<4>)));
-            tv_rev_fused_kernel<4><<<grid, kThreads, kRevSmemBytes, st>>>(p);
-            break;
+        case 1: CNL_TRY(go(tv_rev_fused_kernel<1>)); break;
+        case 2: CNL_TRY(go(tv_rev_fused_kernel<2>)); break;
+        case 3: CNL_TRY(go(tv_rev_fused_kernel<3>)); break;
+        default: CNL_TRY(go(tv_rev_fused_kernel<4>)); break;
     }
     return after_launch("tv_rev_fused_kernel");
 }

@@ -125,15 +125,6 @@ __device__ __forceinline__ float rcp_approx(float x) {
     return r;
 }
 
-__device__ __forceinline__ void tri_flux_fast(float yc, float yr, float yd, float wx, float wy, float& fx, float& fy) {
-    const float wd1 = wx * (yc - yr);
-    const float wd2 = wy * (yc - yd);
-    const float A = fmaf(wd1, yc - yr, wd2 * (yc - yd));
-    const float s = fminf(1.0f, kDelta * rsqrt_approx(A));
-    fx = s * wd1;
-    fy = s * wd2;
-}
-
 // prox with the reciprocal of (1 + c) supplied by the caller
 __device__ __forceinline__ float prox_huber_fast(float x05, float b, float c, float inv1pc) {
     float x = fmaf(c, b, x05) * inv1pc;
@@ -172,29 +163,6 @@ __device__ __forceinline__ float prox_reverse_fast(float df_dxk, float x05, floa
     }
     dgc += copysignf(kLocalGC, diff) * df_dxk;
     return df_dxk;
-}
-
-__device__ __forceinline__ void tri_adjoint_fast(float yc, float yr, float yd, float gc, float gr, float gd,
-                                                 float wx, float wy, float& phi1, float& phi2, float& dwx, float& dwy) {
-    const float d1 = yc - yr;
-    const float d2 = yc - yd;
-    const float e1 = gc - gr;
-    const float e2 = gc - gd;
-    const float wd1 = wx * d1;
-    const float wd2 = wy * d2;
-    const float A = fmaf(wd1, d1, wd2 * d2);
-    const float r = rsqrt_approx(A);             // 1/T
-    const bool big = kDelta * r < 1.0f;          // T > delta
-    const float nom = big ? kDelta * r : 1.0f;
-    const float den = big ? 0.5f * nom * r * r : 0.0f;
-    const float S = fmaf(wd1, e1, wd2 * e2);
-    const float k2 = 2.0f * den * S;
-    phi1 = wx * fmaf(nom, e1, -k2 * d1);
-    phi2 = wy * fmaf(nom, e2, -k2 * d2);
-    // dwx = -kLocalGX d1 (nom e1 - den d1 (wx d1 e1 + wy d2 e2)) ; same for y
-    const float dS = den * S;
-    dwx = -kLocalGX * d1 * fmaf(nom, e1, -dS * d1);
-    dwy = -kLocalGX * d2 * fmaf(nom, e2, -dS * d2);
 }
 
 }  // namespace cnl

@@ -200,7 +200,7 @@ static int run_forward(const float* flow, const float* wts, float* out, int* tap
                        cudaStream_t st) {
     constexpr int K = KS * KS;
     const int smem = K * NT * (int)sizeof(float) + K * NT;
-    CNL_TRY(check_cuda(cudaFuncSetAttribute(wmedian_forward_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"));
+    CNL_TRY(ensure_dynamic_smem(wmedian_forward_kernel<KS>, smem));
     const unsigned blocks = (unsigned)std::min<long long>((total + NT - 1) / NT, 148LL * 64);
     wmedian_forward_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, out, tap, alpha, total, H, W);
     return after_launch("wmedian_forward_kernel");
@@ -211,7 +211,7 @@ static int run_backward(const float* flow, const float* wts, const int* tap, con
                         float* g_flow, float* g_p, double* scratch, long long total, int H, int W, cudaStream_t st) {
     constexpr int K = KS * KS;
     const int smem = K * NT * (int)sizeof(float);
-    CNL_TRY(check_cuda(cudaFuncSetAttribute(wmedian_weight_grad_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute"));
+    CNL_TRY(ensure_dynamic_smem(wmedian_weight_grad_kernel<KS>, smem));
     const int blocks = (int)std::min<long long>((total + NT - 1) / NT, kGradBlocks);
     wmedian_weight_grad_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, tap, alpha, grad, scratch, total, H, W);
     CNL_TRY(after_launch("wmedian_weight_grad_kernel"));
