@@ -2,6 +2,9 @@
 // cudaTGV/cudaCode/TGVInpaintFistaBetas.cu:1546-1776 forward and :224-644 / :1061-1473 reverse, as in tgv.cu).
 #include "tgv_vec.cuh"
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.h"
 #include "tv_math.cuh"
 
@@ -44,12 +47,12 @@ struct Geom {
     size_t pix;       // gy * W + gx (0 when !ok)
 };
 
-__device__ __forceinline__ Geom make_geom(int H, int W) {
+__device__ __forceinline__ Geom make_geom_at(int tx, int ty, int H, int W) {
     Geom g;
     g.lane = threadIdx.x & 31;
     g.warp = threadIdx.x >> 5;
-    g.gx = blockIdx.x * kTgvTileW - 4 + 4 * g.lane;
-    g.gy = blockIdx.y * kTgvTileH - 1 + g.warp;
+    g.gx = tx * kTgvTileW - 4 + 4 * g.lane;
+    g.gy = ty * kTgvTileH - 1 + g.warp;
     const bool col = g.gx >= 0 && g.gx < W;
     g.ok = col && g.gy >= 0 && g.gy < H;
     g.okb = col && g.gy + 1 >= 0 && g.gy + 1 < H;
@@ -60,27 +63,33 @@ __device__ __forceinline__ Geom make_geom(int H, int W) {
     g.pix = g.ok ? (size_t)g.gy * W + g.gx : 0;
     return g;
 }
+__device__ __forceinline__ Geom make_geom(int H, int W) { return make_geom_at(blockIdx.x, blockIdx.y, H, W); }
 
 // Edge weights of the lane's four triangles, scaled by 1/Lipschitz and zero where no edge leaves the pixel.
 struct Weights {
     float wx[4], wy[4], b0[4], b1[4];
 };
-__device__ __forceinline__ Weights load_weights(const float* dx, const float* dy, size_t n, size_t plane, const Geom& g, float L) {
+__device__ __forceinline__ Weights scale_weights(const float4& wx, const float4& wy, const float4& bx, const float4& by,
+                                                 const Geom& g, float L) {
     Weights w;
     float a[4];
-    unpack(ld4(dx + (n * 2 + 0) * plane + g.pix, g.ok), a);
+    unpack(wx, a);
 #pragma unroll
     for (int k = 0; k < 4; ++k) w.wx[k] = g.mx[k] ? __fmul_rn(L, a[k]) : 0.f;
-    unpack(ld4(dy + (n * 2 + 0) * plane + g.pix, g.ok), a);
+    unpack(wy, a);
 #pragma unroll
     for (int k = 0; k < 4; ++k) w.wy[k] = g.my ? __fmul_rn(L, a[k]) : 0.f;
-    unpack(ld4(dx + (n * 2 + 1) * plane + g.pix, g.ok), a);
+    unpack(bx, a);
 #pragma unroll
     for (int k = 0; k < 4; ++k) w.b0[k] = g.ok ? __fmul_rn(L, a[k]) : 0.f;
-    unpack(ld4(dy + (n * 2 + 1) * plane + g.pix, g.ok), a);
+    unpack(by, a);
 #pragma unroll
     for (int k = 0; k < 4; ++k) w.b1[k] = g.ok ? __fmul_rn(L, a[k]) : 0.f;
     return w;
+}
+__device__ __forceinline__ Weights load_weights(const float* dx, const float* dy, size_t n, size_t plane, const Geom& g, float L) {
+    return scale_weights(ld4(dx + (n * 2 + 0) * plane + g.pix, g.ok), ld4(dy + (n * 2 + 0) * plane + g.pix, g.ok),
+                         ld4(dx + (n * 2 + 1) * plane + g.pix, g.ok), ld4(dy + (n * 2 + 1) * plane + g.pix, g.ok), g, L);
 }
 
 // Differences and Huber factors of the triangle anchored at one pixel (c = centre, r = right, d = below).
@@ -196,6 +205,138 @@ tgv_fwd_vec_kernel(const __grid_constant__ FwdVecParams p) {
             st4(p.y_out + o, pack(ou)); st4(p.y_out + o + cstride, pack(o1)); st4(p.y_out + o + 2 * cstride, pack(o2));
         }
     }
+}
+
+// Persistent, software-pipelined forward iteration: two CTAs per SM walk over the (tile, channel) items.  Every operand
+// of an item lands in shared memory by cp.async while the previous item is still being finished, so no warp waits
+// for DRAM at the head of an item, and the row below a warp's own is read from the neighbouring warp's landing slots
+// instead of being fetched twice.
+constexpr int kFwdPipeSmemBytes = (2 * 3 * kNT + 8 * kNT + 4 * kNT + 3 * 32) * (int)sizeof(float4);
+
+__global__ void __launch_bounds__(kNT, 2)
+tgv_fwd_pipe_kernel(const __grid_constant__ FwdVecParams p, int tiles_x, int tiles_y) {
+    extern __shared__ float4 fwd_smem[];
+    float4(*ex)[3][kTgvWarps][32] = reinterpret_cast<float4(*)[3][kTgvWarps][32]>(fwd_smem);          // [2]: flux exchange
+    float4(*sy)[kTgvWarps][32] = reinterpret_cast<float4(*)[kTgvWarps][32]>(fwd_smem + 6 * kNT);     // [3]: y rows of the item
+    float4* sx = fwd_smem + 9 * kNT + threadIdx.x;       // [5][kNT]: x (3 planes), b, c of the lane's own pixels
+    float4* sw = fwd_smem + 14 * kNT + threadIdx.x;      // [4][kNT]: wx, wy, beta_x, beta_y of the tile
+    float4(*sbelow)[32] = reinterpret_cast<float4(*)[32]>(fwd_smem + 18 * kNT);                      // [3]: row under the region
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t plane = (size_t)p.H * p.W;
+    const size_t cstride = (size_t)p.C * plane;
+    const int ntiles = tiles_x * tiles_y * p.N;
+
+    auto tile_geom = [&](int tile, size_t& n) -> Geom {
+        const int tx = tile % tiles_x, q = tile / tiles_x;
+        n = (size_t)(q / tiles_y);
+        return make_geom_at(tx, q % tiles_y, p.H, p.W);
+    };
+    // starts fetching every operand of (tile, ch); the edge weights only with the first channel of a tile
+    auto issue = [&](int tile, int ch) {
+        if (tile < ntiles) {
+            size_t n;
+            const Geom g = tile_geom(tile, n);
+            const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                cp_async16(&sy[q][warp][lane], p.y_in + o + q * cstride, g.ok);
+                if (warp == kTgvWarps - 1) cp_async16(&sbelow[q][lane], p.y_in + o + q * cstride + (g.okb ? p.W : 0), g.okb);
+                cp_async16(sx + q * kNT, p.x + o + q * cstride, g.store);
+            }
+            cp_async16(sx + 3 * kNT, p.b + (n * p.C + ch) * plane + g.pix, g.store);
+            cp_async16(sx + 4 * kNT, p.c + n * plane + g.pix, g.store);
+            if (ch == 0) {
+                cp_async16(sw + 0 * kNT, p.dx + (n * 2 + 0) * plane + g.pix, g.ok);
+                cp_async16(sw + 1 * kNT, p.dy + (n * 2 + 0) * plane + g.pix, g.ok);
+                cp_async16(sw + 2 * kNT, p.dx + (n * 2 + 1) * plane + g.pix, g.ok);
+                cp_async16(sw + 3 * kNT, p.dy + (n * 2 + 1) * plane + g.pix, g.ok);
+            }
+        }
+        cp_async_commit();
+    };
+
+    int tile = blockIdx.x;
+    if (tile >= ntiles) return;
+    issue(tile, 0);
+    int parity = 0;
+    for (; tile < ntiles; tile += gridDim.x) {
+        size_t n;
+        const Geom g = tile_geom(tile, n);
+        const float L = p.L[n];
+        Weights w;
+        for (int ch = 0; ch < p.C; ++ch, parity ^= 1) {
+            const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
+            cp_async_wait_all();
+            __syncthreads();                                  // every thread's operands of this item have landed
+            if (ch == 0) w = scale_weights(sw[0 * kNT], sw[1 * kNT], sw[2 * kNT], sw[3 * kNT], g, L);
+            const float4 yu4 = sy[0][warp][lane], y14 = sy[1][warp][lane], y24 = sy[2][warp][lane];
+            float4 du4, d14, d24;
+            if (warp < kTgvWarps - 1) { du4 = sy[0][warp + 1][lane]; d14 = sy[1][warp + 1][lane]; d24 = sy[2][warp + 1][lane]; }
+            else { du4 = sbelow[0][lane]; d14 = sbelow[1][lane]; d24 = sbelow[2][lane]; }
+            if (p.ckpt && g.store) {
+                st4(p.ckpt + o, yu4); st4(p.ckpt + o + cstride, y14); st4(p.ckpt + o + 2 * cstride, y24);
+            }
+            float yu[5], y1[5], y2[5], du[4], d1[4], d2[4];
+            {
+                float a[4];
+                unpack(yu4, a); for (int k = 0; k < 4; ++k) yu[k] = a[k];
+                unpack(y14, a); for (int k = 0; k < 4; ++k) y1[k] = a[k];
+                unpack(y24, a); for (int k = 0; k < 4; ++k) y2[k] = a[k];
+            }
+            unpack(du4, du); unpack(d14, d1); unpack(d24, d2);
+            yu[4] = __shfl_down_sync(kFull, yu4.x, 1);
+            y1[4] = __shfl_down_sync(kFull, y14.x, 1);
+            y2[4] = __shfl_down_sync(kFull, y24.x, 1);
+            float fx[4], fy[4], g1x[4], g1y[4], g2x[4], g2y[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const TriQ t = tri_quantities(yu[k], yu[k + 1], du[k], y1[k], y1[k + 1], d1[k], y2[k], y2[k + 1], d2[k],
+                                              w.wx[k], w.wy[k], w.b0[k], w.b1[k], g.mx[k], g.my);
+                fx[k] = w.wx[k] * t.z1 * t.Hu;
+                fy[k] = w.wy[k] * t.z2 * t.Hu;
+                g1x[k] = w.b0[k] * t.a1[0] * t.H[0];
+                g1y[k] = w.b0[k] * t.a2[0] * t.H[0];
+                g2x[k] = w.b1[k] * t.a1[1] * t.H[1];
+                g2y[k] = w.b1[k] * t.a2[1] * t.H[1];
+            }
+            ex[parity][0][warp][lane] = pack(fy);
+            ex[parity][1][warp][lane] = pack(g1y);
+            ex[parity][2][warp][lane] = pack(g2y);
+            __syncthreads();                                  // fluxes published; all reads of the y rows are done
+            float xu[4], x1[4], x2[4], bq[4], cf[4];
+            unpack(sx[0 * kNT], xu); unpack(sx[1 * kNT], x1); unpack(sx[2 * kNT], x2); unpack(sx[3 * kNT], bq); unpack(sx[4 * kNT], cf);
+            // every landing slot is free again: start fetching the next item
+            if (ch + 1 < p.C) issue(tile, ch + 1);
+            else issue(tile + gridDim.x, 0);
+            float fya[4], g1ya[4], g2ya[4];
+            unpack(warp > 0 ? ex[parity][0][warp - 1][lane] : zero4(), fya);
+            unpack(warp > 0 ? ex[parity][1][warp - 1][lane] : zero4(), g1ya);
+            unpack(warp > 0 ? ex[parity][2][warp - 1][lane] : zero4(), g2ya);
+            const float fxl = __shfl_up_sync(kFull, fx[3], 1);
+            const float g1xl = __shfl_up_sync(kFull, g1x[3], 1);
+            const float g2xl = __shfl_up_sync(kFull, g2x[3], 1);
+            float hu[4], h1[4], h2[4], nu[4], ou[4], o1[4], o2[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float fx_l = k == 0 ? fxl : fx[k - 1];
+                const float g1x_l = k == 0 ? g1xl : g1x[k - 1];
+                const float g2x_l = k == 0 ? g2xl : g2x[k - 1];
+                hu[k] = yu[k] + fx[k] + fy[k] - fx_l - fya[k];
+                h1[k] = y1[k] + g1x[k] + g1y[k] - g1x_l - g1ya[k] + fx[k];
+                h2[k] = y2[k] + g2x[k] + g2y[k] - g2x_l - g2ya[k] + fy[k];
+                nu[k] = prox_huber_fast(hu[k], bq[k], cf[k], rcp_approx(1.0f + cf[k]));
+                ou[k] = nu[k] + p.t * (nu[k] - xu[k]);
+                o1[k] = h1[k] + p.t * (h1[k] - x1[k]);
+                o2[k] = h2[k] + p.t * (h2[k] - x2[k]);
+            }
+            if (g.store) {
+                st4(p.hist + o, pack(hu)); st4(p.hist + o + cstride, pack(h1)); st4(p.hist + o + 2 * cstride, pack(h2));
+                st4(p.x + o, pack(nu));    st4(p.x + o + cstride, pack(h1));    st4(p.x + o + 2 * cstride, pack(h2));
+                st4(p.y_out + o, pack(ou)); st4(p.y_out + o + cstride, pack(o1)); st4(p.y_out + o + 2 * cstride, pack(o2));
+            }
+        }
+    }
+    cp_async_wait_all();
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -380,8 +521,27 @@ bool tgv_vec_supported(int W, const void* const* ptrs, int nptr) {
     return true;
 }
 
+// Tiles a launch must have before the persistent kernel is used; CNL_TGV_PIPELINE_MIN_TILES overrides the default
+// (read at every call so that tests can force either kernel; a negative value disables the persistent kernel).
+static long long pipeline_min_tiles(int sms) {
+    const char* e = std::getenv("CNL_TGV_PIPELINE_MIN_TILES");
+    if (e && e[0]) { const long long v = std::atoll(e); return v < 0 ? (1ll << 40) : v; }
+    return 16LL * sms;
+}
+
 int launch_tgv_fwd_vec(const FwdVecParams& p, cudaStream_t st) {
     const dim3 grid((p.W + kTgvTileW - 1) / kTgvTileW, (p.H + kTgvTileH - 1) / kTgvTileH, p.N);
+    const long long ntiles = (long long)grid.x * grid.y * grid.z;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    // the persistent kernel pays off once every CTA has a queue of tiles to overlap (measured: 3 % faster at 15 tiles
+    // per CTA, 10 % slower at 4)
+    if (ntiles >= pipeline_min_tiles(sms) && ntiles < (1ll << 30)) {
+        CNL_TRY(ensure_dynamic_smem(tgv_fwd_pipe_kernel, kFwdPipeSmemBytes));
+        const unsigned ctas = (unsigned)std::min<long long>(ntiles, 2LL * sms);
+        tgv_fwd_pipe_kernel<<<ctas, kNT, kFwdPipeSmemBytes, st>>>(p, (int)grid.x, (int)grid.y);
+        return after_launch("tgv_fwd_pipe_kernel");
+    }
     tgv_fwd_vec_kernel<<<grid, kNT, 0, st>>>(p);
     return after_launch("tgv_fwd_vec_kernel");
 }
