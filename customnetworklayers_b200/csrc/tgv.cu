@@ -444,11 +444,23 @@ tgv_stats_kernel(FinArgs a, double* __restrict__ partial) {
     const int o = blockIdx.y;
     const float* p = a.ptr[o];
     double s = 0.0, bad = 0.0;
-    for (unsigned long long i = (unsigned long long)blockIdx.x * 256 + threadIdx.x; i < a.count[o];
-         i += (unsigned long long)gridDim.x * 256) {
-        const float v = p[i];
-        if (finite_f(v)) s += fmin(fabs((double)v), 5000000.0); else bad += 1.0;
+    auto take = [&](float v) { if (finite_f(v)) s += fmin(fabs((double)v), 5000000.0); else bad += 1.0; };
+    const unsigned long long cnt = a.count[o];
+    const unsigned long long tid = (unsigned long long)blockIdx.x * 256 + threadIdx.x, nthreads = (unsigned long long)gridDim.x * 256;
+    // 16-byte vectors where the plane allows it (two in flight per thread), scalars for the tail
+    const unsigned long long nvec = (reinterpret_cast<size_t>(p) & 15) == 0 ? cnt / 4 : 0;
+    const float4* p4 = reinterpret_cast<const float4*>(p);
+    unsigned long long i = tid;
+    for (; i + nthreads < nvec; i += 2 * nthreads) {
+        const float4 a0 = p4[i], a1 = p4[i + nthreads];
+        take(a0.x); take(a0.y); take(a0.z); take(a0.w);
+        take(a1.x); take(a1.y); take(a1.z); take(a1.w);
     }
+    for (; i < nvec; i += nthreads) {
+        const float4 a0 = p4[i];
+        take(a0.x); take(a0.y); take(a0.z); take(a0.w);
+    }
+    for (i = nvec * 4 + tid; i < cnt; i += nthreads) take(p[i]);
     for (int off = 16; off > 0; off >>= 1) {
         s += __shfl_down_sync(0xffffffffu, s, off);
         bad += __shfl_down_sync(0xffffffffu, bad, off);
@@ -493,15 +505,25 @@ tgv_apply_kernel(FinArgs a, const float* __restrict__ factor, const float* __res
     const int o = blockIdx.y;
     float* p = a.ptr[o];
     const float f = factor ? factor[o] : 1.0f;
-    for (unsigned long long i = (unsigned long long)blockIdx.x * 256 + threadIdx.x; i < a.count[o];
-         i += (unsigned long long)gridDim.x * 256) {
-        float v = p[i];
+    const float base = a.scale[o];
+    const bool perL = a.per_image_L[o] != 0;
+    const unsigned long long per = a.per_image[o], cnt = a.count[o];
+    auto fix = [&](float v, float sc) {
         if (!finite_f(v)) v = 0.f;
-        v = clampf(v, -5000000.0f, 5000000.0f);
-        float sc = a.scale[o];
-        if (a.per_image_L[o]) sc *= Lbuf[i / a.per_image[o]];
-        p[i] = v * f * sc;
+        return clampf(v, -5000000.0f, 5000000.0f) * f * sc;
+    };
+    const unsigned long long tid = (unsigned long long)blockIdx.x * 256 + threadIdx.x, nthreads = (unsigned long long)gridDim.x * 256;
+    // a 16-byte vector never straddles two images when the per-image element count is a multiple of 4
+    const bool vec_ok = (reinterpret_cast<size_t>(p) & 15) == 0 && (!perL || per % 4 == 0);
+    const unsigned long long nvec = vec_ok ? cnt / 4 : 0;
+    float4* p4 = reinterpret_cast<float4*>(p);
+    for (unsigned long long i = tid; i < nvec; i += nthreads) {
+        float4 v = p4[i];
+        const float sc = perL ? base * Lbuf[(i * 4) / per] : base;
+        v.x = fix(v.x, sc); v.y = fix(v.y, sc); v.z = fix(v.z, sc); v.w = fix(v.w, sc);
+        p4[i] = v;
     }
+    for (unsigned long long i = nvec * 4 + tid; i < cnt; i += nthreads) p[i] = fix(p[i], perL ? base * Lbuf[i / per] : base);
 }
 
 // flags[0] = number of non-finite entries, flags[1] = number of non-zero entries of the upstream gradient
