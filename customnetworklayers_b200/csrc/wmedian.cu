@@ -4,12 +4,15 @@
 // Output = value of the selected tap; the window, the sort and the pass-through input gradient have no counterpart in
 // the reference.
 //
-// One thread per (image, channel, pixel).  The K = k*k window values live in registers; the rank of every tap is
-// found by comparing it with all others (K*(K-1) compares, no data-dependent branches), which places its weight at
-// its sorted position in a thread-private column of shared memory; the scan then runs over that column in rank
-// order, i.e. in exactly the order the selection rule prescribes, so the selected index is bit-identical to the
-// CPU restatement.  The [N,H,W,K] weight volume of the reference layout is never materialised: HBM traffic is one
+// The K = k*k window values live in registers; the rank of every tap in the stable ascending order (found by
+// comparing it with all others at the start of a run of pixels, then updated incrementally as the window slides)
+// places its weight at its sorted position in a thread-private column of shared memory; the scan then runs over
+// that column in rank order, i.e. in exactly the order the selection rule prescribes, so the selected index is
+// bit-identical to the CPU restatement.  The [N,H,W,K] weight volume of the reference layout is never materialised: HBM traffic is one
 // read and one write per pixel, the kernel is bound by the compares.
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.h"
 
 namespace cnl {
@@ -112,6 +115,120 @@ wmedian_forward_kernel(const float* __restrict__ flow, const float* __restrict__
     }
 }
 
+// Sliding-window variant of the forward kernel.  A thread walks along kRun consecutive pixels of one image row and
+// keeps the window values AND their ranks in registers: moving one pixel to the right removes the left column
+// (every kept rank drops by the number of removed taps below it), shifts the columns, and inserts the new right
+// column (one compare per (kept, new) pair decides both ranks), i.e. about K*2*KS compares per pixel instead of
+// K*(K-1).  The stable order breaks ties by window index (row-major), which is invariant under the shift; a new tap
+// sits in the last column, so it precedes an equal kept tap exactly when its window row is smaller.  Lanes of a
+// warp take consecutive image rows, so the column loads of neighbouring lanes share cache lines.
+constexpr int kRun = 32;
+
+template <int KS>
+__global__ void __launch_bounds__(NT)
+wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __restrict__ weights, float* __restrict__ out,
+                             int* __restrict__ tap, float* __restrict__ alpha, long long nthreads, int H, int W, int runs) {
+    constexpr int K = KS * KS, R = KS / 2;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ float sp[K];
+    stage_weights<K>(weights, sp);
+    float* sw = reinterpret_cast<float*>(smem_raw) + threadIdx.x;                      // sw[r * NT]
+    unsigned char* sidx = smem_raw + (size_t)K * NT * sizeof(float) + threadIdx.x;     // sidx[r * NT]
+    const long long plane = (long long)H * W;
+    for (long long tix = (long long)blockIdx.x * NT + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * NT) {
+        const int h = (int)(tix % H);
+        const long long q = tix / H;
+        const int run = (int)(q % runs);
+        const long long img = q / runs;
+        const float* src = flow + img * plane;
+        const int w0 = run * kRun;
+        int rowoff[KS];
+#pragma unroll
+        for (int dy = 0; dy < KS; ++dy) rowoff[dy] = min(max(h + dy - R, 0), H - 1) * W;
+        float v[K];
+        int rk[K];
+#pragma unroll
+        for (int dy = 0; dy < KS; ++dy)
+#pragma unroll
+            for (int dx = 0; dx < KS; ++dx) v[dy * KS + dx] = __ldg(src + rowoff[dy] + min(max(w0 + dx - R, 0), W - 1));
+#pragma unroll
+        for (int i = 0; i < K; ++i) rk[i] = rank_of<K>(v, i, v[i]);
+        float nxt[KS];                                       // right column of the next pixel's window
+#pragma unroll
+        for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + min(w0 + 1 + R, W - 1));
+        const int wend = min(w0 + kRun, W);
+        for (int w = w0; w < wend; ++w) {
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                sw[rk[i] * NT] = sp[i];
+                sidx[rk[i] * NT] = (unsigned char)i;
+            }
+            const Crossing c = scan_sorted<K>(sw);
+            int t = -1;
+            float o = v[K / 2];                                  // no crossing: the centre value passes through
+            if (c.rank >= 0) {
+                t = sidx[c.rank * NT];
+                const int dy = t / KS, dx = t % KS - R;
+                o = __ldg(src + rowoff[dy] + min(max(w + dx, 0), W - 1));
+            }
+            const long long idx = img * plane + (long long)h * W + w;
+            out[idx] = o;
+            if (tap) tap[idx] = t;
+            if (alpha) alpha[idx] = c.alpha;
+            if (w + 1 >= wend) break;
+            // --- slide the window one pixel to the right ---
+            // 1. remove column 0: a kept tap loses one rank for every removed tap that was below it
+#pragma unroll
+            for (int dy = 0; dy < KS; ++dy)
+#pragma unroll
+                for (int dx = 1; dx < KS; ++dx) {
+                    int drop = 0;
+#pragma unroll
+                    for (int ry = 0; ry < KS; ++ry) drop += (rk[ry * KS] < rk[dy * KS + dx]) ? 1 : 0;
+                    rk[dy * KS + dx] -= drop;
+                }
+            // 2. shift the columns
+#pragma unroll
+            for (int dy = 0; dy < KS; ++dy)
+#pragma unroll
+                for (int dx = 0; dx + 1 < KS; ++dx) {
+                    v[dy * KS + dx] = v[dy * KS + dx + 1];
+                    rk[dy * KS + dx] = rk[dy * KS + dx + 1];
+                }
+            // 3. insert the new right column
+            int rnew[KS];
+#pragma unroll
+            for (int ny = 0; ny < KS; ++ny) rnew[ny] = 0;
+#pragma unroll
+            for (int ny = 0; ny < KS; ++ny) {
+                const float x = nxt[ny];
+#pragma unroll
+                for (int dy = 0; dy < KS; ++dy)
+#pragma unroll
+                    for (int dx = 0; dx + 1 < KS; ++dx) {
+                        // kept tap first: smaller value, or equal value and not a later window row
+                        const bool kept_first = (dy <= ny) ? (v[dy * KS + dx] <= x) : (v[dy * KS + dx] < x);
+                        rnew[ny] += kept_first ? 1 : 0;
+                        rk[dy * KS + dx] += kept_first ? 0 : 1;
+                    }
+#pragma unroll
+                for (int my = 0; my < ny; ++my) {               // among the new taps the smaller row wins ties
+                    const bool other_first = nxt[my] <= x;
+                    rnew[ny] += other_first ? 1 : 0;
+                    rnew[my] += other_first ? 0 : 1;
+                }
+            }
+#pragma unroll
+            for (int ny = 0; ny < KS; ++ny) {
+                v[ny * KS + KS - 1] = nxt[ny];
+                rk[ny * KS + KS - 1] = rnew[ny];
+            }
+#pragma unroll
+            for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + min(w + 2 + R, W - 1));
+        }
+    }
+}
+
 // Weight gradient: per problem d/dp in sorted order (medimax.cu:73, :91-95 with the output gradient as g0, g1 = 0),
 // scattered back to the taps and accumulated per thread in shared memory, reduced per block in a fixed order.
 // The sort is not repeated: a tap precedes the selected one in the stable ascending order exactly when its value is
@@ -195,12 +312,26 @@ wmedian_input_grad_kernel(const int* __restrict__ tap, const float* __restrict__
 
 constexpr int kGradBlocks = 592;
 
+// CNL_WMEDIAN_NO_SLIDE=1 selects the one-thread-per-pixel forward kernel (read at every call)
+static bool slide_enabled() {
+    const char* e = std::getenv("CNL_WMEDIAN_NO_SLIDE");
+    return !(e && e[0] == '1');
+}
+
 template <int KS>
 static int run_forward(const float* flow, const float* wts, float* out, int* tap, float* alpha, long long total, int H, int W,
                        cudaStream_t st) {
     constexpr int K = KS * KS;
     const int smem = K * NT * (int)sizeof(float) + K * NT;
     CNL_TRY(ensure_dynamic_smem(wmedian_forward_kernel<KS>, smem));
+    if (slide_enabled()) {
+        CNL_TRY(ensure_dynamic_smem(wmedian_forward_slide_kernel<KS>, smem));
+        const int runs = (W + kRun - 1) / kRun;
+        const long long nthreads = total / W * runs;                 // one thread per (image-channel, row, run)
+        const unsigned sblocks = (unsigned)std::min<long long>((nthreads + NT - 1) / NT, 148LL * 64);
+        wmedian_forward_slide_kernel<KS><<<sblocks, NT, smem, st>>>(flow, wts, out, tap, alpha, nthreads, H, W, runs);
+        return after_launch("wmedian_forward_slide_kernel");
+    }
     const unsigned blocks = (unsigned)std::min<long long>((total + NT - 1) / NT, 148LL * 64);
     wmedian_forward_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, out, tap, alpha, total, H, W);
     return after_launch("wmedian_forward_kernel");

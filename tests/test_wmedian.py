@@ -43,7 +43,8 @@ def test_weight_gradient_sums_reference_dp_through_the_permutation():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("case", [(1, 1, 1, 1, 7), (1, 2, 9, 11, 3), (2, 2, 17, 33, 5), (1, 2, 40, 56, 7), (3, 1, 8, 64, 7)],
+@pytest.mark.parametrize("case", [(1, 1, 1, 1, 7), (1, 2, 9, 11, 3), (2, 2, 17, 33, 5), (1, 2, 40, 56, 7), (3, 1, 8, 64, 7),
+                                  (1, 1, 37, 200, 7), (2, 1, 5, 97, 5), (1, 1, 3, 70, 3)],
                          ids=lambda c: "n%d_c%d_%dx%d_k%d" % c)
 def test_cuda_matches_oracle(case):
     from customnetworklayers_b200 import wmedian as wm
@@ -51,6 +52,10 @@ def test_cuda_matches_oracle(case):
     flow, wts, grad = make_median_filter_inputs(n, c, h, w, k=k, seed=10 + k)
     if h * w > 4:
         flow[0, 0, 1, :3] = 5.0                    # ties: the stable order decides
+    if w >= 64:                                    # ties that enter and leave the sliding window, also across rows
+        flow[0, 0, h // 2, 20:60] = -1.25
+        flow[0, 0, :, 33] = flow[0, 0, :, 34]
+        flow[0, 0, min(h - 1, 2), 40:50] = flow[0, 0, 0, 40:50]
     p = (wts / wts.sum()).float()
     out, tap, alpha = wm.forward(flow.cuda(), p.cuda(), k)
     g_flow, g_p = wm.backward(flow.cuda(), p.cuda(), tap, alpha, grad.cuda(), k)
