@@ -245,6 +245,12 @@ def run_ours(args, rank, local_rank, world):
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the product path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa_cpus = None
+    if world > 1 and os.environ.get("CNL_BIND_NUMA", "0") == "1":
+        from customnetworklayers_b200.dist import bind_to_gpu_numa_node
+        numa_cpus = bind_to_gpu_numa_node(local_rank)          # before any pinned allocation
+    if os.environ.get("CNL_BENCH_DEBUG"):
+        print(f"[rank {rank}] cpus allowed {sorted(os.sched_getaffinity(0))} numa bind {numa_cpus}", file=sys.stderr, flush=True)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()

@@ -3,7 +3,8 @@ collective is a sum all-reduce of the learned-scalar gradients.  Uses torch.dist
 CPU tests); images never cross ranks."""
 from __future__ import annotations
 
-from typing import Tuple
+import os
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -23,3 +24,27 @@ def allreduce_scalar_grads(g: torch.Tensor, group=None) -> torch.Tensor:
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
     return g
+
+
+def bind_to_gpu_numa_node(device_index: int) -> Optional[List[int]]:
+    """Restricts the calling process to the CPUs NVML reports as closest to CUDA device `device_index`, so that pinned
+    staging buffers allocated afterwards land (by first touch) in the host memory next to that GPU.  Matters when
+    several ranks of one host stream to their GPUs at the same time.  Returns the CPU list, or None when nothing was
+    changed (NVML unavailable, no overlap with the CPUs this process may use).  Reads NVML only; changes no GPU setting."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        props = torch.cuda.get_device_properties(device_index)
+        bus_id = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (max(ncpu, 64) + 63) // 64 * 2)
+        near = {64 * i + b for i, wd in enumerate(words) for b in range(64) if (int(wd) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        cpus = sorted(near & allowed)
+        if not cpus or len(cpus) == len(allowed):
+            return None
+        os.sched_setaffinity(0, cpus)
+        return cpus
+    except Exception:
+        return None
