@@ -276,6 +276,80 @@ wmedian_weight_grad_kernel(const float* __restrict__ flow, const float* __restri
     }
 }
 
+// Sliding-window variant of the weight-gradient kernel: a thread walks along kRun pixels of a row, keeps the window
+// in registers (one new column per pixel instead of K loads) and its per-tap sums in registers too.
+template <int KS>
+__global__ void __launch_bounds__(NT, 3)
+wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __restrict__ weights, const int* __restrict__ tap,
+                                 const float* __restrict__ alpha, const float* __restrict__ grad, double* __restrict__ partial,
+                                 long long nthreads, int H, int W, int runs) {
+    constexpr int K = KS * KS, R = KS / 2;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ float sp[K];
+    stage_weights<K>(weights, sp);
+    const long long plane = (long long)H * W;
+    float acc[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) acc[i] = 0.0f;
+    for (long long tix = (long long)blockIdx.x * NT + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * NT) {
+        const int h = (int)(tix % H);
+        const long long q = tix / H;
+        const int run = (int)(q % runs);
+        const long long img = q / runs;
+        const float* src = flow + img * plane;
+        const int w0 = run * kRun;
+        int rowoff[KS];
+#pragma unroll
+        for (int dy = 0; dy < KS; ++dy) rowoff[dy] = min(max(h + dy - R, 0), H - 1) * W;
+        float v[K];
+#pragma unroll
+        for (int dy = 0; dy < KS; ++dy)
+#pragma unroll
+            for (int dx = 0; dx < KS; ++dx) v[dy * KS + dx] = __ldg(src + rowoff[dy] + min(max(w0 + dx - R, 0), W - 1));
+        const int wend = min(w0 + kRun, W);
+        const long long base = img * plane + (long long)h * W;
+        // per-pixel operands are fetched one pixel ahead so that no load latency sits between two pixels
+        int t_n = tap[base + w0];
+        float g_n = grad[base + w0], a_n = alpha[base + w0];
+        for (int w = w0; w < wend; ++w) {
+            const int t = t_n;
+            const float g0 = g_n, al = a_n;
+            float nxt[KS];                                   // right column of the next pixel's window
+#pragma unroll
+            for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + min(w + 1 + R, W - 1));
+            if (w + 1 < wend) { t_n = tap[base + w + 1]; g_n = grad[base + w + 1]; a_n = alpha[base + w + 1]; }
+            const float pmid = t >= 0 ? sp[t] : 1.0f;
+            const float half = (float)((double)g0 / (2.0 * (double)pmid));
+            const float mid = __fdiv_rn(__fmul_rn(g0, al), -pmid);
+            float vsel = 0.0f;
+#pragma unroll
+            for (int i = 0; i < K; ++i) vsel = (i == t) ? v[i] : vsel;
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                // no crossing (t < 0): every bin counts as "before"
+                const bool before = t < 0 || v[i] < vsel || (v[i] == vsel && i < t);
+                acc[i] += before ? -half : ((i == t) ? mid : half);
+            }
+#pragma unroll
+            for (int dy = 0; dy < KS; ++dy) {
+#pragma unroll
+                for (int dx = 0; dx + 1 < KS; ++dx) v[dy * KS + dx] = v[dy * KS + dx + 1];
+                v[dy * KS + KS - 1] = nxt[dy];
+            }
+        }
+    }
+    float* sacc = reinterpret_cast<float*>(smem_raw) + threadIdx.x;            // sacc[i * NT]
+#pragma unroll
+    for (int i = 0; i < K; ++i) sacc[i * NT] = acc[i];
+    __syncthreads();
+    if (threadIdx.x < K) {
+        const float* row = reinterpret_cast<float*>(smem_raw) + (size_t)threadIdx.x * NT;
+        double s = 0.0;
+        for (int t = 0; t < NT; ++t) s += (double)row[t];
+        partial[(size_t)blockIdx.x * K + threadIdx.x] = s;
+    }
+}
+
 __global__ void __launch_bounds__(64)
 wmedian_weight_grad_final_kernel(const double* __restrict__ partial, int nblocks, int K, float* __restrict__ g_p) {
     const int i = threadIdx.x;
@@ -343,9 +417,19 @@ static int run_backward(const float* flow, const float* wts, const int* tap, con
     constexpr int K = KS * KS;
     const int smem = K * NT * (int)sizeof(float);
     CNL_TRY(ensure_dynamic_smem(wmedian_weight_grad_kernel<KS>, smem));
-    const int blocks = (int)std::min<long long>((total + NT - 1) / NT, kGradBlocks);
-    wmedian_weight_grad_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, tap, alpha, grad, scratch, total, H, W);
-    CNL_TRY(after_launch("wmedian_weight_grad_kernel"));
+    int blocks;
+    if (slide_enabled()) {
+        CNL_TRY(ensure_dynamic_smem(wmedian_weight_grad_slide_kernel<KS>, smem));
+        const int runs = (W + kRun - 1) / kRun;
+        const long long nthreads = total / W * runs;
+        blocks = (int)std::min<long long>((nthreads + NT - 1) / NT, kGradBlocks);
+        wmedian_weight_grad_slide_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, tap, alpha, grad, scratch, nthreads, H, W, runs);
+        CNL_TRY(after_launch("wmedian_weight_grad_slide_kernel"));
+    } else {
+        blocks = (int)std::min<long long>((total + NT - 1) / NT, kGradBlocks);
+        wmedian_weight_grad_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, tap, alpha, grad, scratch, total, H, W);
+        CNL_TRY(after_launch("wmedian_weight_grad_kernel"));
+    }
     wmedian_weight_grad_final_kernel<<<1, 64, 0, st>>>(scratch, blocks, K, g_p);
     CNL_TRY(after_launch("wmedian_weight_grad_final_kernel"));
     wmedian_input_grad_kernel<KS><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(tap, grad, g_flow, total, H, W);
