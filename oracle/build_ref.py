@@ -1,17 +1,17 @@
-"""Recipe that compiles the reference's own CUDA kernels (unmodified, from /root/reference) against the small
-ImageUtilities stand-in in oracle/iu_shim into shared libraries under oracle/_ref/ (libtvref.so, libmedianref.so, ...).  TEST INFRASTRUCTURE ONLY.
+"""Recipe that compiles the reference's own CUDA kernels (unmodified, from where the reference checkout lies:
+environment variable CNL_REFERENCE_ROOT, else the default location below) against the small ImageUtilities stand-in in oracle/iu_shim into shared libraries under oracle/_ref/ (libtvref.so, libmedianref.so, ...).  TEST INFRASTRUCTURE ONLY.
 
     python oracle/build_ref.py
 
-The output is git-ignored; it travels to the GPU box with the working tree.  Without /root/reference (e.g. on the
-GPU box) nothing is built and the prebuilt file, if any, is used as is.
+The output is git-ignored; it travels with the working tree to machines that have a GPU.  Where the reference
+checkout is absent nothing is built and the prebuilt file, if any, is used as is.
 """
 import os
 import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = "/root/reference"
+REF_ROOT = os.environ.get("CNL_REFERENCE_ROOT", "/root/reference")
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "libtvref.so")
 # output library -> (wrapper source, reference source directory)

@@ -1,8 +1,8 @@
 """Generates tests/golden/tv_reference_cuda.npz: inputs and outputs of the REFERENCE's own cudaTV kernels
 (oracle/_ref/libtvref.so, built unmodified by oracle/build_ref.py) on a few small problems.  Needs a GPU:
 
-    python tests/golden/make_golden.py gpurun_out [tv] [median] ...          # on the GPU box
-    cp gpurun_out/*_reference_cuda.npz tests/golden/                         # back in the working tree
+    python tests/golden/make_golden.py <out_dir> [tv] [median] ...           # on a machine with a GPU
+    cp <out_dir>/*_reference_cuda.npz tests/golden/                          # back in the working tree
 
 The committed file pins the CPU oracle (tests/test_golden.py, no GPU needed) and the CUDA path."""
 import os
