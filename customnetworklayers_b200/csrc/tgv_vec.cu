@@ -372,6 +372,104 @@ __device__ __forceinline__ RowState load_row(const RevVecParams& p, size_t o, si
     return r;
 }
 
+
+// Adjoint fluxes of the lane's four triangles (kept for the divergence) and their edge-weight gradients.
+struct RevFlux {
+    float P1[4], P2[4], C1x[4], C1y[4], C2x[4], C2y[4], C2d[4];      // psi1, psi2, chi1x, chi1y, chi2x, chi2y, down-going chi2y
+    float gu[4], g1[4], g2[4];                                        // incoming adjoint of the lane's own pixels
+};
+__device__ __forceinline__ void rev_adjoint_fluxes(const RowState& own, const RowState& below, const Weights& w, const Geom& g,
+                                                   int typo, RevFlux& f, float4 (&gw_out)[4]) {
+    float yu[5], y1[5], y2[5], gu[5], g1[5], g2[5], du[4], d1[4], d2[4], eu[4], e1[4], e2[4];
+    {
+        float a[4];
+        unpack(own.yu, a); for (int k = 0; k < 4; ++k) yu[k] = a[k];
+        unpack(own.y1, a); for (int k = 0; k < 4; ++k) y1[k] = a[k];
+        unpack(own.y2, a); for (int k = 0; k < 4; ++k) y2[k] = a[k];
+        unpack(own.gu, a); for (int k = 0; k < 4; ++k) gu[k] = a[k];
+        unpack(own.g1, a); for (int k = 0; k < 4; ++k) g1[k] = a[k];
+        unpack(own.g2, a); for (int k = 0; k < 4; ++k) g2[k] = a[k];
+    }
+    unpack(below.yu, du); unpack(below.y1, d1); unpack(below.y2, d2);
+    unpack(below.gu, eu); unpack(below.g1, e1); unpack(below.g2, e2);
+    yu[4] = __shfl_down_sync(kFull, own.yu.x, 1); y1[4] = __shfl_down_sync(kFull, own.y1.x, 1); y2[4] = __shfl_down_sync(kFull, own.y2.x, 1);
+    gu[4] = __shfl_down_sync(kFull, own.gu.x, 1); g1[4] = __shfl_down_sync(kFull, own.g1.x, 1); g2[4] = __shfl_down_sync(kFull, own.g2.x, 1);
+    float gw0[4], gw1[4], gw2[4], gw3[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const TriQ tr = tri_quantities(yu[k], yu[k + 1], du[k], y1[k], y1[k + 1], d1[k], y2[k], y2[k + 1], d2[k],
+                                       w.wx[k], w.wy[k], w.b0[k], w.b1[k], g.mx[k], g.my);
+        const float Ex = gu[k] - gu[k + 1] + g1[k];
+        const float Ey = gu[k] - eu[k] + g2[k];
+        const float a1 = tr.z1 * w.wx[k], a2 = tr.z2 * w.wy[k];
+        const float S = a1 * Ex + a2 * Ey;
+        const float dW = tr.Hu < 1.f ? tr.Hu * tr.r_u * tr.r_u : 0.f;
+        f.P1[k] = w.wx[k] * tr.Hu * Ex - dW * a1 * S;
+        f.P2[k] = w.wy[k] * tr.Hu * Ey - dW * a2 * S;
+        gw0[k] = kLocalGX * (Ex * tr.z1 * tr.Hu - 0.5f * tr.z1 * tr.z1 * dW * S);
+        gw2[k] = kLocalGX * (Ey * tr.z2 * tr.Hu - 0.5f * tr.z2 * tr.z2 * dW * S);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float gc = j == 0 ? g1[k] : g2[k], gr = j == 0 ? g1[k + 1] : g2[k + 1], gd = j == 0 ? e1[k] : e2[k];
+            const float E1 = g.mx[k] ? gc - gr : 0.f;
+            const float E2 = g.my ? gc - gd : 0.f;
+            const float b1 = tr.a1[j], b2 = tr.a2[j], beta = j == 0 ? w.b0[k] : w.b1[k], Hj = tr.H[j];
+            const float Sj = b1 * E1 + b2 * E2;
+            const bool act = Hj < 1.f;
+            const float dWj = act ? Hj * tr.r[j] * tr.r[j] : 0.f;
+            const float chx = beta * (Hj * E1 - dWj * beta * b1 * Sj);
+            const float chy = beta * (Hj * E2 - dWj * beta * b2 * Sj);
+            const float gbeta = kLocalGX * (Sj * Hj - 0.5f * (b1 * b1 + b2 * b2) * dWj * beta * Sj);
+            if (j == 0) { f.C1x[k] = chx; f.C1y[k] = chy; gw1[k] = gbeta; }
+            else {
+                f.C2x[k] = chx; f.C2y[k] = chy; gw3[k] = gbeta;
+                float down = chy;
+                if (typo && act) down = beta * (Hj * E2 - (Hj * beta * (b1 * b1 + b2 * b2)) * beta * b2 * Sj);
+                f.C2d[k] = down;
+            }
+        }
+        f.gu[k] = gu[k]; f.g1[k] = g1[k]; f.g2[k] = g2[k];
+    }
+    gw_out[0] = pack(gw0); gw_out[1] = pack(gw1); gw_out[2] = pack(gw2); gw_out[3] = pack(gw3);
+}
+
+// Divergence of the adjoint fluxes, momentum reverse and prox Jacobian for the lane's four pixels.
+struct RevOut {
+    float4 xb0, xb1, xb2;      // dL/dx of this iteration (u, v1, v2)
+    float4 na0, na1, na2;      // new pending momentum terms
+    float4 go;                 // dL/dx^{g-1/2}, primary plane
+    float4 dgc, dgb;           // confidence and data-term gradient contributions
+};
+__device__ __forceinline__ void rev_divergence_and_prox(const RevFlux& f, const float4& P2a4, const float4& C1ya4, const float4& C2da4,
+                                                        const float4& au4, const float4& a14, const float4& a24, const float4& hu4,
+                                                        const float4& b4, const float4& c4, float t, RevOut& r) {
+    float P2a[4], C1ya[4], C2da[4], au[4], a1v[4], a2v[4], hu[4], bq[4], cq[4];
+    unpack(P2a4, P2a); unpack(C1ya4, C1ya); unpack(C2da4, C2da);
+    unpack(au4, au); unpack(a14, a1v); unpack(a24, a2v); unpack(hu4, hu); unpack(b4, bq); unpack(c4, cq);
+    const float P1l = __shfl_up_sync(kFull, f.P1[3], 1);
+    const float C1xl = __shfl_up_sync(kFull, f.C1x[3], 1);
+    const float C2xl = __shfl_up_sync(kFull, f.C2x[3], 1);
+    float xb0[4], xb1[4], xb2[4], na0[4], na1[4], na2[4], go[4], dgc[4], dgb[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float P1_l = k == 0 ? P1l : f.P1[k - 1];
+        const float C1x_l = k == 0 ? C1xl : f.C1x[k - 1];
+        const float C2x_l = k == 0 ? C2xl : f.C2x[k - 1];
+        const float yb0 = f.gu[k] - f.P1[k] - f.P2[k] + P1_l + P2a[k];
+        const float yb1 = f.g1[k] - f.P1[k] - f.C1x[k] - f.C1y[k] + C1x_l + C1ya[k];
+        const float yb2 = f.g2[k] - f.P2[k] - f.C2x[k] - f.C2y[k] + C2x_l + C2da[k];
+        xb0[k] = clampf(au[k] + (1.0f + t) * yb0, -kClip, kClip);
+        xb1[k] = clampf(a1v[k] + (1.0f + t) * yb1, -kClip, kClip);
+        xb2[k] = clampf(a2v[k] + (1.0f + t) * yb2, -kClip, kClip);
+        na0[k] = -t * yb0; na1[k] = -t * yb1; na2[k] = -t * yb2;
+        dgc[k] = 0.f; dgb[k] = 0.f;
+        go[k] = prox_reverse_fast(xb0[k], hu[k], bq[k], cq[k], rcp_approx(1.0f + cq[k]), dgc[k], dgb[k]);
+    }
+    r.xb0 = pack(xb0); r.xb1 = pack(xb1); r.xb2 = pack(xb2);
+    r.na0 = pack(na0); r.na1 = pack(na1); r.na2 = pack(na2);
+    r.go = pack(go); r.dgc = pack(dgc); r.dgb = pack(dgb);
+}
+
 }  // namespace
 
 __global__ void __launch_bounds__(kNT, 2)
@@ -409,105 +507,206 @@ tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
             below.yu = sh_row[0][g.warp + 1][g.lane]; below.y1 = sh_row[1][g.warp + 1][g.lane]; below.y2 = sh_row[2][g.warp + 1][g.lane];
             below.gu = sh_row[3][g.warp + 1][g.lane]; below.g1 = sh_row[4][g.warp + 1][g.lane]; below.g2 = sh_row[5][g.warp + 1][g.lane];
         }
-        float yu[5], y1[5], y2[5], gu[5], g1[5], g2[5], du[4], d1[4], d2[4], eu[4], e1[4], e2[4];
-        {
-            float a[4];
-            unpack(own.yu, a); for (int k = 0; k < 4; ++k) yu[k] = a[k];
-            unpack(own.y1, a); for (int k = 0; k < 4; ++k) y1[k] = a[k];
-            unpack(own.y2, a); for (int k = 0; k < 4; ++k) y2[k] = a[k];
-            unpack(own.gu, a); for (int k = 0; k < 4; ++k) gu[k] = a[k];
-            unpack(own.g1, a); for (int k = 0; k < 4; ++k) g1[k] = a[k];
-            unpack(own.g2, a); for (int k = 0; k < 4; ++k) g2[k] = a[k];
-        }
-        unpack(below.yu, du); unpack(below.y1, d1); unpack(below.y2, d2);
-        unpack(below.gu, eu); unpack(below.g1, e1); unpack(below.g2, e2);
-        yu[4] = __shfl_down_sync(kFull, own.yu.x, 1); y1[4] = __shfl_down_sync(kFull, own.y1.x, 1); y2[4] = __shfl_down_sync(kFull, own.y2.x, 1);
-        gu[4] = __shfl_down_sync(kFull, own.gu.x, 1); g1[4] = __shfl_down_sync(kFull, own.g1.x, 1); g2[4] = __shfl_down_sync(kFull, own.g2.x, 1);
-        // adjoint fluxes of the lane's four triangles and their edge-weight gradients
-        float P1[4], P2[4], C1x[4], C1y[4], C2x[4], C2y[4], C2d[4], gw0[4], gw1[4], gw2[4], gw3[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const TriQ tr = tri_quantities(yu[k], yu[k + 1], du[k], y1[k], y1[k + 1], d1[k], y2[k], y2[k + 1], d2[k],
-                                           w.wx[k], w.wy[k], w.b0[k], w.b1[k], g.mx[k], g.my);
-            const float Ex = gu[k] - gu[k + 1] + g1[k];
-            const float Ey = gu[k] - eu[k] + g2[k];
-            const float a1 = tr.z1 * w.wx[k], a2 = tr.z2 * w.wy[k];
-            const float S = a1 * Ex + a2 * Ey;
-            const float dW = tr.Hu < 1.f ? tr.Hu * tr.r_u * tr.r_u : 0.f;
-            P1[k] = w.wx[k] * tr.Hu * Ex - dW * a1 * S;
-            P2[k] = w.wy[k] * tr.Hu * Ey - dW * a2 * S;
-            gw0[k] = kLocalGX * (Ex * tr.z1 * tr.Hu - 0.5f * tr.z1 * tr.z1 * dW * S);
-            gw2[k] = kLocalGX * (Ey * tr.z2 * tr.Hu - 0.5f * tr.z2 * tr.z2 * dW * S);
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const float gc = j == 0 ? g1[k] : g2[k], gr = j == 0 ? g1[k + 1] : g2[k + 1], gd = j == 0 ? e1[k] : e2[k];
-                const float E1 = g.mx[k] ? gc - gr : 0.f;
-                const float E2 = g.my ? gc - gd : 0.f;
-                const float b1 = tr.a1[j], b2 = tr.a2[j], beta = j == 0 ? w.b0[k] : w.b1[k], Hj = tr.H[j];
-                const float Sj = b1 * E1 + b2 * E2;
-                const bool act = Hj < 1.f;
-                const float dWj = act ? Hj * tr.r[j] * tr.r[j] : 0.f;
-                const float chx = beta * (Hj * E1 - dWj * beta * b1 * Sj);
-                const float chy = beta * (Hj * E2 - dWj * beta * b2 * Sj);
-                const float gbeta = kLocalGX * (Sj * Hj - 0.5f * (b1 * b1 + b2 * b2) * dWj * beta * Sj);
-                if (j == 0) { C1x[k] = chx; C1y[k] = chy; gw1[k] = gbeta; }
-                else {
-                    C2x[k] = chx; C2y[k] = chy; gw3[k] = gbeta;
-                    float down = chy;
-                    if (p.typo && act) down = beta * (Hj * E2 - (Hj * beta * (b1 * b1 + b2 * b2)) * beta * b2 * Sj);
-                    C2d[k] = down;
-                }
-            }
-        }
-        sh_flux[0][g.warp][g.lane] = pack(P2);
-        sh_flux[1][g.warp][g.lane] = pack(C1y);
-        sh_flux[2][g.warp][g.lane] = pack(C2d);
+        RevFlux f;
+        float4 gw[4];
+        rev_adjoint_fluxes(own, below, w, g, p.typo, f, gw);
+        sh_flux[0][g.warp][g.lane] = pack(f.P2);
+        sh_flux[1][g.warp][g.lane] = pack(f.C1y);
+        sh_flux[2][g.warp][g.lane] = pack(f.C2d);
         if (g.store) {      // every triangle's weight gradient is accumulated by the pixel that anchors it
-            red_add4(p.g_dx + (n * 2 + 0) * plane + g.pix, pack(gw0));
-            red_add4(p.g_dx + (n * 2 + 1) * plane + g.pix, pack(gw1));
-            red_add4(p.g_dy + (n * 2 + 0) * plane + g.pix, pack(gw2));
-            red_add4(p.g_dy + (n * 2 + 1) * plane + g.pix, pack(gw3));
+            red_add4(p.g_dx + (n * 2 + 0) * plane + g.pix, gw[0]);
+            red_add4(p.g_dx + (n * 2 + 1) * plane + g.pix, gw[1]);
+            red_add4(p.g_dy + (n * 2 + 0) * plane + g.pix, gw[2]);
+            red_add4(p.g_dy + (n * 2 + 1) * plane + g.pix, gw[3]);
         }
         __syncthreads();
-        float P2a[4], C1ya[4], C2da[4];
-        unpack(g.warp > 0 ? sh_flux[0][g.warp - 1][g.lane] : zero4(), P2a);
-        unpack(g.warp > 0 ? sh_flux[1][g.warp - 1][g.lane] : zero4(), C1ya);
-        unpack(g.warp > 0 ? sh_flux[2][g.warp - 1][g.lane] : zero4(), C2da);
-        const float P1l = __shfl_up_sync(kFull, P1[3], 1);
-        const float C1xl = __shfl_up_sync(kFull, C1x[3], 1);
-        const float C2xl = __shfl_up_sync(kFull, C2x[3], 1);
-        float au[4], a1v[4], a2v[4], hu[4], bq[4], cq[4];
+        const float4 P2a = g.warp > 0 ? sh_flux[0][g.warp - 1][g.lane] : zero4();
+        const float4 C1ya = g.warp > 0 ? sh_flux[1][g.warp - 1][g.lane] : zero4();
+        const float4 C2da = g.warp > 0 ? sh_flux[2][g.warp - 1][g.lane] : zero4();
         cp_async_wait_all();
-        unpack(slot[0 * kNT], hu); unpack(slot[1 * kNT], bq); unpack(slot[2 * kNT], cq);
-        unpack(slot[3 * kNT], au); unpack(slot[4 * kNT], a1v); unpack(slot[5 * kNT], a2v);
-        float xb0[4], xb1[4], xb2[4], na0[4], na1[4], na2[4], go[4], dgc[4], dgb[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float P1_l = k == 0 ? P1l : P1[k - 1];
-            const float C1x_l = k == 0 ? C1xl : C1x[k - 1];
-            const float C2x_l = k == 0 ? C2xl : C2x[k - 1];
-            const float yb0 = gu[k] - P1[k] - P2[k] + P1_l + P2a[k];
-            const float yb1 = g1[k] - P1[k] - C1x[k] - C1y[k] + C1x_l + C1ya[k];
-            const float yb2 = g2[k] - P2[k] - C2x[k] - C2y[k] + C2x_l + C2da[k];
-            xb0[k] = clampf(au[k] + (1.0f + p.t) * yb0, -kClip, kClip);
-            xb1[k] = clampf(a1v[k] + (1.0f + p.t) * yb1, -kClip, kClip);
-            xb2[k] = clampf(a2v[k] + (1.0f + p.t) * yb2, -kClip, kClip);
-            na0[k] = -p.t * yb0; na1[k] = -p.t * yb1; na2[k] = -p.t * yb2;
-            dgc[k] = 0.f; dgb[k] = 0.f;
-            go[k] = prox_reverse_fast(xb0[k], hu[k], bq[k], cq[k], rcp_approx(1.0f + cq[k]), dgc[k], dgb[k]);
-        }
+        RevOut r;
+        rev_divergence_and_prox(f, P2a, C1ya, C2da, slot[3 * kNT], slot[4 * kNT], slot[5 * kNT], slot[0 * kNT], slot[1 * kNT],
+                                slot[2 * kNT], p.t, r);
         if (g.store) {
-            st4(p.acc + o, pack(na0)); st4(p.acc + o + cstride, pack(na1)); st4(p.acc + o + 2 * cstride, pack(na2));
-            if (p.x1bar) { st4(p.x1bar + o, pack(xb0)); st4(p.x1bar + o + cstride, pack(xb1)); st4(p.x1bar + o + 2 * cstride, pack(xb2)); }
-            st4(p.g_out + o, pack(go)); st4(p.g_out + o + cstride, pack(xb1)); st4(p.g_out + o + 2 * cstride, pack(xb2));
-            red_add4(p.g_b + ob, pack(dgb));
-            red_add4(p.g_c + oc, pack(dgc));
+            st4(p.acc + o, r.na0); st4(p.acc + o + cstride, r.na1); st4(p.acc + o + 2 * cstride, r.na2);
+            if (p.x1bar) { st4(p.x1bar + o, r.xb0); st4(p.x1bar + o + cstride, r.xb1); st4(p.x1bar + o + 2 * cstride, r.xb2); }
+            st4(p.g_out + o, r.go); st4(p.g_out + o + cstride, r.xb1); st4(p.g_out + o + 2 * cstride, r.xb2);
+            red_add4(p.g_b + ob, r.dgb);
+            red_add4(p.g_c + oc, r.dgc);
         }
     }
 }
 
+// Tiles a launch must have before the persistent kernel is used; CNL_TGV_PIPELINE_MIN_TILES overrides the default
+// (read at every call so that tests can force either kernel; a negative value disables the persistent kernel).
+static long long pipeline_min_tiles(int sms) {
+    const char* e = std::getenv("CNL_TGV_PIPELINE_MIN_TILES");
+    if (e && e[0]) { const long long v = std::atoll(e); return v < 0 ? (1ll << 40) : v; }
+    return 16LL * sms;
+}
+
+// Same for the reverse kernel (CNL_TGV_REV_PIPELINE_MIN_TILES).
+static long long rev_pipeline_min_tiles(int sms) {
+    const char* e = std::getenv("CNL_TGV_REV_PIPELINE_MIN_TILES");
+    if (e && e[0]) { const long long v = std::atoll(e); return v < 0 ? (1ll << 40) : v; }
+    return 16LL * sms;
+}
+
+// Persistent, software-pipelined reverse iteration (same scheme as tgv_fwd_pipe_kernel): every operand plane of the
+// next (tile, channel) item lands in shared memory while the current item is finished.  The rows of y and of the
+// incoming adjoint arrive raw; each warp rebuilds u of y for its own row and for the row below it from the raw
+// iterates (a few redundant flops instead of a second exchange and barrier).
+constexpr int kRevPipeSmemBytes = (23 * kNT + 9 * 32) * (int)sizeof(float4);
+
+__global__ void __launch_bounds__(kNT, 2)
+tgv_rev_pipe_kernel(const __grid_constant__ RevVecParams p, int tiles_x, int tiles_y) {
+    extern __shared__ float4 rp_smem[];
+    typedef float4 (*Rows)[kTgvWarps][32];
+    float4(*ex)[3][kTgvWarps][32] = reinterpret_cast<float4(*)[3][kTgvWarps][32]>(rp_smem);     // [2]: flux exchange
+    Rows sy = reinterpret_cast<Rows>(rp_smem + 6 * kNT);       // [3] raw y source rows (checkpoint or stored iterate g)
+    Rows sg = reinterpret_cast<Rows>(rp_smem + 9 * kNT);       // [3] incoming adjoint rows
+    Rows sq = reinterpret_cast<Rows>(rp_smem + 12 * kNT);      // [3] stored iterate g-1 (u), b, c rows
+    float4* sacc = rp_smem + 15 * kNT + threadIdx.x;           // [3][kNT] pending momentum of the lane's own pixels
+    float4* shu = rp_smem + 18 * kNT + threadIdx.x;            // [kNT] x^{g+1/2} (u) when y comes from a checkpoint
+    float4* sw = rp_smem + 19 * kNT + threadIdx.x;             // [4][kNT] edge weights of the tile
+    float4(*sbelow)[32] = reinterpret_cast<float4(*)[32]>(rp_smem + 23 * kNT);                   // [9] row under the region
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t plane = (size_t)p.H * p.W;
+    const size_t cstride = (size_t)p.C * plane;
+    const int ntiles = tiles_x * tiles_y * p.N;
+    const float* ysrc = p.ckpt ? p.ckpt : p.hist_g;
+    const bool rebuild = p.ckpt == nullptr;
+
+    auto tile_geom = [&](int tile, size_t& n) -> Geom {
+        const int tx = tile % tiles_x, q = tile / tiles_x;
+        n = (size_t)(q / tiles_y);
+        return make_geom_at(tx, q % tiles_y, p.H, p.W);
+    };
+    auto issue = [&](int tile, int ch) {
+        if (tile < ntiles) {
+            size_t n;
+            const Geom g = tile_geom(tile, n);
+            const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
+            const size_t ob = (n * p.C + ch) * plane + g.pix, oc = n * plane + g.pix;
+            const bool last = warp == kTgvWarps - 1;
+            const size_t dn = g.okb ? (size_t)p.W : 0;         // one image row further down
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                cp_async16(&sy[q][warp][lane], ysrc + o + q * cstride, g.ok);
+                cp_async16(&sg[q][warp][lane], p.g_in + o + q * cstride, g.ok);
+                cp_async16(sacc + q * kNT, p.acc + o + q * cstride, g.store);
+                if (last) {
+                    cp_async16(&sbelow[q][lane], ysrc + o + q * cstride + dn, g.okb);
+                    cp_async16(&sbelow[3 + q][lane], p.g_in + o + q * cstride + dn, g.okb);
+                }
+            }
+            const bool hm_ok = rebuild && p.hist_gm1 != nullptr;
+            cp_async16(&sq[0][warp][lane], hm_ok ? p.hist_gm1 + o : p.b, g.ok && hm_ok);
+            cp_async16(&sq[1][warp][lane], p.b + ob, g.ok);
+            cp_async16(&sq[2][warp][lane], p.c + oc, g.ok);
+            if (last) {
+                cp_async16(&sbelow[6][lane], hm_ok ? p.hist_gm1 + o + dn : p.b, g.okb && hm_ok);
+                cp_async16(&sbelow[7][lane], p.b + ob + dn, g.okb);
+                cp_async16(&sbelow[8][lane], p.c + oc + dn, g.okb);
+            }
+            if (!rebuild) cp_async16(shu, p.hist_g + o, g.store);
+            if (ch == 0) {
+                cp_async16(sw + 0 * kNT, p.dx + (n * 2 + 0) * plane + g.pix, g.ok);
+                cp_async16(sw + 1 * kNT, p.dy + (n * 2 + 0) * plane + g.pix, g.ok);
+                cp_async16(sw + 2 * kNT, p.dx + (n * 2 + 1) * plane + g.pix, g.ok);
+                cp_async16(sw + 3 * kNT, p.dy + (n * 2 + 1) * plane + g.pix, g.ok);
+            }
+        }
+        cp_async_commit();
+    };
+    // y and adjoint of one row from its raw planes
+    auto make_row = [&](const float4& ru, const float4& r1, const float4& r2, const float4& qu, const float4& q1, const float4& q2,
+                        const float4& hm, const float4& b, const float4& c, bool ok) -> RowState {
+        RowState r;
+        r.yu = ru; r.y1 = r1; r.y2 = r2; r.gu = qu; r.g1 = q1; r.g2 = q2;
+        if (rebuild && ok) {
+            r.yu.x = rederive_y_fast(ru.x, hm.x, b.x, c.x, rcp_approx(1.0f + c.x), p.t);
+            r.yu.y = rederive_y_fast(ru.y, hm.y, b.y, c.y, rcp_approx(1.0f + c.y), p.t);
+            r.yu.z = rederive_y_fast(ru.z, hm.z, b.z, c.z, rcp_approx(1.0f + c.z), p.t);
+            r.yu.w = rederive_y_fast(ru.w, hm.w, b.w, c.w, rcp_approx(1.0f + c.w), p.t);
+        }
+        return r;
+    };
+
+    int tile = blockIdx.x;
+    if (tile >= ntiles) return;
+    issue(tile, 0);
+    int parity = 0;
+    for (; tile < ntiles; tile += gridDim.x) {
+        size_t n;
+        const Geom g = tile_geom(tile, n);
+        const float L = p.L[n];
+        const size_t oc = n * plane + g.pix;
+        Weights w;
+        for (int ch = 0; ch < p.C; ++ch, parity ^= 1) {
+            const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
+            const size_t ob = (n * p.C + ch) * plane + g.pix;
+            cp_async_wait_all();
+            __syncthreads();                                  // every thread's operands of this item have landed
+            if (ch == 0) w = scale_weights(sw[0 * kNT], sw[1 * kNT], sw[2 * kNT], sw[3 * kNT], g, L);
+            const RowState own = make_row(sy[0][warp][lane], sy[1][warp][lane], sy[2][warp][lane], sg[0][warp][lane], sg[1][warp][lane],
+                                          sg[2][warp][lane], sq[0][warp][lane], sq[1][warp][lane], sq[2][warp][lane], g.ok);
+            RowState below;
+            if (warp < kTgvWarps - 1)
+                below = make_row(sy[0][warp + 1][lane], sy[1][warp + 1][lane], sy[2][warp + 1][lane], sg[0][warp + 1][lane],
+                                 sg[1][warp + 1][lane], sg[2][warp + 1][lane], sq[0][warp + 1][lane], sq[1][warp + 1][lane],
+                                 sq[2][warp + 1][lane], g.okb);
+            else
+                below = make_row(sbelow[0][lane], sbelow[1][lane], sbelow[2][lane], sbelow[3][lane], sbelow[4][lane], sbelow[5][lane],
+                                 sbelow[6][lane], sbelow[7][lane], sbelow[8][lane], g.okb);
+            RevFlux f;
+            float4 gw[4];
+            rev_adjoint_fluxes(own, below, w, g, p.typo, f, gw);
+            ex[parity][0][warp][lane] = pack(f.P2);
+            ex[parity][1][warp][lane] = pack(f.C1y);
+            ex[parity][2][warp][lane] = pack(f.C2d);
+            if (g.store) {
+                red_add4(p.g_dx + (n * 2 + 0) * plane + g.pix, gw[0]);
+                red_add4(p.g_dx + (n * 2 + 1) * plane + g.pix, gw[1]);
+                red_add4(p.g_dy + (n * 2 + 0) * plane + g.pix, gw[2]);
+                red_add4(p.g_dy + (n * 2 + 1) * plane + g.pix, gw[3]);
+            }
+            __syncthreads();                                  // fluxes published; all reads of the raw rows are done
+            const float4 au4 = sacc[0 * kNT], a14 = sacc[1 * kNT], a24 = sacc[2 * kNT];
+            const float4 hu4 = rebuild ? sy[0][warp][lane] : shu[0];
+            const float4 b4 = sq[1][warp][lane], c4 = sq[2][warp][lane];
+            // every landing slot is free again: start fetching the next item
+            if (ch + 1 < p.C) issue(tile, ch + 1);
+            else issue(tile + gridDim.x, 0);
+            const float4 P2a = warp > 0 ? ex[parity][0][warp - 1][lane] : zero4();
+            const float4 C1ya = warp > 0 ? ex[parity][1][warp - 1][lane] : zero4();
+            const float4 C2da = warp > 0 ? ex[parity][2][warp - 1][lane] : zero4();
+            RevOut r;
+            rev_divergence_and_prox(f, P2a, C1ya, C2da, au4, a14, a24, hu4, b4, c4, p.t, r);
+            if (g.store) {
+                st4(p.acc + o, r.na0); st4(p.acc + o + cstride, r.na1); st4(p.acc + o + 2 * cstride, r.na2);
+                if (p.x1bar) { st4(p.x1bar + o, r.xb0); st4(p.x1bar + o + cstride, r.xb1); st4(p.x1bar + o + 2 * cstride, r.xb2); }
+                st4(p.g_out + o, r.go); st4(p.g_out + o + cstride, r.xb1); st4(p.g_out + o + 2 * cstride, r.xb2);
+                red_add4(p.g_b + ob, r.dgb);
+                red_add4(p.g_c + oc, r.dgc);
+            }
+        }
+    }
+    cp_async_wait_all();
+}
+
+
 int launch_tgv_rev_vec(const RevVecParams& p, cudaStream_t st) {
     const dim3 grid((p.W + kTgvTileW - 1) / kTgvTileW, (p.H + kTgvTileH - 1) / kTgvTileH, p.N);
+    const long long ntiles = (long long)grid.x * grid.y * grid.z;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if (ntiles >= rev_pipeline_min_tiles(sms) && ntiles < (1ll << 30)) {
+        CNL_TRY(ensure_dynamic_smem(tgv_rev_pipe_kernel, kRevPipeSmemBytes));
+        const unsigned ctas = (unsigned)std::min<long long>(ntiles, 2LL * sms);
+        tgv_rev_pipe_kernel<<<ctas, kNT, kRevPipeSmemBytes, st>>>(p, (int)grid.x, (int)grid.y);
+        return after_launch("tgv_rev_pipe_kernel");
+    }
     constexpr int smem_bytes = 15 * kNT * (int)sizeof(float4);
     CNL_TRY(ensure_dynamic_smem(tgv_rev_vec_kernel, smem_bytes));
     tgv_rev_vec_kernel<<<grid, kNT, smem_bytes, st>>>(p);
@@ -519,14 +718,6 @@ bool tgv_vec_supported(int W, const void* const* ptrs, int nptr) {
     for (int i = 0; i < nptr; ++i)
         if ((reinterpret_cast<size_t>(ptrs[i]) & 15) != 0) return false;
     return true;
-}
-
-// Tiles a launch must have before the persistent kernel is used; CNL_TGV_PIPELINE_MIN_TILES overrides the default
-// (read at every call so that tests can force either kernel; a negative value disables the persistent kernel).
-static long long pipeline_min_tiles(int sms) {
-    const char* e = std::getenv("CNL_TGV_PIPELINE_MIN_TILES");
-    if (e && e[0]) { const long long v = std::atoll(e); return v < 0 ? (1ll << 40) : v; }
-    return 16LL * sms;
 }
 
 int launch_tgv_fwd_vec(const FwdVecParams& p, cudaStream_t st) {

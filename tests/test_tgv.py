@@ -131,10 +131,11 @@ def test_cuda_forward_history_and_reverse_sweep_match_oracle(case):
 @pytest.mark.gpu
 @pytest.mark.parametrize("case", [(2, 2, 40, 72, 20), (2, 3, 9, 124, 5), (1, 1, 15, 244, 6), (3, 1, 23, 128, 9)],
                          ids=lambda c: "n%d_c%d_%dx%d_its%d" % c)
-def test_persistent_forward_kernel_matches_oracle(case, monkeypatch):
-    """The persistent, pipelined forward kernel normally serves launches of thousands of tiles; forced here."""
+def test_persistent_kernels_match_oracle(case, monkeypatch):
+    """The persistent, pipelined kernels normally serve launches of thousands of tiles; forced here."""
     from customnetworklayers_b200 import tgvInpaint_cuda_ext as ext
     monkeypatch.setenv("CNL_TGV_PIPELINE_MIN_TILES", "1")
+    monkeypatch.setenv("CNL_TGV_REV_PIPELINE_MIN_TILES", "1")
     n, ch, h, w, its = case
     I = make_tgv_inputs(n, ch, h, w, seed=11 + h + w)
     I["init"][:, 1:] = 0.1 * I["grad"][:, 1:]
@@ -146,9 +147,15 @@ def test_persistent_forward_kernel_matches_oracle(case, monkeypatch):
     assert_close(sol, r_sol, "solution")
     assert_close(hist, r_hist, "history")
     assert_close(cky, r_cky, "checkpoints")
+    ref = G.tgv_backward(I["dx"], I["dy"], I["c"], I["b"], I["grad"], its, hist.cpu(), cky.cpu())
+    for name, g, r in zip(NAMES, grads, ref):
+        assert_close(g, r, name)
     monkeypatch.setenv("CNL_TGV_PIPELINE_MIN_TILES", "-1")
-    sol2 = _run_cuda(ext, D, its, 3, n, ch, h, w)[0]
+    monkeypatch.setenv("CNL_TGV_REV_PIPELINE_MIN_TILES", "-1")
+    sol2, _, _, _, grads2 = _run_cuda(ext, D, its, 3, n, ch, h, w)
     assert torch.equal(sol, sol2), "both forward kernels do the same arithmetic"
+    for name, a, b in zip(NAMES, grads, grads2):
+        assert torch.equal(a, b), name + ": both reverse kernels do the same arithmetic"
 
 
 @pytest.mark.gpu
