@@ -32,6 +32,8 @@ WORKLOADS = {
     "cfg2": (8, 2, 436, 1024, 100),      # TGV-FISTA (secondary workload, run with --workload cfg2)
     "cfg2small": (2, 2, 436, 1024, 10),  # TGV profiling case
     "cfg4": (32, 2, 384, 1280, 0),        # learnable 7x7 weighted-median filter (no iterations)
+    "median": (4, 49, 384, 1280, 0),      # the reference's selection layer on a materialised [N,H,W,K] weight volume
+    "quadfit": (4, 32, 384, 1280, 0),     # the reference's quadratic fit on two feature maps and a flow
     "cfg3": (16, 2, 512, 960, 50),       # coarse-to-fine stack of three TV layers (ids 0,1,2) with quadratic-fit refinement
 }
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -599,6 +601,60 @@ def run_wmedian(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_layer_micro(args, rank, local_rank, world):
+    """Micro workloads for the two remaining reference layers, through their extension modules: `median` (selection on
+    a materialised [N,H,W,K] volume, (3K+4)*4 B per problem fwd+bwd) and `quadfit` (features + flow API,
+    (7C+10)*4 B per pixel fwd+bwd: forward reads both feature maps once and the flow, writes 3 planes; backward
+    reads them again with the upstream gradient, zero-fills and writes both feature gradients).  One GPU each."""
+    import torch
+    from customnetworklayers_b200 import _lib
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    nb, k, h, w, _ = WORKLOADS[args.workload]
+    if args.workload == "median":
+        from customnetworklayers_b200 import median_cuda_ext as ext
+        from customnetworklayers_b200.synthetic import make_median_volume
+        vol, grad = make_median_volume(nb, h, w, k, seed=1238 + rank)
+        vol, grad = vol.to(dev), grad.to(dev)
+        step = lambda: (ext.forward(vol), ext.backward(grad, vol))
+        units, bytes_per_unit = nb * h * w, (3 * k + 4) * 4
+        metric, unit, what = "median_fwd_bwd_gproblems_per_s", "Gproblems/s", f"selection on a [N,H,W,{k}] weight volume"
+    else:
+        from customnetworklayers_b200 import QuadFit_cuda_ext as ext
+        from customnetworklayers_b200.synthetic import make_quadfit_inputs
+        f0, f1, flow, grad = (t.to(dev) for t in make_quadfit_inputs(nb, k, h, w, seed=1237 + rank))
+        step = lambda: (ext.forward(f0, f1, flow), ext.backward(grad, f0, f1, flow))
+        units, bytes_per_unit = nb * h * w, (7 * k + 10) * 4
+        metric, unit, what = "quadfit_fwd_bwd_gpixels_per_s", "Gpixels/s", f"quadratic fit on {k}-channel feature maps"
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = _lib.load().cnl_launch_count()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = _lib.load().cnl_launch_count() - l0
+    clocks = sampler.stop()
+    if rank == 0:
+        peak, kind = measured_peak_gbs()
+        ach = bytes_per_unit * units * args.steps / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": metric, "value": units * args.steps / (ms * 1e-3) / 1e9, "unit": unit, "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {what}, batch {nb}, {h}x{w}, fwd+bwd",
+                       "l2": "inputs of several hundred MB per call, larger than the 126 MB L2; no flush"},
+            "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": ach, "peak": peak, "unit": "GB/s",
+                         "frac": ach / peak, "traffic": None, "peak_kind": kind, "algorithmic_bytes_per_unit": bytes_per_unit},
+            "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -626,6 +682,9 @@ def main():
         raise RuntimeError(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
+    elif args.workload in ("median", "quadfit"):
+        if rank == 0:
+            run_layer_micro(args, rank, local_rank, world)
     elif args.workload == "cfg4":
         run_wmedian(args, rank, local_rank, world)
     elif args.workload == "cfg3":

@@ -14,17 +14,56 @@ constexpr int kMedThreads = kMedWarps * 32;
 
 __device__ __forceinline__ int med_stride(int k) { return k | 1; }
 
-// Cooperative, coalesced copy of the rows of this warp's 32 pixels into shared memory.
+// Division of a small index by the number of bins: q = floor(i / k) for 0 <= i < 2^15, 1 <= k <= 1024, with the
+// multiplier m = floor(2^32 / k) + 1 (exact because i * k < 2^32); k = 1 has no 32-bit multiplier and is marked by 0.
+__device__ __forceinline__ unsigned med_magic(int k) { return k == 1 ? 0u : (unsigned)(0x100000000ULL / (unsigned)k) + 1u; }
+__device__ __forceinline__ int med_div(int i, unsigned magic) { return magic ? (int)__umulhi((unsigned)i, magic) : i; }
+
+// Cooperative, coalesced copy of the rows of this warp's 32 pixels (contiguous in memory) into shared memory:
+// 16-byte vector loads where the chunk is aligned, scalars otherwise and for the tail.
 __device__ __forceinline__ void stage_rows(const float* __restrict__ src, float* __restrict__ dst, long long first_pixel,
                                            long long total_pixels, int k, int lane) {
     const int stride = med_stride(k);
-    long long npix = total_pixels - first_pixel;
-    if (npix > 32) npix = 32;
-    const long long count = npix * k;
+    const unsigned magic = med_magic(k);
+    const long long left = total_pixels - first_pixel;
+    const int count = (int)(left > 32 ? 32 : left) * k;
     const float* base = src + first_pixel * k;
-    for (long long i = lane; i < count; i += 32) {
-        const int p = (int)(i / k), c = (int)(i - (long long)p * k);
-        dst[p * stride + c] = __ldg(base + i);
+    const int nvec = (reinterpret_cast<size_t>(base) & 15) == 0 ? count >> 2 : 0;
+    for (int v = lane; v < nvec; v += 32) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(base) + v);
+        int p = med_div(4 * v, magic), c = 4 * v - p * k;
+        dst[p * stride + c] = q.x; if (++c == k) { c = 0; ++p; }
+        dst[p * stride + c] = q.y; if (++c == k) { c = 0; ++p; }
+        dst[p * stride + c] = q.z; if (++c == k) { c = 0; ++p; }
+        dst[p * stride + c] = q.w;
+    }
+    for (int i = 4 * nvec + lane; i < count; i += 32) {
+        const int p = med_div(i, magic);
+        dst[p * stride + (i - p * k)] = __ldg(base + i);
+    }
+}
+
+// The reverse: coalesced write-back of the warp's rows from shared memory.
+__device__ __forceinline__ void unstage_rows(const float* __restrict__ rows, float* __restrict__ dst, long long first_pixel,
+                                             long long total_pixels, int k, int lane) {
+    const int stride = med_stride(k);
+    const unsigned magic = med_magic(k);
+    const long long left = total_pixels - first_pixel;
+    const int count = (int)(left > 32 ? 32 : left) * k;
+    float* base = dst + first_pixel * k;
+    const int nvec = (reinterpret_cast<size_t>(base) & 15) == 0 ? count >> 2 : 0;
+    for (int v = lane; v < nvec; v += 32) {
+        int p = med_div(4 * v, magic), c = 4 * v - p * k;
+        float4 q;
+        q.x = rows[p * stride + c]; if (++c == k) { c = 0; ++p; }
+        q.y = rows[p * stride + c]; if (++c == k) { c = 0; ++p; }
+        q.z = rows[p * stride + c]; if (++c == k) { c = 0; ++p; }
+        q.w = rows[p * stride + c];
+        reinterpret_cast<float4*>(base)[v] = q;
+    }
+    for (int i = 4 * nvec + lane; i < count; i += 32) {
+        const int p = med_div(i, magic);
+        base[i] = rows[p * stride + (i - p * k)];
     }
 }
 
@@ -110,15 +149,7 @@ median_backward_kernel(const float* __restrict__ vol, const float* __restrict__ 
         }
     }
     __syncwarp();
-    // coalesced write-back of the warp's rows
-    long long npix = total - first;
-    if (npix > 32) npix = 32;
-    const long long count = npix * k;
-    float* base = gvol + first * k;
-    for (long long i = lane; i < count; i += 32) {
-        const int p = (int)(i / k), c = (int)(i - (long long)p * k);
-        base[i] = rows[p * stride + c];
-    }
+    unstage_rows(rows, gvol, first, total, k, lane);
 }
 
 static int median_check(const void* a, const void* b, int n, int h, int w, int k) {
