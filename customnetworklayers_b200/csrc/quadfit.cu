@@ -1,8 +1,8 @@
 // Differentiable per-axis quadratic fit of a 5-point correlation stencil for sm_100a
 // (reference: cudaQuadFit/cudaCode/quadFit.cu, kQuadFitFlow :14-136, kQuadFitFlowGrad :142-297).
 //
-// One thread per pixel; the feature loops are unrolled by four so that 4 x 6 independent loads are in flight per
-// thread.  The kernels are HBM/L2 bound: C reads of the first feature map (coalesced) and 5 C gathered reads of the
+// One thread per pixel; the feature loops are batched by eight channels so that 48 independent loads are in flight
+// per thread.  The kernels are HBM/L2 bound: C reads of the first feature map (coalesced) and 5 C gathered reads of the
 // second one per pixel.  The float/double promotions of the reference's expressions are kept where they decide the
 // rounded integer location and the validity tests, so those are bit-identical.
 #include "common.h"
@@ -70,21 +70,47 @@ __device__ __forceinline__ QfLoc qf_locate(const float* __restrict__ flow, size_
     return L;
 }
 
+// Correlation of the pixel's feature vector with the five stencil positions in the second feature map.  The loads of
+// kQfBatch channels (6 each) are all issued before the first multiply-add, so that a thread has 48 independent
+// loads in flight instead of one round trip per channel.
+constexpr int kQfBatch = 8;
+
 __device__ __forceinline__ void qf_costs(const float* __restrict__ f0, const float* __restrict__ f1, size_t n, int C,
                                          size_t plane, int pix, const QfLoc& L, int W, float (&cost)[5]) {
     const int o00 = L.y * W + L.x, o0p = L.y * W + L.xp, op0 = L.yp * W + L.x, o0m = L.y * W + L.xm, om0 = L.ym * W + L.x;
     cost[0] = cost[1] = cost[2] = cost[3] = cost[4] = 0.0f;
     const float* a = f0 + n * C * plane + pix;
     const float* b = f1 + n * C * plane;
-#pragma unroll 4
-    for (int cc = 0; cc < C; ++cc) {
-        const float I1 = __ldg(a + (size_t)cc * plane);
-        const float* bc = b + (size_t)cc * plane;
-        cost[0] = fmaf(I1, __ldg(bc + o00), cost[0]);
-        cost[1] = fmaf(I1, __ldg(bc + o0p), cost[1]);
-        cost[2] = fmaf(I1, __ldg(bc + op0), cost[2]);
-        cost[3] = fmaf(I1, __ldg(bc + o0m), cost[3]);
-        cost[4] = fmaf(I1, __ldg(bc + om0), cost[4]);
+    int cc = 0;
+    for (; cc + kQfBatch <= C; cc += kQfBatch) {
+        float I1[kQfBatch], v[5][kQfBatch];
+#pragma unroll
+        for (int j = 0; j < kQfBatch; ++j) {
+            const float* bc = b + (size_t)j * plane;
+            I1[j] = __ldg(a + (size_t)j * plane);
+            v[0][j] = __ldg(bc + o00);
+            v[1][j] = __ldg(bc + o0p);
+            v[2][j] = __ldg(bc + op0);
+            v[3][j] = __ldg(bc + o0m);
+            v[4][j] = __ldg(bc + om0);
+        }
+#pragma unroll
+        for (int j = 0; j < kQfBatch; ++j) {            // channel order as in a plain loop: same rounding
+#pragma unroll
+            for (int q = 0; q < 5; ++q) cost[q] = fmaf(I1[j], v[q][j], cost[q]);
+        }
+        a += (size_t)kQfBatch * plane;
+        b += (size_t)kQfBatch * plane;
+    }
+    for (; cc < C; ++cc) {
+        const float I1 = __ldg(a);
+        cost[0] = fmaf(I1, __ldg(b + o00), cost[0]);
+        cost[1] = fmaf(I1, __ldg(b + o0p), cost[1]);
+        cost[2] = fmaf(I1, __ldg(b + op0), cost[2]);
+        cost[3] = fmaf(I1, __ldg(b + o0m), cost[3]);
+        cost[4] = fmaf(I1, __ldg(b + om0), cost[4]);
+        a += plane;
+        b += plane;
     }
 }
 
@@ -140,8 +166,36 @@ quadfit_backward_kernel(const float* __restrict__ f0, const float* __restrict__ 
                   k00, k0p, k0m, kp0, km0);
     const int o00 = L.y * W + L.x, o0p = L.y * W + L.xp, op0 = L.yp * W + L.x, o0m = L.y * W + L.xm, om0 = L.ym * W + L.x;
     const bool stencil = q.vx || q.vy;
-#pragma unroll 2
-    for (int cc = 0; cc < C; ++cc) {
+    constexpr int kB = 4;                      // channels whose loads are issued together
+    int cc = 0;
+    for (; cc + kB <= C; cc += kB) {
+        float I1[kB], v[5][kB];
+#pragma unroll
+        for (int j = 0; j < kB; ++j) {
+            const size_t base = (n * C + cc + j) * plane;
+            I1[j] = __ldg(f0 + base + pix);
+            v[0][j] = __ldg(f1 + base + o00);
+            if (stencil) {
+                v[1][j] = __ldg(f1 + base + o0p); v[2][j] = __ldg(f1 + base + o0m);
+                v[3][j] = __ldg(f1 + base + op0); v[4][j] = __ldg(f1 + base + om0);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kB; ++j) {
+            const size_t base = (n * C + cc + j) * plane;
+            float acc = k00 * v[0][j];
+            atomicAdd(g1 + base + o00, I1[j] * k00);
+            if (stencil) {
+                acc += k0p * v[1][j] + k0m * v[2][j] + kp0 * v[3][j] + km0 * v[4][j];
+                atomicAdd(g1 + base + o0p, I1[j] * k0p);
+                atomicAdd(g1 + base + o0m, I1[j] * k0m);
+                atomicAdd(g1 + base + op0, I1[j] * kp0);
+                atomicAdd(g1 + base + om0, I1[j] * km0);
+            }
+            g0[base + pix] = acc;
+        }
+    }
+    for (; cc < C; ++cc) {
         const size_t base = (n * C + cc) * plane;
         const float I1 = __ldg(f0 + base + pix);
         float acc = k00 * __ldg(f1 + base + o00);
