@@ -114,7 +114,7 @@ __device__ __forceinline__ void qf_costs(const float* __restrict__ f0, const flo
     }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 quadfit_forward_kernel(const float* __restrict__ f0, const float* __restrict__ f1, const float* __restrict__ flow,
                        int flow_ch, float* __restrict__ out, int* __restrict__ loc, int C, int H, int W) {
     const size_t plane = (size_t)H * W;
@@ -143,7 +143,7 @@ quadfit_forward_kernel(const float* __restrict__ f0, const float* __restrict__ f
 
 // g0 is written directly (one owner per element); g1 is a scatter with fp32 atomics like the reference's, so its
 // summation order is not deterministic.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 quadfit_backward_kernel(const float* __restrict__ f0, const float* __restrict__ f1, const float* __restrict__ flow,
                         int flow_ch, const float* __restrict__ grad, float* __restrict__ g0, float* __restrict__ g1,
                         int C, int H, int W) {
