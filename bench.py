@@ -28,6 +28,7 @@ WORKLOADS = {
     "cfg1": (8, 2, 384, 1280, 100),
     "cfg0": (1, 2, 96, 320, 20),
     "small": (2, 2, 384, 1280, 20),      # profiling case: a few hundred MB on the device
+    "odd": (8, 2, 375, 1242, 100),        # rows of 1242 floats: not a multiple of four, runs on zero-padded staging copies
     "prof": (8, 2, 384, 1280, 20),       # profiling case with the launch geometry of cfg1 and a fifth of its history
     "cfg2": (8, 2, 436, 1024, 100),      # TGV-FISTA (secondary workload, run with --workload cfg2)
     "cfg2small": (2, 2, 436, 1024, 10),  # TGV profiling case

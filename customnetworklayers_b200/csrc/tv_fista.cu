@@ -330,6 +330,8 @@ struct Slot {
     int opt_fuse = 0;
     int opt_timing = 0;
     int opt_recompute = 0;           // 1: keep only checkpoints and rebuild each segment's history in the backward pass
+    int pitch = 0;                   // row pitch (floats) of the arena planes of the stored forward pass
+    bool staged = false;             // the temporally blocked kernels ran on zero-padded copies (pitch > w or unaligned tensors)
     bool recompute = false;          // mode the stored forward pass was run in
     bool window_valid = false;       // recompute mode: the history window holds the LAST segment (left by the forward)
     // timing ring: per recorded call one (start, stop) event pair around the iteration loop and its launch count
@@ -383,13 +385,17 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 struct ArenaLayout {
     size_t vol;       // n*ch*h*w rounded up to 64 floats
     size_t y0, y1, xbuf, hist, ckpt, xck, ga, gb, acc, acc2, ybuf, total;
+    size_t map;       // n*h*w rounded up to 64 floats (w = row pitch)
+    size_t stage_map, stage_vol;     // 6 map-sized and 4 volume-sized staging buffers (staged mode only)
 };
 
 // hist_planes: its_eff when every iterate is kept, the longest segment in recompute mode; xck_planes: primal iterate
 // at every checkpoint (recompute mode only, needed to restart the iteration there).
-static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t hist_planes, size_t nckpt, size_t xck_planes = 0) {
+static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t hist_planes, size_t nckpt, size_t xck_planes = 0,
+                               bool staged = false) {
     ArenaLayout L;
     L.vol = align_up(n * ch * h * w, 64);
+    L.map = align_up(n * h * w, 64);
     size_t o = 0;
     L.y0 = o; o += L.vol;
     L.y1 = o; o += L.vol;
@@ -402,6 +408,8 @@ static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t h
     L.ckpt = o; o += L.vol * nckpt;
     L.xck = o; o += L.vol * xck_planes;
     L.hist = o; o += L.vol * hist_planes;
+    L.stage_map = o; o += staged ? 6 * L.map : 0;
+    L.stage_vol = o; o += staged ? 4 * L.vol : 0;
     L.total = o;
     return L;
 }
@@ -430,9 +438,22 @@ static int longest_segment(const std::vector<int>& sched, int its_eff) {
     for (int i = 0; i < (int)sched.size(); ++i) m = std::max(m, seg_end(sched, i, its_eff) - seg_begin(sched, i));
     return m;
 }
-static ArenaLayout slot_layout(size_t n, size_t ch, size_t h, size_t w, int its_eff, const std::vector<int>& sched, bool recompute) {
-    if (recompute) return make_layout(n, ch, h, w, (size_t)longest_segment(sched, its_eff), sched.size(), sched.size());
-    return make_layout(n, ch, h, w, (size_t)its_eff, sched.size());
+// `pitch` is the row pitch of every arena plane in floats (w, or w rounded up to 4 in staged mode).
+static ArenaLayout slot_layout(size_t n, size_t ch, size_t h, size_t pitch, int its_eff, const std::vector<int>& sched, bool recompute,
+                               bool staged = false) {
+    if (recompute) return make_layout(n, ch, h, pitch, (size_t)longest_segment(sched, its_eff), sched.size(), sched.size(), staged);
+    return make_layout(n, ch, h, pitch, (size_t)its_eff, sched.size(), 0, staged);
+}
+
+// Zero-padded copy of `rows` image rows of w floats into rows of `pitch` floats, and back.
+static int pad_rows(float* dst, const float* src, size_t rows, int w, int pitch, cudaStream_t st) {
+    CNL_TRY(check_cuda(cudaMemsetAsync(dst, 0, rows * pitch * sizeof(float), st), "zero staging buffer"));
+    return check_cuda(cudaMemcpy2DAsync(dst, pitch * sizeof(float), src, w * sizeof(float), w * sizeof(float), rows,
+                                        cudaMemcpyDeviceToDevice, st), "pad rows");
+}
+static int unpad_rows(float* dst, const float* src, size_t rows, int w, int pitch, cudaStream_t st) {
+    return check_cuda(cudaMemcpy2DAsync(dst, w * sizeof(float), src, pitch * sizeof(float), w * sizeof(float), rows,
+                                        cudaMemcpyDeviceToDevice, st), "unpad rows");
 }
 
 static int check_common(const void* const* ptrs, int nptr, int n, int ch, int h, int w, int its, int id) {
@@ -499,17 +520,37 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
     const int its_eff = 2 * (its / 2);
     const void* aligned[] = {wx, wy, c, b, init, out};          // the arena itself is 256-byte aligned
     const int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
-    const bool fused = fuse > 1 && fused_supported(w, aligned, 6);
-    ArenaLayout L = slot_layout(n, ch, h, w, its_eff, s.sched, false);
+    const bool fused = fuse > 1;
+    // The temporally blocked kernels read 16-byte vectors: tensors whose rows are not a multiple of 4 floats, or that
+    // are not 16-byte aligned, are staged into zero-padded copies with such a pitch; everything the kernels touch
+    // then lives in the arena and the results are copied back row by row.
+    const bool staged = fused && !fused_supported(w, aligned, 6);
+    const int P = staged ? ((w + 3) & ~3) : w;
+    ArenaLayout L = slot_layout(n, ch, h, P, its_eff, s.sched, false, staged);
     // Keeping every iterate costs its_eff volumes.  When that exceeds the budget (or on request) only the checkpoints
     // are kept and the backward pass rebuilds the history segment by segment, like the reference does
     // (TVInpaintFista.cu:1690-1760); the temporally blocked kernels are needed for that.
     const bool recompute = fused && (s.opt_recompute || L.total > arena_budget_floats());
-    if (recompute) L = slot_layout(n, ch, h, w, its_eff, s.sched, true);
+    if (recompute) L = slot_layout(n, ch, h, P, its_eff, s.sched, true, staged);
     CNL_TRY(ensure_arena(s, L.total));
     s.recompute = recompute;
+    s.staged = staged;
+    s.pitch = P;
     s.window_valid = false;
-    const size_t vol_bytes = (size_t)n * ch * h * w * sizeof(float);
+    const size_t vol_bytes = (size_t)n * ch * h * P * sizeof(float);
+    if (staged) {
+        float* m = s.arena + L.stage_map;
+        float* v = s.arena + L.stage_vol;
+        CNL_TRY(pad_rows(m + 0 * L.map, wx, (size_t)n * h, w, P, st));
+        CNL_TRY(pad_rows(m + 1 * L.map, wy, (size_t)n * h, w, P, st));
+        CNL_TRY(pad_rows(m + 2 * L.map, c, (size_t)n * h, w, P, st));
+        CNL_TRY(pad_rows(v + 0 * L.vol, b, (size_t)n * ch * h, w, P, st));
+        CNL_TRY(pad_rows(v + 1 * L.vol, init, (size_t)n * ch * h, w, P, st));
+        wx = m + 0 * L.map; wy = m + 1 * L.map; c = m + 2 * L.map;
+        b = v + 0 * L.vol; init = v + 1 * L.vol;
+    }
+    float* const user_out = out;
+    if (staged) out = s.arena + L.stage_vol + 2 * L.vol;
     float* y0 = s.arena + L.y0;
     float* y1 = s.arena + L.y1;
     if (fused) {
@@ -545,7 +586,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
             fp.y_out = (i & 1) ? y1 : y0;
             fp.x_out = ((nlaunch - 1 - i) & 1) ? xbuf : out;
             fp.b = b; fp.c = c; fp.wx = wx; fp.wy = wy;
-            fp.N = n; fp.C = ch; fp.H = h; fp.W = w;
+            fp.N = n; fp.C = ch; fp.H = h; fp.W = w; fp.P = P;
             for (int j = 0; j < K; ++j) {
                 const int g = g0 + j;
                 fp.t[j] = s.steps[g];
@@ -569,6 +610,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
             s.launches_fwd[s.n_fwd] = (int)(g_launches.load() - launches0);
             s.n_fwd += 1;
         }
+        if (staged) CNL_TRY(unpad_rows(user_out, out, (size_t)n * ch * h, w, P, st));
         s.n = n; s.ch = ch; s.h = h; s.w = w; s.its = its;
         s.window_valid = recompute;
         s.have_forward = true;
@@ -622,10 +664,34 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
                     id, id);
     CNL_TRY(ensure_cond(s));
     const int its_eff = 2 * (its / 2);
-    const ArenaLayout L = slot_layout(n, ch, h, w, its_eff, s.sched, s.recompute);
-    const size_t plane = (size_t)h * w;
+    const bool staged = s.staged;
+    const int P = s.pitch;                        // row pitch of the arena planes (w unless staged)
+    const ArenaLayout L = slot_layout(n, ch, h, P, its_eff, s.sched, s.recompute, staged);
+    const size_t plane = (size_t)h * P;
+    const size_t uplane = (size_t)h * w;          // plane of the caller's tensors
     const size_t vol_bytes = (size_t)n * ch * plane * sizeof(float);
     const size_t map_bytes = (size_t)n * plane * sizeof(float);
+    const void* aligned[] = {wx, wy, c, b, grad_out, g_wx, g_wy, g_c, g_b, g_init};
+    const int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
+    const bool fused = fuse > 1 && (staged || fused_supported(w, aligned, 10));
+    if ((s.recompute || staged) && !fused)
+        return fail(CNL_ERR_BAD_OPTION, "the forward pass of id %d ran on the temporally blocked kernels (%s); the backward pass "
+                    "needs them too: keep the fuse option and pass 16-byte aligned tensors", id,
+                    staged ? "zero-padded staging" : "checkpoints only");
+    float* const u_gwx = g_wx; float* const u_gwy = g_wy; float* const u_gc = g_c; float* const u_gb = g_b; float* const u_ginit = g_init;
+    if (staged) {          // same staging as in the forward pass, plus the upstream gradient and the five outputs
+        float* m = s.arena + L.stage_map;
+        float* v = s.arena + L.stage_vol;
+        CNL_TRY(pad_rows(m + 0 * L.map, wx, (size_t)n * h, w, P, st));
+        CNL_TRY(pad_rows(m + 1 * L.map, wy, (size_t)n * h, w, P, st));
+        CNL_TRY(pad_rows(m + 2 * L.map, c, (size_t)n * h, w, P, st));
+        CNL_TRY(pad_rows(v + 0 * L.vol, b, (size_t)n * ch * h, w, P, st));
+        CNL_TRY(pad_rows(v + 1 * L.vol, grad_out, (size_t)n * ch * h, w, P, st));
+        wx = m + 0 * L.map; wy = m + 1 * L.map; c = m + 2 * L.map;
+        b = v + 0 * L.vol; grad_out = v + 1 * L.vol;
+        g_wx = m + 3 * L.map; g_wy = m + 4 * L.map; g_c = m + 5 * L.map;
+        g_b = v + 2 * L.vol; g_init = v + 3 * L.vol;
+    }
     float* ga = s.arena + L.ga;      // d_gxk05_0_temp
     float* gb = s.arena + L.gb;      // d_gxk05_1_temp
     float* acc = s.arena + L.acc;
@@ -649,11 +715,6 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
             if (s.sched[i] == g) return s.arena + L.ckpt + i * L.vol;      // segment start: the checkpointed y_g (:1724-1727)
         return nullptr;
     };
-    const void* aligned[] = {wx, wy, c, b, g_wx, g_wy, g_c, g_b, g_init, s.arena};
-    const int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
-    const bool fused = fuse > 1 && fused_supported(w, aligned, 10);
-    if (s.recompute && !fused)
-        return fail(CNL_ERR_BAD_SHAPE, "the forward pass kept checkpoints only; the backward pass then needs 16-byte aligned tensors");
     const int nseg = (int)s.sched.size();
     // Recompute mode: rebuilds the history window of segment i from the y and x saved at its checkpoint.
     auto rebuild_segment = [&](int i) -> int {
@@ -668,7 +729,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
             fp.y_out = s.arena + ((k & 1) ? L.y1 : L.y0);        // iterates beyond the window are scratch
             fp.x_out = s.arena + ((k & 1) ? L.ybuf : L.xbuf);
             fp.b = b; fp.c = c; fp.wx = wx; fp.wy = wy;
-            fp.N = n; fp.C = ch; fp.H = h; fp.W = w;
+            fp.N = n; fp.C = ch; fp.H = h; fp.W = w; fp.P = P;
             for (int j = 0; j < K; ++j) {
                 fp.t[j] = s.steps[g0 + j];
                 fp.ckpt[j] = nullptr;
@@ -717,7 +778,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
             rp.acc_out = flip ? acc : acc2;
             rp.b = b; rp.c = c; rp.wx = wx; rp.wy = wy;
             rp.g_c = g_c; rp.g_b = g_b; rp.g_wx = g_wx; rp.g_wy = g_wy;
-            rp.N = n; rp.C = ch; rp.H = h; rp.W = w;
+            rp.N = n; rp.C = ch; rp.H = h; rp.W = w; rp.P = P;
             for (int j = 0; j <= K; ++j) {
                 const int g = g0 - j;
                 rp.hist[j] = g >= 0 ? hist_of(g) : nullptr;
@@ -756,12 +817,19 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
         s.n_rev += 1;
     }
 
+    if (staged) {
+        CNL_TRY(unpad_rows(u_gwx, g_wx, (size_t)n * h, w, P, st));
+        CNL_TRY(unpad_rows(u_gwy, g_wy, (size_t)n * h, w, P, st));
+        CNL_TRY(unpad_rows(u_gc, g_c, (size_t)n * h, w, P, st));
+        CNL_TRY(unpad_rows(u_gb, g_b, (size_t)n * ch * h, w, P, st));
+        CNL_TRY(unpad_rows(u_ginit, g_init, (size_t)n * ch * h, w, P, st));
+    }
     FinalizeArgs fa;
-    fa.ptr[0] = g_c;  fa.count[0] = (unsigned long long)n * plane;      fa.scale[0] = kGlobalG;
-    fa.ptr[1] = g_wx; fa.count[1] = (unsigned long long)n * plane;      fa.scale[1] = kGlobalG * kLip;
-    fa.ptr[2] = g_wy; fa.count[2] = (unsigned long long)n * plane;      fa.scale[2] = kGlobalG * kLip;
-    fa.ptr[3] = g_b;  fa.count[3] = (unsigned long long)n * ch * plane; fa.scale[3] = kGlobalG;
-    fa.ptr[4] = g_init; fa.count[4] = (unsigned long long)n * ch * plane; fa.scale[4] = 1.0f;
+    fa.ptr[0] = u_gc;  fa.count[0] = (unsigned long long)n * uplane;      fa.scale[0] = kGlobalG;
+    fa.ptr[1] = u_gwx; fa.count[1] = (unsigned long long)n * uplane;      fa.scale[1] = kGlobalG * kLip;
+    fa.ptr[2] = u_gwy; fa.count[2] = (unsigned long long)n * uplane;      fa.scale[2] = kGlobalG * kLip;
+    fa.ptr[3] = u_gb;  fa.count[3] = (unsigned long long)n * ch * uplane; fa.scale[3] = kGlobalG;
+    fa.ptr[4] = u_ginit; fa.count[4] = (unsigned long long)n * ch * uplane; fa.scale[4] = 1.0f;
     double* state = s.cond;
     double* partial = s.cond + kNumOutputs;
     float* factor = reinterpret_cast<float*>(s.cond + kNumOutputs + (size_t)kNumOutputs * kStatBlocks * 2);
@@ -827,7 +895,7 @@ static int read_iterate(int id, int idx, bool checkpoint, float* dst, void* stre
     const int its_eff = 2 * (sp->its / 2);
     const int limit = checkpoint ? (int)sp->sched.size() : its_eff;
     if (idx < 0 || idx >= limit) return fail(CNL_ERR_BAD_SHAPE, "index %d is outside 0..%d", idx, limit - 1);
-    const ArenaLayout L = slot_layout(sp->n, sp->ch, sp->h, sp->w, its_eff, sp->sched, sp->recompute);
+    const ArenaLayout L = slot_layout(sp->n, sp->ch, sp->h, sp->pitch, its_eff, sp->sched, sp->recompute, sp->staged);
     if (!checkpoint && sp->recompute) {
         const int first = sp->sched.back();
         if (!sp->window_valid || idx < first)
@@ -835,9 +903,7 @@ static int read_iterate(int id, int idx, bool checkpoint, float* dst, void* stre
         idx -= first;
     }
     const float* src = sp->arena + (checkpoint ? L.ckpt : L.hist) + (size_t)idx * L.vol;
-    const size_t bytes = (size_t)sp->n * sp->ch * sp->h * sp->w * sizeof(float);
-    return check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)),
-                      "copy stored iterate");
+    return unpad_rows(dst, src, (size_t)sp->n * sp->ch * sp->h, sp->w, sp->pitch, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int cnl_tv_read_history(int id, int g, float* dst, void* stream) {

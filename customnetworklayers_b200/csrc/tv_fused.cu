@@ -118,10 +118,10 @@ __device__ __forceinline__ TileGeom make_geom_at(int tx, int ty, int H, int W) {
 template <typename P>
 __device__ __forceinline__ void load_maps(const P& p, const TileGeom& g, size_t n, float4 (&c)[kRows],
                                           float4 (&wx)[kRows], float4 (&wy)[kRows]) {
-    const size_t plane = (size_t)p.H * p.W;
+    const size_t plane = (size_t)p.H * p.P;
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
-        const size_t o = n * plane + (size_t)g.gy[r] * p.W + g.gx;
+        const size_t o = n * plane + (size_t)g.gy[r] * p.P + g.gx;
         c[r] = ld4(p.c + o, g.ok[r]);
         float4 a = ld4(p.wx + o, g.ok[r]);
         float4 bq = ld4(p.wy + o, g.ok[r]);
@@ -183,7 +183,7 @@ tv_fwd_fused_kernel(const __grid_constant__ FwdFusedParams p) {
     __shared__ float4 sh_f[kWarps][32];     // each warp's last-row vertical flux
     const TileGeom g = make_geom<K>(p.H, p.W);
     const size_t n = blockIdx.z;
-    const size_t plane = (size_t)p.H * p.W;
+    const size_t plane = (size_t)p.H * p.P;
     float4 c[kRows], wx[kRows], wy[kRows];
     load_maps(p, g, n, c, wx, wy);
     for (int ch = 0; ch < p.C; ++ch) {
@@ -191,7 +191,7 @@ tv_fwd_fused_kernel(const __grid_constant__ FwdFusedParams p) {
         size_t off[kRows];
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            off[r] = (n * p.C + ch) * plane + (size_t)g.gy[r] * p.W + g.gx;
+            off[r] = (n * p.C + ch) * plane + (size_t)g.gy[r] * p.P + g.gx;
             y[r] = ld4(p.y_in + off[r], g.ok[r]);
             x[r] = ld4(p.x_in + off[r], g.ok[r]);
             b[r] = ld4(p.b + off[r], g.ok[r]);
@@ -250,14 +250,14 @@ tv_fwd_pipe_kernel(const __grid_constant__ FwdFusedParams p, int tiles_x, int ti
     float4* buf_maps = buf_item + 3 * kRows * kThreads;         // c, wx, wy of the next tile
     const int tid = threadIdx.x;
     const int ntiles = tiles_x * tiles_y * p.N;
-    const size_t plane = (size_t)p.H * p.W;
+    const size_t plane = (size_t)p.H * p.P;
 
     auto issue = [&](int tile, int ch) {
         const TileCoord tc = tile_coord(tile, tiles_x, tiles_y);
         const TileGeom gg = make_geom_at<K>(tc.tx, tc.ty, p.H, p.W);
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            const size_t pix = gg.ok[r] ? (size_t)gg.gy[r] * p.W + gg.gx : 0;
+            const size_t pix = gg.ok[r] ? (size_t)gg.gy[r] * p.P + gg.gx : 0;
             const size_t o = gg.ok[r] ? (tc.n * p.C + ch) * plane + pix : 0;
             cp_async16(buf_item + (0 * kRows + r) * kThreads + tid, p.y_in + o, gg.ok[r]);
             cp_async16(buf_item + (1 * kRows + r) * kThreads + tid, p.x_in + o, gg.ok[r]);
@@ -294,7 +294,7 @@ tv_fwd_pipe_kernel(const __grid_constant__ FwdFusedParams p, int tiles_x, int ti
             size_t off[kRows];
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
-                off[r] = (tc.n * p.C + ch) * plane + (size_t)g.gy[r] * p.W + g.gx;
+                off[r] = (tc.n * p.C + ch) * plane + (size_t)g.gy[r] * p.P + g.gx;
                 y[r] = buf_item[(0 * kRows + r) * kThreads + tid];
                 x[r] = buf_item[(1 * kRows + r) * kThreads + tid];
                 b[r] = buf_item[(2 * kRows + r) * kThreads + tid];
@@ -451,7 +451,7 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
     float4(*sh_p)[32] = sh_g + kWarps;                                               // last-row vertical adjoint flux
     const TileGeom g = make_geom<K>(p.H, p.W);
     const size_t n = blockIdx.z;
-    const size_t plane = (size_t)p.H * p.W;
+    const size_t plane = (size_t)p.H * p.P;
     float4 c[kRows], wx[kRows], wy[kRows];
     load_maps(p, g, n, c, wx, wy);
 #pragma unroll
@@ -465,7 +465,7 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
         size_t off[kRows];
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            off[r] = (n * p.C + ch) * plane + (size_t)g.gy[r] * p.W + g.gx;
+            off[r] = (n * p.C + ch) * plane + (size_t)g.gy[r] * p.P + g.gx;
             gq[r] = ld4(p.g_in + off[r], g.ok[r]);
             acc[r] = ld4(p.acc_in + off[r], g.ok[r]);
             b[r] = ld4(p.b + off[r], g.ok[r]);
@@ -554,7 +554,7 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
         if (!g.store[r]) continue;
-        const size_t o = n * plane + (size_t)g.gy[r] * p.W + g.gx;
+        const size_t o = n * plane + (size_t)g.gy[r] * p.P + g.gx;
         const float4 dc = sh_dc[r * kThreads + threadIdx.x];
         float4 ax = sh_dwx[r * kThreads + threadIdx.x];
         float4 ay = sh_dwy[r * kThreads + threadIdx.x];

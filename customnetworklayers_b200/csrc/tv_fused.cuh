@@ -31,6 +31,7 @@ struct FwdFusedParams {
     float* ckpt[kFuseMax];      // if non-null: y before fused iteration j is stored here (checkpoint)
     float t[kFuseMax];          // momentum factors
     int N, C, H, W;
+    int P;                      // row pitch of every plane in floats (multiple of 4, >= W; pad columns hold zeros)
 };
 
 struct RevFusedParams {
@@ -51,9 +52,11 @@ struct RevFusedParams {
     float* g_wy;
     float* x1bar;               // if non-null: dL/dx of the last fused step is stored here (init gradient)
     int N, C, H, W;
+    int P;                      // row pitch in floats, as in FwdFusedParams
 };
 
-// True if the fused kernels can run on this shape / these pointers (16-byte vectors need W % 4 == 0).
+// True if the fused kernels can run directly on these tensors: 16-byte vectors need a row pitch divisible by 4 and
+// aligned base pointers.  Otherwise the driver stages zero-padded copies with such a pitch.
 bool fused_supported(int W, const void* const* ptrs, int nptr);
 
 // Enqueue K (1..kFuseMax) fused iterations.  Return 0 or a CNL_ERR_* code.

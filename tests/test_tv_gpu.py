@@ -395,3 +395,56 @@ def test_full_size_properties(ext):
         for p in (pid, pid1):
             ext.set_option(p, _lib.OPT_CONDITIONER, 1)
             ext.release(p)
+
+
+def test_widths_and_pointers_that_need_staging(ext):
+    """Rows that are not a multiple of four floats (e.g. the 1242-pixel rows of a common flow benchmark) and tensors
+    that are not 16-byte aligned run the same temporally blocked kernels on zero-padded copies."""
+    from customnetworklayers_b200 import _lib
+    pid = 9
+    ext.release(pid)
+    ext.set_option(pid, _lib.OPT_CONDITIONER, 0)
+    try:
+        n, ch, h, w, its = 2, 2, 30, 1242, 10
+        I = R.make_inputs(n, ch, h, w, seed=4242)
+        D = _dev(I)
+        sol, hist, cky, grads = _run_cuda(ext, D, its, pid)
+        ref_sol, ref_hist, ref_cky = R.tv_forward_history(I["wx"], I["wy"], I["c"], I["b"], I["init"], its)
+        assert_close(sol, ref_sol, "solution")
+        assert_close(hist, ref_hist, "history")
+        assert_close(cky, ref_cky, "checkpoints")
+        ref = R.tv_backward_raw(I["wx"], I["wy"], I["c"], I["b"], I["grad"], its, None, hist=hist.cpu(), ckpt_y=cky.cpu())
+        for name, g, r in zip(GRAD_NAMES, grads, ref):
+            assert_close(g, r, name)
+        # checkpoint-only storage on top of the staging
+        ext.set_option(pid, _lib.OPT_RECOMPUTE, 1)
+        sol_r = ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, pid)[0]
+        g_r = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, pid)
+        assert torch.equal(sol_r, sol)
+        for name, a, b2 in zip(GRAD_NAMES, grads, g_r):
+            assert_close(b2, a, name, tol=1e-5)
+        ext.set_option(pid, _lib.OPT_RECOMPUTE, 0)
+        # misaligned tensors of an aligned shape give the bits of the aligned call
+        n, ch, h, w, its = 1, 2, 24, 64, 12
+        I = R.make_inputs(n, ch, h, w, seed=77)
+        D = _dev(I)
+        sol_a = ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, pid)[0]
+        g_a = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, pid)
+
+        def shifted(t):              # same values, storage offset of one float
+            buf = torch.empty(t.numel() + 1, device=t.device, dtype=t.dtype)
+            view = buf[1:].view(t.shape)
+            view.copy_(t)
+            return view
+        U = {k: shifted(v) for k, v in D.items()}
+        assert all(v.data_ptr() % 16 != 0 for v in U.values())
+        sol_u = ext.forward(U["wx"], U["wy"], U["c"], U["b"], U["init"], its, pid)[0]
+        g_u = ext.backward(U["grad"], U["wx"], U["wy"], U["c"], U["b"], its, pid)
+        torch.cuda.synchronize()
+        assert torch.equal(sol_u, sol_a)
+        for name, a, b2 in zip(GRAD_NAMES, g_a, g_u):
+            assert torch.equal(a, b2), name
+    finally:
+        ext.set_option(pid, _lib.OPT_RECOMPUTE, 0)
+        ext.set_option(pid, _lib.OPT_CONDITIONER, 1)
+        ext.release(pid)
