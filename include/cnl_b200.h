@@ -34,7 +34,9 @@ extern "C" {
 #define CNL_OPT_CONDITIONER 1   /* 1 (default): stateful spike kill / rescale of returned gradients after 10 runs
                                    (cudaTV/cudaCode/TVInpaintFista.cu:128-155, :1760-1792); 0: off */
 #define CNL_OPT_FUSE 2          /* iterations fused per launch: 0 = automatic (default), 1 = one launch per iteration,
-                                   2..4 = fixed temporal-blocking factor */
+                                   2..4 = fixed temporal-blocking factor.  Rows that are not a multiple of four floats
+                                   and tensors that are not 16-byte aligned are staged into zero-padded copies (any
+                                   value but 1); keep the value between a forward call and its backward call */
 
 #define CNL_OPT_TIMING 3        /* 1: bracket the forward and the reverse iteration loop of every call with CUDA events on
                                    the caller's stream (up to 64 calls are kept); setting the option clears the records */
@@ -42,8 +44,8 @@ extern "C" {
                                    that exceeds the CNL_MAX_ARENA_GB budget; 1: always keep only the floor(sqrt(its))
                                    checkpoints (y and x) and let the backward pass rebuild the history one checkpoint
                                    segment at a time, as the reference does (cudaTV/cudaCode/TVInpaintFista.cu:1690-1760).
-                                   Costs one extra forward sweep per backward pass; needs widths divisible by 4 and
-                                   16-byte aligned tensors */
+                                   Costs one extra forward sweep per backward pass; not available with
+                                   CNL_OPT_FUSE = 1 */
 
 /*
  * Forward pass of the unrolled FISTA TV-inpainting layer: 2*floor(its/2) iterations starting from x = y = init.
