@@ -548,6 +548,8 @@ struct Slot {
     size_t arena_floats = 0;
     double* cond = nullptr;
     int n = 0, ch = 0, h = 0, w = 0, its = 0;
+    int pitch = 0;                   // row pitch (floats) of the arena planes of the stored forward pass
+    bool staged = false;             // the register-tiled kernels ran on zero-padded copies
     bool have_forward = false;
     int run = 0;
     int opt_conditioner = 1;
@@ -572,13 +574,16 @@ static Slot* get_slot(int id, int* rc) {
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Layout {
-    size_t vol;                        // n*3*ch*h*w rounded up
+    size_t vol;                        // n*3*ch*h*w rounded up (w = row pitch)
+    size_t map;                        // n*h*w rounded up
     size_t y0, y1, ga, gb, acc, L, lip, flags, ckpt, hist, total;
+    size_t stage;                      // staged mode: 2*(2+2+1+ch) maps and 2 volumes of zero-padded copies
 };
 
-static Layout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t its_eff, size_t nckpt) {
+static Layout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t its_eff, size_t nckpt, bool staged = false) {
     Layout l;
     l.vol = align_up(n * 3 * ch * h * w, 64);
+    l.map = align_up(n * h * w, 64);
     size_t o = 0;
     l.y0 = o; o += l.vol;
     l.y1 = o; o += l.vol;
@@ -590,6 +595,7 @@ static Layout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t its_ef
     l.flags = o; o += 64;
     l.ckpt = o; o += l.vol * nckpt;
     l.hist = o; o += l.vol * its_eff;
+    l.stage = o; o += staged ? 2 * (5 + ch) * l.map + 2 * l.vol : 0;
     l.total = o;
     return l;
 }
@@ -634,6 +640,17 @@ static bool vec_enabled() {
     return v == 1;
 }
 
+// Zero-padded copy of `rows` image rows of w floats into rows of `pitch` floats, and back.
+static int pad_rows(float* dst, const float* src, size_t rows, int w, int pitch, cudaStream_t st) {
+    CNL_TRY(check_cuda(cudaMemsetAsync(dst, 0, rows * pitch * sizeof(float), st), "zero staging buffer"));
+    return check_cuda(cudaMemcpy2DAsync(dst, pitch * sizeof(float), src, w * sizeof(float), w * sizeof(float), rows,
+                                        cudaMemcpyDeviceToDevice, st), "pad rows");
+}
+static int unpad_rows(float* dst, const float* src, size_t rows, int w, int pitch, cudaStream_t st) {
+    return check_cuda(cudaMemcpy2DAsync(dst, w * sizeof(float), src, pitch * sizeof(float), w * sizeof(float), rows,
+                                        cudaMemcpyDeviceToDevice, st), "unpad rows");
+}
+
 static int lipschitz(const float* dx, const float* dy, float* Lbuf, int* lip_bits, int n, int h, int w, cudaStream_t st) {
     tgv_lipschitz_init_kernel<<<(n + 127) / 128, 128, 0, st>>>(lip_bits, n);
     CNL_TRY(after_launch("tgv_lipschitz_init_kernel"));
@@ -657,18 +674,38 @@ static int forward_impl(const float* dx, const float* dy, const float* c, const 
     s.have_forward = false;
     schedule(its, s.sched, s.steps);
     const int its_eff = 2 * (its / 2);
-    const Layout l = make_layout(n, ch, h, w, its_eff, s.sched.size());
+    // The register-tiled kernels read 16-byte vectors: tensors whose rows are not a multiple of 4 floats, or that are
+    // not 16-byte aligned, are staged into zero-padded copies with such a pitch (pad columns stay zero through both
+    // sweeps); the results are copied back row by row.
+    const void* planes[] = {dx, dy, c, b, init, out};
+    const bool direct = tgv_vec_supported(w, planes, 6);
+    const bool vec = vec_enabled();
+    const bool staged = vec && !direct;
+    const int P = staged ? ((w + 3) & ~3) : w;
+    const Layout l = make_layout(n, ch, h, P, its_eff, s.sched.size(), staged);
     CNL_TRY(ensure_arena(s, l.total));
-    const size_t vol_bytes = (size_t)n * 3 * ch * h * w * sizeof(float);
+    s.staged = staged;
+    s.pitch = P;
+    const size_t vol_bytes = (size_t)n * 3 * ch * h * P * sizeof(float);
     float* y0 = s.arena + l.y0;
     float* y1 = s.arena + l.y1;
     float* Lbuf = s.arena + l.L;
     CNL_TRY(lipschitz(dx, dy, Lbuf, reinterpret_cast<int*>(s.arena + l.lip), n, h, w, st));
+    float* const user_out = out;
+    if (staged) {
+        float* m = s.arena + l.stage;
+        float* v = m + 2 * (5 + ch) * l.map;
+        CNL_TRY(pad_rows(m + 0 * l.map, dx, (size_t)n * 2 * h, w, P, st));
+        CNL_TRY(pad_rows(m + 2 * l.map, dy, (size_t)n * 2 * h, w, P, st));
+        CNL_TRY(pad_rows(m + 4 * l.map, c, (size_t)n * h, w, P, st));
+        CNL_TRY(pad_rows(m + 5 * l.map, b, (size_t)n * ch * h, w, P, st));
+        CNL_TRY(pad_rows(v, init, (size_t)n * 3 * ch * h, w, P, st));
+        dx = m; dy = m + 2 * l.map; c = m + 4 * l.map; b = m + 5 * l.map; init = v;
+        out = v + l.vol;
+    }
     CNL_TRY(check_cuda(cudaMemcpyAsync(out, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->x"));
     CNL_TRY(check_cuda(cudaMemcpyAsync(y0, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->y"));
     const dim3 grid((w + TW - 1) / TW, (h + TH - 1) / TH, n);
-    const void* planes[] = {dx, dy, c, b, out, s.arena};
-    const bool vec = vec_enabled() && tgv_vec_supported(w, planes, 6);
     size_t next = 0;
     for (int g = 0; g < its_eff; ++g) {
         float* yin = (g & 1) ? y1 : y0;
@@ -681,7 +718,7 @@ static int forward_impl(const float* dx, const float* dy, const float* c, const 
         if (vec) {
             FwdVecParams q{};
             q.y_in = yin; q.y_out = yout; q.x = out; q.hist = s.arena + l.hist + (size_t)g * l.vol; q.ckpt = ck;
-            q.b = b; q.c = c; q.dx = dx; q.dy = dy; q.L = Lbuf; q.N = n; q.C = ch; q.H = h; q.W = w; q.t = s.steps[g];
+            q.b = b; q.c = c; q.dx = dx; q.dy = dy; q.L = Lbuf; q.N = n; q.C = ch; q.H = h; q.W = w; q.P = P; q.t = s.steps[g];
             CNL_TRY(launch_tgv_fwd_vec(q, st));
             continue;
         }
@@ -689,6 +726,7 @@ static int forward_impl(const float* dx, const float* dy, const float* c, const 
         tgv_fwd_kernel<<<grid, NT, 0, st>>>(yin, yout, out, b, c, dx, dy, Lbuf, s.arena + l.hist + (size_t)g * l.vol, ch, h, w, s.steps[g]);
         CNL_TRY(after_launch("tgv_fwd_kernel"));
     }
+    if (staged) CNL_TRY(unpad_rows(user_out, out, (size_t)n * 3 * ch * h, w, P, st));
     s.n = n; s.ch = ch; s.h = h; s.w = w; s.its = its;
     s.have_forward = true;
     return CNL_OK;
@@ -714,8 +752,10 @@ static int backward_impl(const float* dx, const float* dy, const float* c, const
         CNL_TRY(check_cuda(cudaMemset(s.cond, 0, bytes), "cudaMemset"));
     }
     const int its_eff = 2 * (its / 2);
-    const Layout l = make_layout(n, ch, h, w, its_eff, s.sched.size());
-    const size_t plane = (size_t)h * w;
+    const bool staged = s.staged;
+    const int P = s.pitch;                        // row pitch of the arena planes (w unless staged)
+    const Layout l = make_layout(n, ch, h, P, its_eff, s.sched.size(), staged);
+    const size_t plane = (size_t)h * w;           // plane of the caller's tensors
     const size_t vol = (size_t)n * 3 * ch * plane;
     float* Lbuf = s.arena + l.L;
     unsigned int* flags = reinterpret_cast<unsigned int*>(s.arena + l.flags);
@@ -740,14 +780,31 @@ static int backward_impl(const float* dx, const float* dy, const float* c, const
     float* gb = s.arena + l.gb;
     float* acc = s.arena + l.acc;
     const float* hist = s.arena + l.hist;
-    CNL_TRY(check_cuda(cudaMemsetAsync(acc, 0, vol * sizeof(float), st), "zero acc"));
+    const size_t aplane = (size_t)h * P;          // plane of the arena buffers
+    CNL_TRY(check_cuda(cudaMemsetAsync(acc, 0, (size_t)n * 3 * ch * aplane * sizeof(float), st), "zero acc"));
     const dim3 grid((w + TW - 1) / TW, (h + TH - 1) / TH, n);
-    const void* planes[] = {dx, dy, c, b, g_dx, g_dy, g_c, g_b, g_init, s.arena};
-    const bool vec = vec_enabled() && tgv_vec_supported(w, planes, 10);
+    const void* planes[] = {dx, dy, c, b, grad, g_dx, g_dy, g_c, g_b, g_init};
+    const bool vec = vec_enabled() && (staged || tgv_vec_supported(w, planes, 10));
+    if (staged && !vec) return fail(CNL_ERR_BAD_OPTION, "the forward pass of id %d ran on zero-padded staging copies; the backward pass needs the same kernels", id);
+    float* const u_gdx = g_dx; float* const u_gdy = g_dy; float* const u_gc = g_c; float* const u_gb = g_b; float* const u_ginit = g_init;
+    if (staged) {          // same staging as in the forward pass, plus the upstream gradient and the five outputs
+        float* m = s.arena + l.stage;
+        float* v = m + 2 * (5 + ch) * l.map;
+        CNL_TRY(pad_rows(m + 0 * l.map, dx, (size_t)n * 2 * h, w, P, st));
+        CNL_TRY(pad_rows(m + 2 * l.map, dy, (size_t)n * 2 * h, w, P, st));
+        CNL_TRY(pad_rows(m + 4 * l.map, c, (size_t)n * h, w, P, st));
+        CNL_TRY(pad_rows(m + 5 * l.map, b, (size_t)n * ch * h, w, P, st));
+        CNL_TRY(pad_rows(v, grad, (size_t)n * 3 * ch * h, w, P, st));
+        dx = m; dy = m + 2 * l.map; c = m + 4 * l.map; b = m + 5 * l.map; grad = v;
+        float* o = m + (5 + ch) * l.map;
+        g_dx = o; g_dy = o + 2 * l.map; g_c = o + 4 * l.map; g_b = o + 5 * l.map; g_init = v + l.vol;
+        CNL_TRY(check_cuda(cudaMemsetAsync(g_dx, 0, (size_t)n * 2 * aplane * sizeof(float), st), "zero g_dx"));
+        CNL_TRY(check_cuda(cudaMemsetAsync(g_dy, 0, (size_t)n * 2 * aplane * sizeof(float), st), "zero g_dy"));
+    }
     CNL_TRY(ensure_dynamic_smem(tgv_rev_kernel, kRevSmemFloats * (int)sizeof(float)));
     {
         const int g = its_eff - 1;
-        tgv_seed_kernel<<<dim3((unsigned)((plane + NT - 1) / NT), n), NT, 0, st>>>(grad, hist + (size_t)g * l.vol, b, c, gb, g_c, g_b, ch, plane);
+        tgv_seed_kernel<<<dim3((unsigned)((aplane + NT - 1) / NT), n), NT, 0, st>>>(grad, hist + (size_t)g * l.vol, b, c, gb, g_c, g_b, ch, aplane);
         CNL_TRY(after_launch("tgv_seed_kernel"));
     }
     for (int g = its_eff - 2; g >= 0; --g) {
@@ -760,7 +817,7 @@ static int backward_impl(const float* dx, const float* dy, const float* c, const
             q.hist_g = hist + (size_t)g * l.vol; q.hist_gm1 = g > 0 ? hist + (size_t)(g - 1) * l.vol : nullptr; q.ckpt = ck;
             q.g_in = gin; q.g_out = gout; q.acc = acc; q.b = b; q.c = c; q.dx = dx; q.dy = dy; q.L = Lbuf;
             q.g_c = g_c; q.g_b = g_b; q.g_dx = g_dx; q.g_dy = g_dy; q.x1bar = g == 0 ? g_init : nullptr;
-            q.N = n; q.C = ch; q.H = h; q.W = w; q.t = s.steps[g]; q.typo = ck ? 0 : 1;
+            q.N = n; q.C = ch; q.H = h; q.W = w; q.P = P; q.t = s.steps[g]; q.typo = ck ? 0 : 1;
             CNL_TRY(launch_tgv_rev_vec(q, st));
             continue;
         }
@@ -769,8 +826,15 @@ static int backward_impl(const float* dx, const float* dy, const float* c, const
             g_c, g_b, g_dx, g_dy, g == 0 ? g_init : nullptr, ch, h, w, s.steps[g], ck ? 0 : 1);
         CNL_TRY(after_launch("tgv_rev_kernel"));
     }
+    if (staged) {
+        CNL_TRY(unpad_rows(u_gdx, g_dx, (size_t)n * 2 * h, w, P, st));
+        CNL_TRY(unpad_rows(u_gdy, g_dy, (size_t)n * 2 * h, w, P, st));
+        CNL_TRY(unpad_rows(u_gc, g_c, (size_t)n * h, w, P, st));
+        CNL_TRY(unpad_rows(u_gb, g_b, (size_t)n * ch * h, w, P, st));
+        CNL_TRY(unpad_rows(u_ginit, g_init, (size_t)n * 3 * ch * h, w, P, st));
+    }
     FinArgs fa{};
-    float* outs[kOut] = {g_c, g_dx, g_dy, g_b, g_init};
+    float* outs[kOut] = {u_gc, u_gdx, u_gdy, u_gb, u_ginit};
     const unsigned long long counts[kOut] = {(unsigned long long)n * plane, (unsigned long long)n * 2 * plane, (unsigned long long)n * 2 * plane,
                                              (unsigned long long)n * ch * plane, (unsigned long long)n * 3 * ch * plane};
     for (int o = 0; o < kOut; ++o) { fa.ptr[o] = outs[o]; fa.count[o] = counts[o]; fa.scale[o] = kGlobalG; fa.per_image_L[o] = 0; fa.per_image[o] = 1; }
@@ -851,13 +915,15 @@ extern "C" int cnl_tgv_read_state(int id, int kind, int idx, float* dst, void* s
     if (!sp) return rc;
     if (!sp->have_forward) return fail(CNL_ERR_NO_FORWARD, "slot %d holds no forward pass", id);
     const int its_eff = 2 * (sp->its / 2);
-    const tgv::Layout l = tgv::make_layout(sp->n, sp->ch, sp->h, sp->w, its_eff, sp->sched.size());
+    const tgv::Layout l = tgv::make_layout(sp->n, sp->ch, sp->h, sp->pitch, its_eff, sp->sched.size(), sp->staged);
     const float* src;
     size_t bytes = (size_t)sp->n * 3 * sp->ch * sp->h * sp->w * sizeof(float);
     if (kind == 0) { if (idx < 0 || idx >= its_eff) return fail(CNL_ERR_BAD_SHAPE, "iteration %d out of range", idx); src = sp->arena + l.hist + (size_t)idx * l.vol; }
     else if (kind == 1) { if (idx < 0 || idx >= (int)sp->sched.size()) return fail(CNL_ERR_BAD_SHAPE, "checkpoint %d out of range", idx); src = sp->arena + l.ckpt + (size_t)idx * l.vol; }
     else if (kind == 2) { src = sp->arena + l.L; bytes = (size_t)sp->n * sizeof(float); }
     else return fail(CNL_ERR_BAD_OPTION, "unknown kind %d", kind);
+    if (kind != 2)
+        return tgv::unpad_rows(dst, src, (size_t)sp->n * 3 * sp->ch * sp->h, sp->w, sp->pitch, static_cast<cudaStream_t>(stream));
     return check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)), "copy stored iterate");
 }
 

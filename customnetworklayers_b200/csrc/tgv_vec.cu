@@ -44,10 +44,10 @@ struct Geom {
     bool store;       // inside the interior this CTA writes
     bool my;          // a vertical edge leaves this row
     bool mx[4];       // a horizontal edge leaves pixel k
-    size_t pix;       // gy * W + gx (0 when !ok)
+    size_t pix;       // gy * pitch + gx (0 when !ok)
 };
 
-__device__ __forceinline__ Geom make_geom_at(int tx, int ty, int H, int W) {
+__device__ __forceinline__ Geom make_geom_at(int tx, int ty, int H, int W, int P) {
     Geom g;
     g.lane = threadIdx.x & 31;
     g.warp = threadIdx.x >> 5;
@@ -60,10 +60,10 @@ __device__ __forceinline__ Geom make_geom_at(int tx, int ty, int H, int W) {
     g.my = g.ok && g.gy < H - 1;
 #pragma unroll
     for (int k = 0; k < 4; ++k) g.mx[k] = g.ok && g.gx + k < W - 1;
-    g.pix = g.ok ? (size_t)g.gy * W + g.gx : 0;
+    g.pix = g.ok ? (size_t)g.gy * P + g.gx : 0;
     return g;
 }
-__device__ __forceinline__ Geom make_geom(int H, int W) { return make_geom_at(blockIdx.x, blockIdx.y, H, W); }
+__device__ __forceinline__ Geom make_geom(int H, int W, int P) { return make_geom_at(blockIdx.x, blockIdx.y, H, W, P); }
 
 // Edge weights of the lane's four triangles, scaled by 1/Lipschitz and zero where no edge leaves the pixel.
 struct Weights {
@@ -125,8 +125,8 @@ tgv_fwd_vec_kernel(const __grid_constant__ FwdVecParams p) {
     __shared__ float4 sh[2][3][kTgvWarps][32];        // per channel parity: Fy, G1y, G2y of each warp's row
     __shared__ float4 slots[5][kNT];                  // private landing slots of the pointwise operands
     float4* slot = &slots[0][threadIdx.x];
-    const Geom g = make_geom(p.H, p.W);
-    const size_t plane = (size_t)p.H * p.W;
+    const Geom g = make_geom(p.H, p.W, p.P);
+    const size_t plane = (size_t)p.H * p.P;
     const size_t n = blockIdx.z;
     const float L = p.L[n];
     const Weights w = load_weights(p.dx, p.dy, n, plane, g, L);
@@ -134,8 +134,8 @@ tgv_fwd_vec_kernel(const __grid_constant__ FwdVecParams p) {
     for (int ch = 0; ch < p.C; ++ch) {
         const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
         const float4 yu4 = ld4(p.y_in + o, g.ok), y14 = ld4(p.y_in + o + cstride, g.ok), y24 = ld4(p.y_in + o + 2 * cstride, g.ok);
-        const float4 du4 = ld4(p.y_in + o + p.W, g.okb), d14 = ld4(p.y_in + o + cstride + p.W, g.okb),
-                     d24 = ld4(p.y_in + o + 2 * cstride + p.W, g.okb);
+        const float4 du4 = ld4(p.y_in + o + p.P, g.okb), d14 = ld4(p.y_in + o + cstride + p.P, g.okb),
+                     d24 = ld4(p.y_in + o + 2 * cstride + p.P, g.okb);
         // pointwise operands are only needed where the CTA stores and not before the divergence: fetched
         // asynchronously so that they hold no registers meanwhile
         cp_async16(slot + 0 * kNT, p.x + o, g.store);
@@ -222,14 +222,14 @@ tgv_fwd_pipe_kernel(const __grid_constant__ FwdVecParams p, int tiles_x, int til
     float4* sw = fwd_smem + 14 * kNT + threadIdx.x;      // [4][kNT]: wx, wy, beta_x, beta_y of the tile
     float4(*sbelow)[32] = reinterpret_cast<float4(*)[32]>(fwd_smem + 18 * kNT);                      // [3]: row under the region
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const size_t plane = (size_t)p.H * p.W;
+    const size_t plane = (size_t)p.H * p.P;
     const size_t cstride = (size_t)p.C * plane;
     const int ntiles = tiles_x * tiles_y * p.N;
 
     auto tile_geom = [&](int tile, size_t& n) -> Geom {
         const int tx = tile % tiles_x, q = tile / tiles_x;
         n = (size_t)(q / tiles_y);
-        return make_geom_at(tx, q % tiles_y, p.H, p.W);
+        return make_geom_at(tx, q % tiles_y, p.H, p.W, p.P);
     };
     // starts fetching every operand of (tile, ch); the edge weights only with the first channel of a tile
     auto issue = [&](int tile, int ch) {
@@ -240,7 +240,7 @@ tgv_fwd_pipe_kernel(const __grid_constant__ FwdVecParams p, int tiles_x, int til
 #pragma unroll
             for (int q = 0; q < 3; ++q) {
                 cp_async16(&sy[q][warp][lane], p.y_in + o + q * cstride, g.ok);
-                if (warp == kTgvWarps - 1) cp_async16(&sbelow[q][lane], p.y_in + o + q * cstride + (g.okb ? p.W : 0), g.okb);
+                if (warp == kTgvWarps - 1) cp_async16(&sbelow[q][lane], p.y_in + o + q * cstride + (g.okb ? p.P : 0), g.okb);
                 cp_async16(sx + q * kNT, p.x + o + q * cstride, g.store);
             }
             cp_async16(sx + 3 * kNT, p.b + (n * p.C + ch) * plane + g.pix, g.store);
@@ -478,8 +478,8 @@ tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
     float4(*sh_row)[kTgvWarps][32] = reinterpret_cast<float4(*)[kTgvWarps][32]>(rev_smem);             // [6]: y and g planes of each warp's row
     float4(*sh_flux)[kTgvWarps][32] = reinterpret_cast<float4(*)[kTgvWarps][32]>(rev_smem + 6 * kNT);  // [3]: psi2, chi1y, down-going chi2y
     float4* slot = rev_smem + 9 * kNT + threadIdx.x;   // [6][kNT] private landing slots of the pointwise operands
-    const Geom g = make_geom(p.H, p.W);
-    const size_t plane = (size_t)p.H * p.W;
+    const Geom g = make_geom(p.H, p.W, p.P);
+    const size_t plane = (size_t)p.H * p.P;
     const size_t n = blockIdx.z;
     const float L = p.L[n];
     const Weights w = load_weights(p.dx, p.dy, n, plane, g, L);
@@ -501,7 +501,7 @@ tgv_rev_vec_kernel(const __grid_constant__ RevVecParams p) {
         sh_row[0][g.warp][g.lane] = own.yu; sh_row[1][g.warp][g.lane] = own.y1; sh_row[2][g.warp][g.lane] = own.y2;
         sh_row[3][g.warp][g.lane] = own.gu; sh_row[4][g.warp][g.lane] = own.g1; sh_row[5][g.warp][g.lane] = own.g2;
         RowState below;
-        if (g.warp == kTgvWarps - 1) below = load_row(p, o + p.W, ob + p.W, oc + p.W, cstride, g.okb);   // row under the region
+        if (g.warp == kTgvWarps - 1) below = load_row(p, o + p.P, ob + p.P, oc + p.P, cstride, g.okb);   // row under the region
         __syncthreads();
         if (g.warp < kTgvWarps - 1) {
             below.yu = sh_row[0][g.warp + 1][g.lane]; below.y1 = sh_row[1][g.warp + 1][g.lane]; below.y2 = sh_row[2][g.warp + 1][g.lane];
@@ -571,7 +571,7 @@ tgv_rev_pipe_kernel(const __grid_constant__ RevVecParams p, int tiles_x, int til
     float4* sw = rp_smem + 19 * kNT + threadIdx.x;             // [4][kNT] edge weights of the tile
     float4(*sbelow)[32] = reinterpret_cast<float4(*)[32]>(rp_smem + 23 * kNT);                   // [9] row under the region
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const size_t plane = (size_t)p.H * p.W;
+    const size_t plane = (size_t)p.H * p.P;
     const size_t cstride = (size_t)p.C * plane;
     const int ntiles = tiles_x * tiles_y * p.N;
     const float* ysrc = p.ckpt ? p.ckpt : p.hist_g;
@@ -580,7 +580,7 @@ tgv_rev_pipe_kernel(const __grid_constant__ RevVecParams p, int tiles_x, int til
     auto tile_geom = [&](int tile, size_t& n) -> Geom {
         const int tx = tile % tiles_x, q = tile / tiles_x;
         n = (size_t)(q / tiles_y);
-        return make_geom_at(tx, q % tiles_y, p.H, p.W);
+        return make_geom_at(tx, q % tiles_y, p.H, p.W, p.P);
     };
     auto issue = [&](int tile, int ch) {
         if (tile < ntiles) {
@@ -589,7 +589,7 @@ tgv_rev_pipe_kernel(const __grid_constant__ RevVecParams p, int tiles_x, int til
             const size_t o = n * 3 * cstride + (size_t)ch * plane + g.pix;
             const size_t ob = (n * p.C + ch) * plane + g.pix, oc = n * plane + g.pix;
             const bool last = warp == kTgvWarps - 1;
-            const size_t dn = g.okb ? (size_t)p.W : 0;         // one image row further down
+            const size_t dn = g.okb ? (size_t)p.P : 0;         // one image row further down
 #pragma unroll
             for (int q = 0; q < 3; ++q) {
                 cp_async16(&sy[q][warp][lane], ysrc + o + q * cstride, g.ok);

@@ -4,8 +4,8 @@
 // one row, every lane four consecutive pixels of it (one 16-byte vector per plane).  The first row and the first /
 // last lane of the region are halo: they only supply fluxes / neighbour values, so the CTA stores an interior of
 // (kTgvWarps - 1) x 120 pixels.  Horizontal neighbours travel by warp shuffle, vertical ones through one
-// shared-memory row per warp and plane.  Requires W % 4 == 0 and 16-byte aligned planes; other shapes use the
-// scalar shared-memory kernels.
+// shared-memory row per warp and plane.  Needs a row pitch divisible by 4 and 16-byte aligned planes; the driver
+// stages zero-padded copies of tensors that do not have them.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -28,6 +28,7 @@ struct FwdVecParams {
     const float* dy;        // [N][2][H][W] = wy, beta_y
     const float* L;         // [N] 1/Lipschitz per image
     int N, C, H, W;
+    int P;                  // row pitch of every plane in floats (multiple of 4, >= W; pad columns hold zeros)
     float t;
 };
 
@@ -49,6 +50,7 @@ struct RevVecParams {
     float* g_dy;
     float* x1bar;           // if non-null: dL/dx of this iteration is stored here (last reverse step)
     int N, C, H, W;
+    int P;                  // row pitch in floats, as in FwdVecParams
     float t;
     int typo;               // reproduce the reference's factor in the v2 term arriving from the triangle above
 };

@@ -246,3 +246,41 @@ def test_full_size_properties():
         for pid in (7, 8):
             ext.set_option(pid, 1, 1)
             ext.release(pid)
+
+
+@pytest.mark.gpu
+def test_widths_and_pointers_that_need_staging():
+    """Rows that are not a multiple of four floats and misaligned tensors run the register-tiled kernels on zero-padded
+    copies: oracle parity on a 1242-pixel-wide problem, and the bits of the aligned call for a misaligned one."""
+    from customnetworklayers_b200 import tgvInpaint_cuda_ext as ext
+    n, ch, h, w, its = 2, 2, 20, 1242, 6
+    I = make_tgv_inputs(n, ch, h, w, seed=321)
+    I["init"][:, 1:] = 0.1 * I["grad"][:, 1:]
+    D = {k: v.cuda() for k, v in I.items()}
+    ext.release(3)
+    ext.set_option(3, 1, 0)
+    sol, hist, cky, L, grads = _run_cuda(ext, D, its, 3, n, ch, h, w)
+    r_sol, r_hist, r_cky, _, r_L = G.tgv_forward_history(I["dx"], I["dy"], I["c"], I["b"], I["init"], its)
+    assert_close(sol, r_sol, "solution")
+    assert_close(hist, r_hist, "history")
+    ref = G.tgv_backward(I["dx"], I["dy"], I["c"], I["b"], I["grad"], its, hist.cpu(), cky.cpu())
+    for name, g, r in zip(NAMES, grads, ref):
+        assert_close(g, r, name)
+
+    n, ch, h, w, its = 1, 2, 16, 64, 8
+    I = make_tgv_inputs(n, ch, h, w, seed=322)
+    D = {k: v.cuda() for k, v in I.items()}
+    sol_a, _, _, _, g_a = _run_cuda(ext, D, its, 3, n, ch, h, w)
+
+    def shifted(t):              # same values, storage offset of one float
+        buf = torch.empty(t.numel() + 1, device=t.device, dtype=t.dtype)
+        view = buf[1:].view(t.shape)
+        view.copy_(t)
+        return view
+    U = {k: shifted(v) for k, v in D.items()}
+    sol_u, _, _, _, g_u = _run_cuda(ext, U, its, 3, n, ch, h, w)
+    assert torch.equal(sol_a, sol_u)
+    for name, a, b in zip(NAMES, g_a, g_u):
+        assert torch.equal(a, b), name
+    ext.set_option(3, 1, 1)
+    ext.release(3)
