@@ -32,6 +32,7 @@ WORKLOADS = {
     "prof": (8, 2, 384, 1280, 20),       # profiling case with the launch geometry of cfg1 and a fifth of its history
     "cfg2": (8, 2, 436, 1024, 100),      # TGV-FISTA (secondary workload, run with --workload cfg2)
     "cfg2small": (2, 2, 436, 1024, 10),  # TGV profiling case
+    "cfg2prof": (8, 2, 436, 1024, 6),    # TGV profiling case with the launch geometry of cfg2 (persistent kernels)
     "cfg4": (32, 2, 384, 1280, 0),        # learnable 7x7 weighted-median filter (no iterations)
     "median": (4, 49, 384, 1280, 0),      # the reference's selection layer on a materialised [N,H,W,K] weight volume
     "quadfit": (4, 32, 384, 1280, 0),     # the reference's quadratic fit on two feature maps and a flow
