@@ -91,3 +91,29 @@ def test_filter_module_learns_through_normalisation():
     x2 = flow.cuda().requires_grad_(True)
     m(x2).backward(grad.cuda())
     assert torch.equal(x2.grad, x.grad)
+
+
+@pytest.mark.gpu
+def test_full_size_properties():
+    """Size-independent properties at the benchmark's full size (batch 32, 2x384x1280, 7x7): the output is the window
+    value at the reported tap, the pass-through gradient conserves mass, two runs give the same bits."""
+    from customnetworklayers_b200 import wmedian as wm
+    n, c, h, w, k = 32, 2, 384, 1280, 7
+    flow, wts, grad = make_median_filter_inputs(n, c, h, w, k=k, seed=1238)
+    flow, grad = flow.cuda(), grad.cuda()
+    p = (wts / wts.sum()).float().cuda()
+    out, tap, alpha = wm.forward(flow, p, k)
+    g_flow, g_p = wm.backward(flow, p, tap, alpha, grad, k)
+    out2, tap2, alpha2 = wm.forward(flow, p, k)
+    g_flow2, g_p2 = wm.backward(flow, p, tap2, alpha2, grad, k)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2) and torch.equal(tap, tap2) and torch.equal(g_flow, g_flow2) and torch.equal(g_p, g_p2)
+    assert int((tap < 0).sum()) == 0 and int(tap.max()) < k * k          # normalised weights always cross 0.5
+    hh = torch.arange(h, device="cuda").view(1, 1, h, 1)
+    ww = torch.arange(w, device="cuda").view(1, 1, 1, w)
+    th = (hh + torch.div(tap, k, rounding_mode="floor") - k // 2).clamp(0, h - 1)
+    tw = (ww + tap % k - k // 2).clamp(0, w - 1)
+    picked = flow.reshape(n * c, h * w).gather(1, (th * w + tw).reshape(n * c, h * w).long()).view_as(flow)
+    assert torch.equal(out, picked), "the output must be the window value at the selected tap"
+    assert abs(float(g_flow.double().sum()) - float(grad.double().sum())) < 1e-2 * max(1.0, float(grad.double().abs().sum()) ** 0.5)
+    assert bool(torch.isfinite(g_p).all())
