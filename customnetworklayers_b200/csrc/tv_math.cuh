@@ -183,32 +183,6 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __
 __device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(b, f2(-1.0f), a); }
 __device__ __forceinline__ float2 neg2(float2 a) { return make_float2(-a.x, -a.y); }
 
-// fluxes of two triangles given their differences d1 = y - y_right, d2 = y - y_down
-__device__ __forceinline__ void tri_flux2(float2 d1, float2 d2, float2 wx, float2 wy, float2& fx, float2& fy) {
-    const float2 wd1 = mul2(wx, d1);
-    const float2 wd2 = mul2(wy, d2);
-    const float2 A = fma2(wd1, d1, mul2(wd2, d2));
-    const float2 dr = mul2(f2(kDelta), f2(rsqrt_approx(A.x), rsqrt_approx(A.y)));
-    const float2 s = f2(fminf(1.0f, dr.x), fminf(1.0f, dr.y));
-    fx = mul2(s, wd1);
-    fy = mul2(s, wd2);
-}
-
-__device__ __forceinline__ float2 prox_huber2(float2 x05, float2 b, float2 c) {
-    const float2 opc = add2(c, f2(1.0f));
-    const float2 inv = f2(rcp_approx(opc.x), rcp_approx(opc.y));
-    float2 x = mul2(fma2(c, b, x05), inv);
-    const float2 lo = sub2(x05, c);
-    const float2 hi = add2(x05, c);
-    const float2 bp = add2(b, f2(1.0f));
-    const float2 bm = add2(b, f2(-1.0f));
-    if (lo.x > bp.x) x.x = lo.x;
-    if (lo.y > bp.y) x.y = lo.y;
-    if (hi.x < bm.x) x.x = hi.x;
-    if (hi.y < bm.y) x.y = hi.y;
-    return x;
-}
-
 // y_{k+1} rebuilt from two stored pre-prox iterates for two pixels (see rederive_y_fast)
 __device__ __forceinline__ float2 rederive_y2(float2 x05, float2 x05m, float2 b, float2 c, float t) {
     const float2 opc = add2(c, f2(1.0f));
