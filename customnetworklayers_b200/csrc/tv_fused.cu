@@ -165,13 +165,6 @@ __device__ __forceinline__ void load_maps(const P& p, const TileGeom& g, size_t 
     }
 }
 
-// After fused step j only rows j+1 .. 30-j of the region can still influence what the CTA stores, so a warp whose
-// two rows lie outside that band skips the update of step j (it still publishes its rows and its last-row flux,
-// which its neighbours read).  The condition is uniform per warp.
-__device__ __forceinline__ bool rows_needed(int warp, int j) {
-    return (warp * kRows + kRows - 1 >= j + 1) && (warp * kRows <= kRegionH - 2 - j);
-}
-
 // Scales / masks edge weights that were fetched raw (see load_maps).
 __device__ __forceinline__ void finish_maps(const TileGeom& g, int H, int W, float4 (&wx)[kRows], float4 (&wy)[kRows]) {
 #pragma unroll
@@ -240,7 +233,6 @@ tv_fwd_fused_kernel(const __grid_constant__ FwdFusedParams p) {
             sh_f[g.warp][g.lane] = fyl;
             __syncthreads();
             float4 fyc = (g.warp > 0) ? sh_f[g.warp - 1][g.lane] : zero4();    // vertical flux arriving from above
-            if (!rows_needed(g.warp, j)) continue;           // pure halo rows at this step: only their fluxes were needed
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
                 float4 fx, fy;
@@ -346,7 +338,6 @@ tv_fwd_pipe_kernel(const __grid_constant__ FwdFusedParams p, int tiles_x, int ti
                 sh_f[g.warp][g.lane] = fyl;
                 __syncthreads();
                 float4 fyc = (g.warp > 0) ? sh_f[g.warp - 1][g.lane] : zero4();
-                if (!rows_needed(g.warp, j)) continue;       // pure halo rows at this step: only their fluxes were needed
 #pragma unroll
                 for (int r = 0; r < kRows; ++r) {
                     float4 fx, fy;
@@ -535,12 +526,6 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
             add4(sh_dwy[(kRows - 1) * kThreads + threadIdx.x], dwyl);
             __syncthreads();
             float4 p2c = (g.warp > 0) ? sh_p[g.warp - 1][g.lane] : zero4();
-            if (!rows_needed(g.warp, j)) {                   // pure halo rows at this step: keep the history pipeline moving only
-                cp_async_wait_all();
-#pragma unroll
-                for (int r = 0; r < kRows; ++r) { xh[r] = xhm[r]; xhm[r] = (j + 2 <= K) ? sh_xn[r * kThreads + threadIdx.x] : zero4(); }
-                continue;
-            }
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
                 float4 p1, p2;
