@@ -124,7 +124,7 @@ def cpu_fwd_bwd(I, its):
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the 4-iteration kernels at the launch
 # geometry of cfg1 / prof (batch 8, 2x384x1280; 1408 tiles), from an `ncu --set full` capture of one launch each
 # (profiles/tv_fused_kernels_prof_and_cfg1.md).  Other geometries have no capture and report null.
-NCU_TRAFFIC = {(8, 2, 384, 1280): {"reverse": 528.3e6, "forward": 307.3e6}}
+NCU_TRAFFIC = {(8, 2, 384, 1280): {"reverse": 523.0e6, "forward": 307.7e6}}
 
 
 def cpu_baseline_sample(ch, h, w, its, budget_s=20.0):
