@@ -20,13 +20,14 @@ class TVInpaintingFunction(Function):
         ctx.save_for_backward(dx, dy, dc, db)
         ctx.its = int(its)
         ctx.pid = int(pid)
+        ctx.generation = tvInpaint_cuda_ext.forward_count(pid, db.device)
         return sol
 
     @staticmethod
     def backward(ctx, grad_sol):
         dx, dy, dc, db = ctx.saved_tensors
         d_oGx, d_oGy, d_oGc, d_oGb, d_oGi = tvInpaint_cuda_ext.backward(grad_sol.contiguous(), dx, dy, dc, db,
-                                                                       ctx.its, ctx.pid)
+                                                                       ctx.its, ctx.pid, generation=ctx.generation)
         return d_oGx, d_oGy, d_oGc, d_oGb, d_oGi, None, None
 
 

@@ -21,6 +21,7 @@ SIGNATURES = {
     "cnl_tv_set_option": (c_int, [c_int, c_int, c_int]),
     "cnl_tv_get_timing": (c_int, [c_int, c_void_p]),
     "cnl_tv_run_count": (c_int, [c_int]),
+    "cnl_tv_forward_count": (c_int, [c_int]),
     "cnl_launch_count": (c_ulonglong, []),
     "cnl_tv_lambda_grad": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]),
     "cnl_dot_scratch_floats": (c_int, []),

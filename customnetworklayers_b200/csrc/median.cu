@@ -11,6 +11,7 @@ namespace cnl {
 
 constexpr int kMedWarps = 4;
 constexpr int kMedThreads = kMedWarps * 32;
+constexpr int kMedMaxBins = 453;          // 128 staged rows of (k | 1) floats fill the 227 KB of shared memory a block may use
 
 __device__ __forceinline__ int med_stride(int k) { return k | 1; }
 
@@ -155,11 +156,14 @@ median_backward_kernel(const float* __restrict__ vol, const float* __restrict__ 
 static int median_check(const void* a, const void* b, int n, int h, int w, int k) {
     if (!a || !b) return fail(CNL_ERR_NULL, "null pointer argument");
     if (n < 1 || h < 1 || w < 1 || k < 1) return fail(CNL_ERR_BAD_SHAPE, "n, h, w, k must be >= 1 (got %d, %d, %d, %d)", n, h, w, k);
-    if (k > 1024) return fail(CNL_ERR_BAD_SHAPE, "at most 1024 bins are supported (got %d)", k);
+    if (k > kMedMaxBins)
+        return fail(CNL_ERR_BAD_SHAPE, "at most %d bins are supported (got %d): a block stages %d rows of k floats in shared memory",
+                    kMedMaxBins, k, kMedWarps * 32);
     return CNL_OK;
 }
 
 static int median_smem(int k) { return kMedWarps * 32 * (k | 1) * (int)sizeof(float); }
+static_assert(kMedWarps * 32 * (kMedMaxBins | 1) * (int)sizeof(float) <= 227 * 1024, "staging rows must fit the shared memory of one block");
 
 template <typename Kern>
 static int median_prepare(Kern kern, int k) {

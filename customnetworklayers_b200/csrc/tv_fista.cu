@@ -326,6 +326,7 @@ struct Slot {
     int n = 0, ch = 0, h = 0, w = 0, its = 0;
     bool have_forward = false;
     int run = 0;
+    int generation = 0;              // forward passes stored on this slot so far; survives release
     int opt_conditioner = 1;
     int opt_fuse = 0;
     int opt_timing = 0;
@@ -614,6 +615,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
         s.n = n; s.ch = ch; s.h = h; s.w = w; s.its = its;
         s.window_valid = recompute;
         s.have_forward = true;
+        s.generation += 1;
         return CNL_OK;
     }
     CNL_TRY(check_cuda(cudaMemcpyAsync(out, init, vol_bytes, cudaMemcpyDeviceToDevice, st), "copy init->x"));
@@ -646,6 +648,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
     }
     s.n = n; s.ch = ch; s.h = h; s.w = w; s.its = its;
     s.have_forward = true;
+    s.generation += 1;
     return CNL_OK;
 }
 
@@ -876,8 +879,9 @@ extern "C" int cnl_tv_release(int id) {
     if (sp->events_ready)
         for (int i = 0; i < Slot::kRing; ++i)
             for (int j = 0; j < 2; ++j) { cudaEventDestroy(sp->ev_fwd[i][j]); cudaEventDestroy(sp->ev_rev[i][j]); }
-    const int keep_cond = sp->opt_conditioner, keep_fuse = sp->opt_fuse, keep_rec = sp->opt_recompute;
+    const int keep_cond = sp->opt_conditioner, keep_fuse = sp->opt_fuse, keep_rec = sp->opt_recompute, keep_gen = sp->generation;
     *sp = Slot();
+    sp->generation = keep_gen;
     sp->opt_conditioner = keep_cond;
     sp->opt_fuse = keep_fuse;
     sp->opt_recompute = keep_rec;
@@ -925,6 +929,8 @@ extern "C" int cnl_tv_num_checkpoints(int id) {
 
 extern "C" int cnl_tv_set_option(int id, int option, int value) {
     if (id < 0 || id >= CNL_NUM_IDS) return fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1);
+    if (option < CNL_OPT_CONDITIONER || option > CNL_OPT_RECOMPUTE)      // rejected before anything touches the device
+        return fail(CNL_ERR_BAD_OPTION, "unknown option %d", option);
     std::lock_guard<std::mutex> lock(g_mutex);
     int rc;
     Slot* sp = get_slot(id, &rc);
@@ -976,6 +982,14 @@ extern "C" int cnl_tv_run_count(int id) {
     int rc;
     Slot* sp = get_slot(id, &rc);
     return sp ? sp->run : -1;
+}
+
+extern "C" int cnl_tv_forward_count(int id) {
+    if (id < 0 || id >= CNL_NUM_IDS) { fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1); return -1; }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int rc;
+    Slot* sp = get_slot(id, &rc);
+    return sp ? sp->generation : -1;
 }
 
 extern "C" int cnl_dot_scratch_floats(void) { return 2 * kDotBlocks; }

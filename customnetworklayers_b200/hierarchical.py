@@ -23,7 +23,7 @@ from .dist import allreduce_scalar_grads
 class HierarchicalTV(nn.Module):
     def __init__(self, levels: int = 3, its: int = 50, first_id: int = 0):
         super().__init__()
-        if not 0 <= first_id and first_id + levels <= 10:
+        if levels < 1 or not (0 <= first_id and first_id + levels <= 10):
             raise ValueError("levels need distinct ids within 0..9")
         self.levels, self.its, self.first_id = levels, its, first_id
         self.lam = nn.Parameter(torch.ones(levels))

@@ -47,14 +47,27 @@ def forward(d_x, d_y, d_c, d_b, d_i, its: int, id: int):
     return [solution]
 
 
-def backward(d_iGf, d_x, d_y, d_c, d_b, its: int, id: int):
-    """tvInpaint_backward (TVInpaintFista_cuda.cpp:99-143): returns [gX, gY, gC, gB, gI]."""
+def backward(d_iGf, d_x, d_y, d_c, d_b, its: int, id: int, generation=None):
+    """tvInpaint_backward (TVInpaintFista_cuda.cpp:99-143): returns [gX, gY, gC, gB, gI].
+
+    `generation` (optional, no reference counterpart): the value forward_count(id) had right after the forward pass
+    this call belongs to; if another forward pass has replaced the slot's history since, the call raises instead of
+    returning gradients of the wrong problem."""
     for t, name in ((d_x, "d_x"), (d_y, "d_y"), (d_c, "d_c"), (d_b, "d_b"), (d_iGf, "d_iGf")):
         _check_input(t, name)
     n, ch, h, w = d_b.shape
     if d_iGf.shape != d_b.shape:
         raise RuntimeError("d_iGf must have the shape of d_b")
+    for t, name in ((d_x, "d_x"), (d_y, "d_y"), (d_c, "d_c")):
+        if tuple(t.shape) != (n, 1, h, w):
+            raise RuntimeError(f"{name} must have shape [N,1,H,W] matching d_b")
     lib = _lib.load()
+    if generation is not None:
+        with torch.cuda.device(d_b.device):
+            now = lib.cnl_tv_forward_count(int(id))
+        if now != int(generation):
+            raise RuntimeError(f"tvInpaint backward: slot {id} holds forward pass {now}, not {generation}: another forward "
+                               f"call on this id replaced the history (give each live layer its own id)")
     g_x = torch.empty_like(d_x)
     g_y = torch.empty_like(d_y)
     g_c = torch.empty_like(d_c)
@@ -84,6 +97,15 @@ def dummy_only():
 def release(id: int) -> None:
     """Frees the device buffers of slot `id` on the current device."""
     _lib.check(_lib.load().cnl_tv_release(int(id)), "tvInpaint release")
+
+
+def forward_count(id: int, device=None) -> int:
+    """Forward passes stored on slot `id` of `device` (default: current device) so far; see backward(generation=...)."""
+    with torch.cuda.device(device):
+        k = _lib.load().cnl_tv_forward_count(int(id))
+    if k < 0:
+        raise RuntimeError("tvInpaint forward_count: " + _lib.last_error())
+    return k
 
 
 def set_option(id: int, option: int, value: int) -> None:

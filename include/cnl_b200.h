@@ -104,6 +104,12 @@ int cnl_tv_get_timing(int id, double* out_host);
  * negative on error. */
 int cnl_tv_run_count(int id);
 
+/* Number of forward passes stored on slot `id` of the current device since the library was loaded (not reset by
+ * cnl_tv_release); negative on error.  A slot keeps only its LAST forward pass, like the reference's idStruct
+ * (cudaTV/cudaCode/TVInpaintFista.h:18-37, checkpoints freed on re-forward): a caller that remembers this value after
+ * its forward call can tell, before calling backward, whether another forward pass has replaced its history. */
+int cnl_tv_forward_count(int id);
+
 /* Kernel launches enqueued by this library on the calling thread's process since load (for benchmark accounting). */
 unsigned long long cnl_launch_count(void);
 
@@ -125,7 +131,10 @@ int cnl_dot_scratch_floats(void);
  * Limits: count <= cnl_tv_lambda_grad_static_max_count() (16,777,216), otherwise CNL_ERR_BAD_SHAPE.  All calls on a
  * device share the array: calls that overlap on the GPU (different streams) race; calls on one stream are safe.
  * The first call on each device resolves the array's address and should be made outside stream capture.
- * Allocates nothing (no cudaMalloc / cudaFree).
+ * The entry point itself calls no cudaMalloc / cudaFree and no allocating library routine.  One thing it cannot
+ * avoid: when the CUDA runtime loads modules lazily, the first cudaGetSymbolAddress or kernel launch on a device
+ * loads this library's module, and that one-time load may synchronise and allocate inside the driver.  Callers that
+ * must never see that inside their loop make one warm-up call per device at initialisation, outside capture.
  */
 int cnl_tv_lambda_grad_static(const float* g_c, const float* c_raw, long long count, float* out, void* stream);
 long long cnl_tv_lambda_grad_static_max_count(void);
@@ -140,7 +149,8 @@ long long cnl_tv_lambda_grad_static_max_count(void);
  *   index [n][h][w] (optional, may be null): crossing bin, -1 if none.  No reference counterpart (debug / tests).
  *   grad  [n][2][h][w] upstream gradient; gvol [n][h][w][k] gradient w.r.t. vol (fully overwritten).
  * Unlike the reference, n > 1 is decoded correctly (the reference decodes pixel indices against the 2-channel
- * output, medimax.cu:18-22).
+ * output, medimax.cu:18-22).  k <= 453: a block stages 128 rows of k floats in shared memory; larger k returns
+ * CNL_ERR_BAD_SHAPE (the reference takes any numDisp).
  */
 int cnl_median_forward(const float* vol, float* out, int* index, int n, int h, int w, int k, void* stream);
 int cnl_median_backward(const float* vol, const float* grad, float* gvol, int n, int h, int w, int k, void* stream);

@@ -1,7 +1,7 @@
 """Shared helpers of the parity tests: error norms and tolerances."""
 import torch
 
-# north-star tolerance for fp32 forward and backward: 1e-4 relative, measured norm-wise per output tensor
+# tolerance for fp32 forward and backward: 1e-4 relative, measured norm-wise per output tensor
 REL_TOL = 1e-4
 
 

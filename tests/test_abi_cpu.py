@@ -47,7 +47,9 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.cnl_tv_forward(None, 1, 1, 1, 1, 1, 1, 2, 8, 8, 20, 0, None) == 7   # null pointer
     assert lib.cnl_tv_backward(1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 2, 8, 8, 20, 12, None) == 1
     assert lib.cnl_tv_release(10) == 1
-    assert lib.cnl_tv_set_option(0, 99, 1) == 1 or lib.cnl_tv_set_option(0, 99, 1) in (6, 8)
+    assert lib.cnl_tv_set_option(0, 99, 1) == 8      # unknown option: rejected before the device is touched
+    assert "unknown option 99" in _lib.last_error()
+    assert lib.cnl_tv_set_option(10, 1, 1) == 1
 
 
 def test_python_layer_refuses_cpu_tensors():
@@ -64,3 +66,20 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+def test_median_bin_limit_is_the_documented_one(lib):
+    from customnetworklayers_b200 import _lib
+    # validation precedes any device work: 454 bins do not fit the staging rows of a block, 0 bins is no problem at all
+    assert lib.cnl_median_forward(1, 1, None, 1, 4, 4, 454, None) == 2
+    assert "at most 453 bins" in _lib.last_error()
+    assert lib.cnl_median_backward(1, 1, 1, 1, 4, 4, 454, None) == 2
+    assert lib.cnl_median_forward(1, 1, None, 1, 4, 4, 0, None) == 2
+
+
+def test_hierarchy_rejects_id_ranges_outside_the_ten_slots():
+    from customnetworklayers_b200.hierarchical import HierarchicalTV
+    for first_id, levels in ((8, 3), (-1, 2), (10, 1), (0, 11), (0, 0)):
+        with pytest.raises(ValueError):
+            HierarchicalTV(levels=levels, first_id=first_id)
+    assert HierarchicalTV(levels=3, first_id=7).first_id == 7

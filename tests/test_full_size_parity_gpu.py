@@ -1,0 +1,164 @@
+"""Parity at the benchmarked image size and iteration count, through the C ABI.
+
+One image of the headline workload (2 x 384 x 1280, 100 iterations: 16 x 11 tiles of the temporally blocked kernels,
+every checkpoint segment of ten iterations) and one of the TGV workload (2 x 436 x 1024, 100 iterations) are compared
+  * with the float64 CPU oracle: solution, every stored iterate and every checkpoint at 1e-4, and the reverse sweep
+    on exactly the iterates the device stored at 1e-4 (the sweep is discontinuous at the Huber thresholds);
+  * live with the reference's own kernels (oracle/_ref, built unmodified) where the size is one they handle safely:
+    they read one value before their bounds check, so heights must be multiples of 16 and widths multiples of 32.
+    384 x 1280 qualifies; 436 does not, so the TGV kernels are run at 432 x 1024.
+End to end (each side runs its own fp32 forward pass) the gradient difference is printed in both norms next to the
+oracle's own fp32-vs-fp64 difference and bounded, in both norms, by the larger of 1e-4 and five times that difference.
+"""
+import pytest
+import torch
+
+from customnetworklayers_b200.synthetic import make_tgv_inputs
+from oracle import ref_cuda
+from oracle import tgv_ref as G
+from oracle import tv_ref as R
+from tests.parity import REL_TOL, assert_close, rel_errors
+
+pytestmark = pytest.mark.gpu
+
+TV_NAMES = ["g_wx", "g_wy", "g_c", "g_b", "g_init"]
+TGV_NAMES = ["g_dx", "g_dy", "g_c", "g_b", "g_init"]
+
+
+def _dev(I):
+    return {k: v.cuda() for k, v in I.items()}
+
+
+def _bounded_in_both_norms(what, name, err, gap):
+    """err, gap: (max-norm, l2) relative differences; the bound is max(1e-4, 5 x gap) per norm."""
+    for norm, e, g in zip(("max", "l2"), err, gap):
+        bound = max(REL_TOL, 5.0 * g)
+        assert e <= bound, f"{what}: {name} {norm}-norm {e:.2e} > {bound:.2e} (oracle fp32-vs-fp64 {g:.2e})"
+
+
+def test_tv_full_size_image_matches_oracle_and_reference_kernels():
+    from customnetworklayers_b200 import _lib, tvInpaint_cuda_ext as ext
+    ch, h, w, its = 2, 384, 1280, 100
+    I = R.make_inputs(1, ch, h, w, seed=20241)
+    D = _dev(I)
+    pid = 4
+    ext.release(pid)
+    ext.set_option(pid, _lib.OPT_CONDITIONER, 0)
+    try:
+        sol = ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, pid)[0]
+        hist, cky = ext.read_history(pid, D["b"], its)
+        grads = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, pid)
+        torch.cuda.synchronize()
+        hist, cky = hist.cpu(), cky.cpu()
+        # --- float64 oracle, forward end to end
+        o_sol, o_hist, o_cky = R.tv_forward_history(I["wx"], I["wy"], I["c"], I["b"], I["init"], its)
+        print("solution", rel_errors(sol, o_sol), "history", rel_errors(hist, o_hist), "checkpoints", rel_errors(cky, o_cky))
+        assert_close(sol, o_sol, "solution")
+        assert_close(hist, o_hist, "history")
+        assert_close(cky, o_cky, "checkpointed y")
+        # --- float64 oracle, reverse sweep on the device's iterates
+        ref = R.tv_backward_raw(I["wx"], I["wy"], I["c"], I["b"], I["grad"], its, None, hist=hist, ckpt_y=cky)
+        for name, g, r in zip(TV_NAMES, grads, ref):
+            print(name, "reverse sweep on device iterates", rel_errors(g, r))
+            assert_close(g, r, name)
+        # --- end to end, both norms, beside the oracle's own fp32-vs-fp64 gap
+        g64 = R.tv_backward_raw(I["wx"], I["wy"], I["c"], I["b"], I["grad"], its, None, hist=o_hist, ckpt_y=o_cky)
+        del o_hist
+        _, ck32 = R.tv_forward_raw(I["wx"], I["wy"], I["c"], I["b"], I["init"], its, torch.float32)
+        g32 = R.tv_backward_raw(I["wx"], I["wy"], I["c"], I["b"], I["grad"], its, ck32, torch.float32)
+        gaps = [rel_errors(a, b) for a, b in zip(g32, g64)]
+        for name, g, r, gap in zip(TV_NAMES, grads, g64, gaps):
+            e = rel_errors(g, r)
+            print(f"{name}: end to end cuda-vs-fp64 max {e[0]:.2e} l2 {e[1]:.2e} | oracle fp32-vs-fp64 max {gap[0]:.2e} l2 {gap[1]:.2e}")
+            _bounded_in_both_norms("this library vs fp64 oracle", name, e, gap)
+        # --- the reference's own kernels on the same image
+        if not ref_cuda.available():
+            pytest.skip("oracle/_ref/libtvref.so not built: live comparison with the reference kernels skipped")
+        r_sol = ref_cuda.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, 1)
+        r_g = ref_cuda.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, 1)
+        assert_close(r_sol, o_sol, "reference kernels vs oracle: solution")
+        assert_close(sol, r_sol.cpu(), "this library vs reference kernels: solution")
+        for name, mg, rg, o64, gap in zip(TV_NAMES, grads, r_g, g64, gaps):
+            e_ref, e_my = rel_errors(rg, o64), rel_errors(mg, rg.cpu())
+            print(f"{name}: ref-vs-fp64 max {e_ref[0]:.2e} l2 {e_ref[1]:.2e} | lib-vs-ref max {e_my[0]:.2e} l2 {e_my[1]:.2e}")
+            _bounded_in_both_norms("reference kernels vs fp64 oracle", name, e_ref, gap)
+            _bounded_in_both_norms("this library vs reference kernels", name, e_my, gap)
+    finally:
+        ext.set_option(pid, _lib.OPT_CONDITIONER, 1)
+        ext.release(pid)
+
+
+def _tgv_run(ext, D, its, pid, ch, h, w):
+    flat = lambda t: t.reshape(1, 3 * ch, h, w)
+    sol = ext.forward(D["dx"], D["dy"], D["c"], D["b"], flat(D["init"]), its, pid)[0]
+    hist, cky, L = ext.read_history(pid, flat(D["init"]), its)
+    grads = ext.backward(flat(D["grad"]), D["dx"], D["dy"], D["c"], D["b"], its, pid)
+    torch.cuda.synchronize()
+    five = lambda t: t.reshape(t.shape[:-3] + (3, ch, h, w))
+    return five(sol), five(hist), five(cky), L, grads[:4] + [five(grads[4])]
+
+
+def test_tgv_full_size_image_matches_oracle():
+    from customnetworklayers_b200 import tgvInpaint_cuda_ext as ext
+    ch, h, w, its = 2, 436, 1024, 100
+    I = make_tgv_inputs(1, ch, h, w, seed=20242)
+    I["init"][:, 1:] = 0.1 * I["grad"][:, 1:]
+    D = _dev(I)
+    pid = 4
+    ext.release(pid)
+    ext.set_option(pid, 1, 0)
+    try:
+        sol, hist, cky, L, grads = _tgv_run(ext, D, its, pid, ch, h, w)
+        hist, cky = hist.cpu(), cky.cpu()
+        r_sol, r_hist, r_cky, _, r_L = G.tgv_forward_history(I["dx"], I["dy"], I["c"], I["b"], I["init"], its)
+        assert torch.equal(L.cpu(), r_L.reshape(-1)), "1/Lipschitz must be bit-exact"
+        print("solution", rel_errors(sol, r_sol), "history", rel_errors(hist, r_hist), "checkpoints", rel_errors(cky, r_cky))
+        assert_close(sol, r_sol, "solution")
+        assert_close(hist, r_hist, "history")
+        assert_close(cky, r_cky, "checkpointed y")
+        del r_hist
+        ref = G.tgv_backward(I["dx"], I["dy"], I["c"], I["b"], I["grad"], its, hist, cky)
+        for name, g, r in zip(TGV_NAMES, grads, ref):
+            print(name, "reverse sweep on device iterates", rel_errors(g, r))
+            assert_close(g, r, name)
+    finally:
+        ext.set_option(pid, 1, 1)
+        ext.release(pid)
+
+
+@pytest.mark.skipif(not ref_cuda.tgv_available(), reason="oracle/_ref/libtgvref.so not built")
+@pytest.mark.parametrize("case", [(2, 96, 320, 20), (2, 432, 1024, 100)], ids=lambda c: "c%d_%dx%d_its%d" % c)
+def test_tgv_reference_kernels_agree_with_oracle_and_cuda_path(case):
+    """Live three-way comparison on the TGV layer: the reference's kernels, the fp64 oracle and this library."""
+    from customnetworklayers_b200 import tgvInpaint_cuda_ext as ext
+    ch, h, w, its = case
+    I = make_tgv_inputs(1, ch, h, w, seed=61 + h + w + its)
+    I["init"][:, 1:] = 0.1 * I["grad"][:, 1:]
+    D = _dev(I)
+    pid = 5
+    ext.release(pid)
+    ext.set_option(pid, 1, 0)
+    try:
+        sol, _, _, _, grads = _tgv_run(ext, D, its, pid, ch, h, w)
+        r_sol = ref_cuda.tgv_forward(D["dx"], D["dy"], D["c"], D["b"], D["init"], its, 2)
+        r_g = ref_cuda.tgv_backward(D["grad"], D["dx"], D["dy"], D["c"], D["b"], its, 2)
+        o_sol, o_hist, o_cky, _, _ = G.tgv_forward_history(I["dx"], I["dy"], I["c"], I["b"], I["init"], its)
+        assert_close(r_sol, o_sol, "reference kernels vs oracle: solution")
+        assert_close(sol, r_sol.cpu(), "this library vs reference kernels: solution")
+        g64 = G.tgv_backward(I["dx"], I["dy"], I["c"], I["b"], I["grad"], its, o_hist, o_cky)
+        del o_hist
+        # the oracle's own fp32 run measures how far threshold flips move an fp32 implementation on these inputs
+        I32 = {k: v.float() for k, v in I.items()}
+        _, h32, c32, _, _ = G.tgv_forward_history(I32["dx"], I32["dy"], I32["c"], I32["b"], I32["init"], its, dtype=torch.float32)
+        g32 = G.tgv_backward(I32["dx"], I32["dy"], I32["c"], I32["b"], I32["grad"], its, h32, c32, dtype=torch.float32)
+        del h32
+        for name, mg, rg, o64, o32 in zip(TGV_NAMES, grads, r_g, g64, g32):
+            gap = rel_errors(o32, o64)
+            e_ref, e_my = rel_errors(rg, o64), rel_errors(mg, rg.cpu())
+            print(f"{name}: ref-vs-fp64 max {e_ref[0]:.2e} l2 {e_ref[1]:.2e} | lib-vs-ref max {e_my[0]:.2e} l2 {e_my[1]:.2e}"
+                  f" | oracle fp32-vs-fp64 max {gap[0]:.2e} l2 {gap[1]:.2e}")
+            _bounded_in_both_norms("reference kernels vs fp64 oracle", name, e_ref, gap)
+            _bounded_in_both_norms("this library vs reference kernels", name, e_my, gap)
+    finally:
+        ext.set_option(pid, 1, 1)
+        ext.release(pid)

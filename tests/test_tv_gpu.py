@@ -162,6 +162,29 @@ def test_python_layer_autograd_and_hwc_convention(ext):
     assert_close(out3.permute(0, 3, 1, 2), ref3, "batched layer output")
 
 
+def test_stale_history_and_wrong_shapes_are_refused(ext):
+    """A slot keeps its last forward pass only: the backward pass of an earlier forward on the same id must raise,
+    not return gradients of the other problem; wrongly shaped weight maps are refused before any kernel runs."""
+    from customnetworklayers_b200 import TVInpaintingFunction
+    I = R.make_inputs(1, 2, 16, 24, seed=3)
+    D = _dev(I)
+    ext.release(7)
+    first = [D[k].clone().requires_grad_(True) for k in ("wx", "wy", "c", "b", "init")]
+    second = [D[k].clone().requires_grad_(True) for k in ("wx", "wy", "c", "b", "init")]
+    out1 = TVInpaintingFunction.apply(*first, 6, 7)
+    out2 = TVInpaintingFunction.apply(*second, 6, 7)
+    with pytest.raises(RuntimeError, match="replaced the history"):
+        out1.backward(D["grad"])
+    out2.backward(D["grad"])
+    assert all(t.grad is not None for t in second)
+    ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], 6, 7)
+    with pytest.raises(RuntimeError, match=r"d_c must have shape \[N,1,H,W\]"):
+        ext.backward(D["grad"], D["wx"], D["wy"], D["c"][:, :, :8].contiguous(), D["b"], 6, 7)
+    with pytest.raises(RuntimeError, match=r"d_x must have shape \[N,1,H,W\]"):
+        ext.backward(D["grad"], D["b"], D["wy"], D["c"], D["b"], 6, 7)
+    ext.release(7)
+
+
 def test_properties(ext):
     n, ch, h, w, its = 1, 2, 32, 48, 30
     I = R.make_inputs(n, ch, h, w, seed=8)
@@ -246,6 +269,61 @@ def test_conditioner_matches_oracle_state_machine(ext):
     plain = ext.backward(D["grad"] * 30.0, D["wx"], D["wy"], D["c"], D["b"], its, 1)
     ratio = float(grads[3].norm() / plain[3].norm())
     assert 0.2 < ratio < 0.5
+
+
+def test_conditioner_kill_branch_matches_oracle_state_machine(ext):
+    """After ten runs an upstream gradient 100 times larger than usual exceeds 50 times the running mean of every
+    returned gradient: all five are zeroed (TVInpaintFista.cu:132-140) and the running means move as the oracle's
+    transcription says, which the following ordinary rounds (one of them rescaled) show."""
+    n, ch, h, w, its = 1, 2, 16, 24, 6
+    I = R.make_inputs(n, ch, h, w, seed=13)
+    D = _dev(I)
+    ext.release(0)
+    ext.set_option(0, 1, 1)
+    st = R.IdState()
+    scales = [1.0] * 11 + [100.0, 1.0, 30.0, 1.0]
+    for r, scale in enumerate(scales):
+        ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, 0)
+        hist, cky = ext.read_history(0, D["b"], its)
+        grads = ext.backward(D["grad"] * scale, D["wx"], D["wy"], D["c"], D["b"], its, 0)
+        ref = R.tv_backward_raw(I["wx"], I["wy"], I["c"], I["b"], I["grad"] * scale, its, None, state=st,
+                                hist=hist.cpu(), ckpt_y=cky.cpu())
+        for name, a, rr in zip(GRAD_NAMES, grads, ref):
+            assert_close(a, rr, f"round {r} {name}")
+        if scale == 100.0:
+            assert all(float(rr.abs().max()) == 0.0 for rr in ref), "the oracle kills this round"
+            assert all(float(a.abs().max()) == 0.0 for a in grads), "every returned gradient is zeroed"
+    ext.release(0)
+
+
+def test_nonfinite_returned_gradient_after_ten_runs_is_killed(ext):
+    """A confidence of -1 at one pixel makes 1/(1+c) infinite there, so NaNs spread through a patch of the iterates and
+    into the returned gradients.  The sanitiser zeroes them; after ten runs the conditioner treats such a gradient as a
+    spike (running mean restarted from 1000 x its value, TVInpaintFista.cu:171) and zeroes the whole tensor.  The
+    reference's mean then depends on where the entry sits; here it does not, so only the outcome is checked: finite
+    outputs, the affected tensors zeroed, and ordinary gradients again on the next clean run."""
+    n, ch, h, w, its = 1, 2, 16, 24, 6
+    I = R.make_inputs(n, ch, h, w, seed=14)
+    D = _dev(I)
+    ext.release(0)
+    ext.set_option(0, 1, 1)
+    clean = None
+    for r in range(11):
+        ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, 0)
+        clean = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, 0)
+    bad_c = D["c"].clone()
+    bad_c[0, 0, 12, 17] = -1.0
+    ext.forward(D["wx"], D["wy"], bad_c, D["b"], D["init"], its, 0)
+    hist, _ = ext.read_history(0, D["b"], its)
+    assert not bool(torch.isfinite(hist).all()), "the iterates must contain non-finite values for this test to bite"
+    grads = ext.backward(D["grad"], D["wx"], D["wy"], bad_c, D["b"], its, 0)
+    assert all(bool(torch.isfinite(g).all()) for g in grads)
+    assert float(grads[2].abs().max()) == 0.0 and float(grads[3].abs().max()) == 0.0, "g_c and g_b carried NaNs: killed"
+    ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, 0)
+    again = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, 0)
+    for name, a, b2 in zip(GRAD_NAMES, again, clean):
+        assert torch.equal(a, b2), name + ": a clean run after the spike is an ordinary run"
+    ext.release(0)
 
 
 def test_host_pipeline_matches_direct_calls(ext):

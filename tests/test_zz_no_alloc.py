@@ -3,8 +3,6 @@
 Some users of this library cannot allocate device memory at call time: a real-time loop that must avoid the
 allocator's implicit synchronisation, or a plugin inside an engine that owns the whole device.  For them the
 reduction's block partials sit in a fixed array inside the library.  This file is named to be collected last."""
-import ctypes
-
 import pytest
 import torch
 
@@ -58,3 +56,16 @@ def test_static_variant_handles_empty_and_rejects_oversize():
     too_many = lib.cnl_tv_lambda_grad_static_max_count() + 1
     rc = lib.cnl_tv_lambda_grad_static(a.data_ptr(), a.data_ptr(), too_many, out.data_ptr(), st)
     assert rc == 2 and "at most" in _lib.last_error()
+
+
+def test_static_variant_at_its_maximum_count():
+    """count == cnl_tv_lambda_grad_static_max_count() uses every slot of the array and must still be accepted."""
+    from customnetworklayers_b200 import _lib
+    lib = _lib.load()
+    n = lib.cnl_tv_lambda_grad_static_max_count()
+    gen = torch.Generator().manual_seed(22)
+    a = torch.randn(n, generator=gen).cuda()
+    b = torch.rand(n, generator=gen).cuda()
+    for _ in range(2):
+        got, ref = _both(lib, a, b)
+        assert abs(got - ref) <= 1e-4 * max(1.0, abs(ref)), (got, ref)
