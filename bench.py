@@ -3,9 +3,11 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
 
-One "step" = forward + backward of one batch of synthetic flow fields (2 x 384 x 1280, 100 iterations, batch 8 per
-GPU), plus the lambda-gradient reduction and, on more than one GPU, its NCCL all-reduce.  Metric: Gpixel-iters/s =
-N*H*W*its_eff / t / 1e9.  Rank 0 prints one JSON line.
+One "step" = forward + backward of one batch of synthetic flow fields (2 x 384 x 1280, 100 iterations), plus the
+lambda-gradient reduction and, on more than one GPU, its NCCL all-reduce.  The batch of 8 is sharded over the GPUs
+(8/4/2/1 images per GPU at 1/2/4/8 GPUs: strong scaling, the default); `--scaling weak` keeps 8 images per GPU, and a
+multi-GPU strong run carries that figure in `weak_scaling`.  Metric: Gpixel-iters/s = N*H*W*its_eff / t / 1e9.
+Rank 0 prints one JSON line.
 """
 from __future__ import annotations
 
@@ -121,10 +123,19 @@ def cpu_fwd_bwd(I, its):
     return sol
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the 4-iteration kernels at the launch
-# geometry of cfg1 / prof (batch 8, 2x384x1280; 1408 tiles), from an `ncu --set full` capture of one launch each
-# (profiles/tv_fused_kernels_prof_and_cfg1.md).  Other geometries have no capture and report null.
-NCU_TRAFFIC = {(8, 2, 384, 1280): {"reverse": 523.0e6, "forward": 307.7e6}}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the 4-iteration kernels at batch 8,
+# 2x384x1280 (1408 tiles), from an `ncu --set full` capture of one launch each, NOT measured in this run
+# (profiles/tv_fused_kernels_prof_and_cfg1.md).  Traffic grows in proportion to the images of a launch, so other batch
+# sizes of the same image scale it; other image sizes have no capture and report null.
+NCU_TRAFFIC_BATCH8 = {(2, 384, 1280): {"reverse": 523.0e6, "forward": 307.7e6}}
+TRAFFIC_SOURCE = "ncu capture of one launch (profiles/tv_fused_kernels_prof_and_cfg1.md), scaled by batch/8 and iterations/4; not measured in this run"
+
+
+def ncu_traffic_per_launch(nb, ch, h, w, rev_ipl, fwd_ipl):
+    t = NCU_TRAFFIC_BATCH8.get((ch, h, w))
+    if not t:
+        return None
+    return {"reverse": t["reverse"] * nb / 8.0 * rev_ipl / 4.0, "forward": t["forward"] * nb / 8.0 * fwd_ipl / 4.0}
 
 
 def cpu_baseline_sample(ch, h, w, its, budget_s=20.0):
@@ -185,8 +196,25 @@ def reference_cuda_sample(ch, h, w, its):
         return {"unavailable": str(e)[:200]}
 
 
+def workload_config(args, world):
+    """The `config` block both arms print: names the workload, not the arm."""
+    nb, ch, h, w, its = WORKLOADS[args.workload]
+    scaling = resolve_scaling(args)
+    gb = nb if scaling == "strong" else nb * world
+    return {"workload": f"{args.workload}: TV-FISTA fwd+bwd, batch {gb}, flow {ch}x{h}x{w}, {its} iterations, "
+                        f"sharded over {world} GPU(s), lambda gradient all-reduced",
+            "global_batch": gb, "parallelism": f"dp{world}",
+            "l2": "per-step working set (iterate history) is far larger than the 126 MB L2; no flush"}
+
+
+def resolve_scaling(args):
+    return args.scaling or "strong"
+
+
 def run_reference_arm(args, rank, world):
-    """--impl reference: the reference math on the host cores (oracle port, all threads), same metric and config."""
+    """--impl reference: the reference math on the host cores (oracle port, all threads), same metric and config.
+    One step = forward + backward of ONE full image of the workload (the reference's own calling pattern is one image
+    per call); the metric is per pixel-iteration, so the number compares directly."""
     if rank != 0:
         return
     import torch
@@ -195,81 +223,46 @@ def run_reference_arm(args, rank, world):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     its_eff = 2 * (its // 2)
-    # bounded sample: one image, cropped in height so that (steps + warmup) passes stay within ~4 minutes
-    probe = make_inputs(1, ch, min(h, 96), min(w, 320), seed=1234)
-    pits = min(its, 20)
-    cpu_fwd_bwd(probe, pits)
-    t0 = time.perf_counter()
-    cpu_fwd_bwd(probe, pits)
-    rate = probe["b"].shape[2] * probe["b"].shape[3] * 2 * (pits // 2) / (time.perf_counter() - t0)
-    budget = 220.0 / max(1, args.steps + args.warmup)
-    sh = h
-    while sh * w * its_eff / rate > budget and sh > 16:
-        sh //= 2
-    I = make_inputs(1, ch, sh, w, seed=1235)
+    I = make_inputs(1, ch, h, w, seed=1235)
     for _ in range(args.warmup):
         cpu_fwd_bwd(I, its)
     t0 = time.perf_counter()
     for _ in range(args.steps):
         cpu_fwd_bwd(I, its)
     dt = time.perf_counter() - t0
-    val = args.steps * sh * w * its_eff / dt / 1e9
-    sample = f"fp32 torch-CPU oracle port, per step 1 image {ch}x{sh}x{w}, {its} iterations, fwd+bwd"
+    val = args.steps * h * w * its_eff / dt / 1e9
+    sample = (f"fp32 torch-CPU oracle port on {cores} threads; per step 1 full image {ch}x{h}x{w}, {its} iterations, fwd+bwd "
+              f"(1/{nb} of the batch: the reference solves one image per call)")
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": f"{args.workload}: TV-FISTA fwd+bwd, per-GPU batch {nb}, flow {ch}x{h}x{w}, {its} iterations",
-                       "note": "the reference is CUDA-only and does not build without ImageUtilities; this arm times its CPU restatement"},
+            "higher_is_better": True, "scaling": resolve_scaling(args), "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(args, world),
+            "arm": {"what": "the reference is CUDA-only and does not build without ImageUtilities; this arm times its CPU "
+                            "restatement (oracle/tv_ref.py, float32)", "step": sample},
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    try:
-        import torch as _t
-        if _t.cuda.is_available():
-            rc = reference_cuda_sample(ch, h, w, its)
-            if rc is not None:
-                line["reference_cuda"] = rc
-    except Exception:
-        pass
     print(json.dumps(line), flush=True)
 
 
 # ---------------------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------------------
-def run_ours(args, rank, local_rank, world):
+def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, warmup, sample_clocks):
+    """Times `steps` forward+backward steps of a per-GPU batch of nb images, inputs resident, then the same through the
+    host-buffer API.  Returns a dict of raw figures (times are the maximum over ranks)."""
     import torch
     import torch.distributed as dist
     from customnetworklayers_b200 import _lib, tvInpaint_cuda_ext as ext
     from customnetworklayers_b200.dist import allreduce_scalar_grads
+    from customnetworklayers_b200.host_pipeline import HostPipeline, tv_fwd_bwd_from_host
     from customnetworklayers_b200.synthetic import make_inputs
 
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the product path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    numa_cpus = None
-    if world > 1 and os.environ.get("CNL_BIND_NUMA", "0") == "1":
-        from customnetworklayers_b200.dist import bind_to_gpu_numa_node
-        numa_cpus = bind_to_gpu_numa_node(local_rank)          # before any pinned allocation
-    if os.environ.get("CNL_BENCH_DEBUG"):
-        print(f"[rank {rank}] cpus allowed {sorted(os.sched_getaffinity(0))} numa bind {numa_cpus}", file=sys.stderr, flush=True)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    _lib.load()
-
-    nb, ch, h, w, its = WORKLOADS[args.workload]
-    if args.scaling == "strong":
-        if nb % world:
-            raise RuntimeError("strong scaling needs the batch to divide by the number of GPUs")
-        nb //= world
-    its_eff = 2 * (its // 2)
     pid = 0
+    ext.release(pid)
     ext.set_option(pid, _lib.OPT_FUSE, args.fuse)
     ext.set_option(pid, _lib.OPT_RECOMPUTE, 1 if args.recompute else 0)
     ext.set_option(pid, _lib.OPT_CONDITIONER, 1)
-
     # seeded synthetic inputs; every rank draws its own shard
     I = make_inputs(nb, ch, h, w, seed=1234 + 1 + 1000 * rank)
     keys = ("wx", "wy", "c", "b", "init", "grad")
@@ -287,57 +280,100 @@ def run_ours(args, rank, local_rank, world):
         allreduce_scalar_grads(g_lam)
         return sol, grads, g_lam
 
-    host_out = {"lam": torch.empty(1).pin_memory()}
-
-    from customnetworklayers_b200.host_pipeline import HostPipeline, tv_fwd_bwd_from_host
+    host_lam = torch.empty(1).pin_memory()
     pipe = HostPipeline(dev)
     out_keys = ("sol", "g_wx", "g_wy", "g_c", "g_b", "g_init")
     like = {"sol": "b", "g_wx": "wx", "g_wy": "wy", "g_c": "c", "g_b": "b", "g_init": "b"}
     host_res = {k: torch.empty_like(host[like[k]]).pin_memory() for k in out_keys}
+    chunk = max(1, min(args.e2e_chunk, nb))
 
     def step_e2e():
         # the public host-buffer API: chunked H2D copy -> forward -> backward -> D2H copy, copies overlapped
-        tv_fwd_bwd_from_host(pipe, host, host_res, its, pid, lam=lam, chunk=args.e2e_chunk,
-                             host_lam_grad=host_out["lam"])
-
-    h2d = sum(host[k].numel() * 4 for k in keys)
-    d2h = sum(t.numel() * 4 for t in host_res.values()) + 4
+        tv_fwd_bwd_from_host(pipe, host, host_res, its, pid, lam=lam, chunk=chunk, host_lam_grad=host_lam)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, sample_clocks=False):
+    def timed(fn, nsteps, clocks=False, finish=None):
         barrier()
-        sampler = ClockSampler(local_rank) if sample_clocks else None
+        sampler = ClockSampler(local_rank) if clocks else None
         if sampler:
             sampler.start()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         launches0 = _lib.load().cnl_launch_count()
         e0.record()
-        for _ in range(steps):
+        for _ in range(nsteps):
             fn()
+        if finish:
+            finish()                  # the timed stream waits for the last result copy before the closing event
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         launches = _lib.load().cnl_launch_count() - launches0
-        clocks = sampler.stop() if sampler else None
-        return float(ms.item()), launches, clocks
+        return float(ms.item()), launches, (sampler.stop() if sampler else None)
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step_resident()
     ext.set_option(pid, _lib.OPT_TIMING, 1)
-    ms, launches, clocks = timed(step_resident, args.steps, sample_clocks=True)
+    ms, launches, clocks = timed(step_resident, steps, clocks=sample_clocks)
     tm = ext.get_timing(pid)
     ext.set_option(pid, _lib.OPT_TIMING, 0)
-    for _ in range(min(2, args.warmup)):
+    for _ in range(max(3, min(3, warmup))):
         step_e2e()
-    ms_e2e, _, _ = timed(step_e2e, args.steps)
+    ms_e2e, _, _ = timed(step_e2e, steps, finish=pipe.join)
+    # where an end-to-end step spends its time: one call alone, CUDA events per chunk from the call's start
+    breakdown = None
+    if rank == 0:
+        torch.cuda.synchronize()
+        pipe.timeline = []
+        step_e2e()
+        torch.cuda.synchronize()
+        breakdown = [{k: round(v, 3) for k, v in row.items()} for row in pipe.chunk_breakdown()]
+        pipe.timeline = None
+    barrier()
+    res = {"nb": nb, "ms": ms, "launches": launches, "clocks": clocks, "tm": tm, "ms_e2e": ms_e2e, "chunk": chunk,
+           "h2d": sum(host[k].numel() * 4 for k in keys), "d2h": sum(t.numel() * 4 for t in host_res.values()) + 4,
+           "breakdown": breakdown}
+    del D, host, host_res, pipe
+    ext.release(pid)
+    torch.cuda.empty_cache()
+    return res
 
+
+def run_ours(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+    from customnetworklayers_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    nb_full, ch, h, w, its = WORKLOADS[args.workload]
+    scaling = resolve_scaling(args)
+    nb = nb_full
+    if scaling == "strong":
+        if nb_full % world:
+            raise RuntimeError("strong scaling needs the batch to divide by the number of GPUs")
+        nb = nb_full // world
+    if args.per_gpu_batch:
+        nb = args.per_gpu_batch          # one GPU standing in for one rank of a larger job (development aid)
+    its_eff = 2 * (its // 2)
+    M = measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, args.steps, args.warmup, True)
+    weak = None
+    if world > 1 and scaling == "strong" and not args.per_gpu_batch:
+        weak = measure_tv(args, dev, rank, local_rank, world, nb_full, ch, h, w, its, args.steps, args.warmup, False)
+
+    ms, ms_e2e, tm = M["ms"], M["ms_e2e"], M["tm"]
     pixel_iters = world * nb * h * w * its_eff
     value = pixel_iters * args.steps / (ms * 1e-3) / 1e9
     e2e_value = pixel_iters * args.steps / (ms_e2e * 1e-3) / 1e9
@@ -355,39 +391,76 @@ def run_ours(args, rank, local_rank, world):
         fwd_ipl = its_eff * tm["fwd_calls"] / max(1, tm["fwd_launches"])
         fwd_achieved = fwd_b * nb * h * w * fwd_ipl / (fwd_launch_ms * 1e-3) / 1e9 if fwd_launch_ms > 0 else 0.0
         whole = (fwd_b + rev_b) * pixel_iters / world * args.steps / (ms * 1e-3) / 1e9
-        ncu_traffic = NCU_TRAFFIC.get((nb, ch, h, w)) if args.fuse in (0, 4) else None
+        traffic = ncu_traffic_per_launch(nb, ch, h, w, iters_per_launch, fwd_ipl) if args.fuse in (0, 4) else None
+        cfg = workload_config(args, world)
+        if args.per_gpu_batch:
+            cfg["workload"] += f" [one GPU timing a shard of {nb} image(s)]"
+            cfg["global_batch"] = nb
+        cfg.update({"per_gpu_batch": nb, "fuse": args.fuse,
+                    "history": "checkpoints only, segments recomputed in the backward pass" if args.recompute else "every iterate resident"})
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: TV-FISTA fwd+bwd, per-GPU batch {nb}, flow {ch}x{h}x{w}, {its} iterations, lambda gradient all-reduced",
-                       "global_batch": nb * world, "parallelism": f"dp{world}", "fuse": args.fuse,
-                       "history": "checkpoints only, segments recomputed in the backward pass" if args.recompute else "every iterate resident",
-                       "l2": "per-step working set (iterate history) is far larger than the 126 MB L2; no flush"},
+            "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
             "roofline": {"bound": "hbm", "kernel": "reverse iteration", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": ncu_traffic["reverse"] if ncu_traffic else None,
-                         "peak_kind": peak_kind,
-                         "launch_ms": rev_launch_ms, "algorithmic_bytes_per_launch": bytes_per_launch,
-                         "note": "achieved counts the bytes a one-iteration-per-launch schedule streams; four fused "
-                                 "iterations per launch move about a third of that through DRAM (traffic), hence frac > 1",
+                         "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic["reverse"] if traffic else None,
+                         "frac_traffic": (traffic["reverse"] / (rev_launch_ms * 1e-3) / 1e9 / peak) if traffic and rev_launch_ms > 0 else None,
+                         "traffic_source": TRAFFIC_SOURCE if traffic else None,
+                         "peak_kind": peak_kind, "limiter": "instruction issue, not DRAM: see frac_traffic",
+                         "launch_ms": rev_launch_ms, "iterations_per_launch": iters_per_launch,
+                         "algorithmic_bytes_per_launch": bytes_per_launch,
+                         "note": "achieved counts the bytes a one-iteration-per-launch schedule streams; fused iterations "
+                                 "move about a third of that through DRAM (traffic), hence frac > 1 while frac_traffic, "
+                                 "the share of the copy peak the launch really draws, is well below 1",
                          "forward_kernel": {"achieved": fwd_achieved, "frac": fwd_achieved / peak, "launch_ms": fwd_launch_ms,
-                                            "traffic": ncu_traffic["forward"] if ncu_traffic else None},
+                                            "iterations_per_launch": fwd_ipl,
+                                            "traffic": traffic["forward"] if traffic else None,
+                                            "frac_traffic": (traffic["forward"] / (fwd_launch_ms * 1e-3) / 1e9 / peak) if traffic and fwd_launch_ms > 0 else None},
                          "whole_step": {"achieved": whole, "frac": whole / peak}},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": M["h2d"], "d2h_bytes_per_step": M["d2h"],
                     "ms_per_step": ms_e2e / args.steps, "api": "host_pipeline.tv_fwd_bwd_from_host",
-                    "chunk_images": args.e2e_chunk},
-            "gpu_launches": int(launches),
-            "clocks": clocks,
+                    "chunk_images": M["chunk"],
+                    "single_call_ms_since_start": M["breakdown"]},
+            "gpu_launches": int(M["launches"]),
+            "clocks": M["clocks"],
         }
+        if weak is not None:
+            wpi = world * nb_full * h * w * its_eff
+            line["weak_scaling"] = {"per_gpu_batch": nb_full, "global_batch": nb_full * world,
+                                    "value": wpi * args.steps / (weak["ms"] * 1e-3) / 1e9, "ms_per_step": weak["ms"] / args.steps,
+                                    "e2e_value": wpi * args.steps / (weak["ms_e2e"] * 1e-3) / 1e9,
+                                    "e2e_ms_per_step": weak["ms_e2e"] / args.steps, "unit": UNIT}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample(ch, h, w, its)
             rc = reference_cuda_sample(ch, h, w, its)
             if rc is not None:
                 line["reference_cuda"] = rc
+        if world == 1 and not args.no_secondary and args.workload == "cfg1" and not args.per_gpu_batch:
+            line["secondary"] = secondary_workloads(args, local_rank)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def secondary_workloads(args, local_rank):
+    """Compact records of the other configurations (TGV, the coarse-to-fine stack, the weighted-median filter and the two
+    small layers), three steps each after three warm-up steps, measured after and outside the timed region above."""
+    import copy
+    out = {}
+    for name, fn in (("cfg2", run_tgv), ("cfg3", run_hierarchy), ("cfg4", run_wmedian), ("median", run_layer_micro),
+                     ("quadfit", run_layer_micro)):
+        a = copy.copy(args)
+        a.workload, a.steps, a.warmup = name, 3, 3
+        try:
+            r = fn(a, 0, local_rank, 1)
+            out[name] = {"metric": r["metric"], "value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"],
+                         "frac": r["roofline"]["frac"], "roofline_kernel": r["roofline"]["kernel"],
+                         "workload": r["config"]["workload"], "gpu_launches": r["gpu_launches"]}
+        except Exception as e:          # a secondary record must not take the headline down with it
+            out[name] = {"error": str(e)[:200]}
+    return out
 
 
 def run_tgv(args, rank, local_rank, world):
@@ -442,13 +515,14 @@ def run_tgv(args, rank, local_rank, world):
     ms = float(ms)
     launches = _lib.load().cnl_launch_count() - l0
     clocks = sampler.stop()
+    result = None
     if rank == 0:
         pixel_iters = world * nb * h * w * its_eff
         value = pixel_iters * args.steps / (ms * 1e-3) / 1e9
         bytes_pi = (16 * ch + 5) * 4 + (21 * ch + 15) * 4
         peak, kind = measured_peak_gbs()
         ach = bytes_pi * pixel_iters / world * args.steps / (ms * 1e-3) / 1e9
-        print(json.dumps({
+        result = ({
             "metric": "tgv_fista_fwd_bwd_gpixel_iters_per_s", "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -456,10 +530,11 @@ def run_tgv(args, rank, local_rank, world):
                        "global_batch": nb * world, "parallelism": f"dp{world}"},
             "roofline": {"bound": "hbm", "kernel": "whole step (one launch per iteration)", "achieved": ach, "peak": peak,
                          "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_kind": kind},
-            "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+            "gpu_launches": int(launches), "clocks": clocks})
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return result
 
 
 def run_hierarchy(args, rank, local_rank, world):
@@ -513,13 +588,14 @@ def run_hierarchy(args, rank, local_rank, world):
     ms = float(ms)
     launches = _lib.load().cnl_launch_count() - l0
     clocks = sampler.stop()
+    result = None
     if rank == 0:
         pixel_iters = world * nb * sum((h >> s) * (w >> s) for s in (2, 1, 0)) * its_eff
         value = pixel_iters * args.steps / (ms * 1e-3) / 1e9
         peak, kind = measured_peak_gbs()
         fwd_b, rev_b = algorithmic_bytes_per_pixel_iter(ch)
         ach = (fwd_b + rev_b) * pixel_iters / world * args.steps / (ms * 1e-3) / 1e9
-        print(json.dumps({
+        result = ({
             "metric": "hierarchical_tv_fwd_bwd_gpixel_iters_per_s", "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -527,10 +603,11 @@ def run_hierarchy(args, rank, local_rank, world):
                        "global_batch": nb * world, "parallelism": f"dp{world}"},
             "roofline": {"bound": "hbm", "kernel": "whole step (TV pixel-iterations only)", "achieved": ach, "peak": peak,
                          "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_kind": kind},
-            "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+            "gpu_launches": int(launches), "clocks": clocks})
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return result
 
 
 def run_wmedian(args, rank, local_rank, world):
@@ -581,6 +658,7 @@ def run_wmedian(args, rank, local_rank, world):
     ms = float(ms)
     launches = _lib.load().cnl_launch_count() - l0
     clocks = sampler.stop()
+    result = None
     if rank == 0:
         problems = world * nb * ch * h * w
         value = problems * args.steps / (ms * 1e-3) / 1e9
@@ -588,7 +666,7 @@ def run_wmedian(args, rank, local_rank, world):
         # fused layout: read flow + grad, write out + tap + g_flow, re-read tap + grad: 7 words per problem; the
         # reference's materialised layout would move (3*49+4)*4 = 604 B per problem
         ach = 28.0 * problems / world * args.steps / (ms * 1e-3) / 1e9
-        print(json.dumps({
+        result = ({
             "metric": "weighted_median_fwd_bwd_gproblems_per_s", "value": value, "unit": "Gproblems/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -597,10 +675,11 @@ def run_wmedian(args, rank, local_rank, world):
             "roofline": {"bound": "hbm", "kernel": "whole step; the kernels are bound by the rank updates of the sliding window (about 2*K*k compares per problem), not by HBM",
                          "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_kind": kind,
                          "materialised_layout_equivalent_gbs": 604.0 * problems / world * args.steps / (ms * 1e-3) / 1e9},
-            "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+            "gpu_launches": int(launches), "clocks": clocks})
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return result
 
 
 def run_layer_micro(args, rank, local_rank, world):
@@ -643,10 +722,11 @@ def run_layer_micro(args, rank, local_rank, world):
     ms = e0.elapsed_time(e1)
     launches = _lib.load().cnl_launch_count() - l0
     clocks = sampler.stop()
+    result = None
     if rank == 0:
         peak, kind = measured_peak_gbs()
         ach = bytes_per_unit * units * args.steps / (ms * 1e-3) / 1e9
-        print(json.dumps({
+        result = ({
             "metric": metric, "value": units * args.steps / (ms * 1e-3) / 1e9, "unit": unit, "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -654,7 +734,8 @@ def run_layer_micro(args, rank, local_rank, world):
                        "l2": "inputs of several hundred MB per call, larger than the 126 MB L2; no flush"},
             "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": ach, "peak": peak, "unit": "GB/s",
                          "frac": ach / peak, "traffic": None, "peak_kind": kind, "algorithmic_bytes_per_unit": bytes_per_unit},
-            "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+            "gpu_launches": int(launches), "clocks": clocks})
+    return result
 
 
 def main():
@@ -663,7 +744,11 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
+                    help="strong (default): the batch of the workload is sharded over the GPUs; weak: that batch per GPU")
+    ap.add_argument("--per-gpu-batch", type=int, default=0,
+                    help="development aid: time this many images on the GPU(s) given, as one rank of a larger job would")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the compact records of the other configurations")
     ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
     ap.add_argument("--fuse", type=int, default=0)
     ap.add_argument("--recompute", action="store_true",
@@ -684,17 +769,21 @@ def main():
         raise RuntimeError(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
-    elif args.workload in ("median", "quadfit"):
+        return
+    result = None
+    if args.workload in ("median", "quadfit"):
         if rank == 0:
-            run_layer_micro(args, rank, local_rank, world)
+            result = run_layer_micro(args, rank, local_rank, world)
     elif args.workload == "cfg4":
-        run_wmedian(args, rank, local_rank, world)
+        result = run_wmedian(args, rank, local_rank, world)
     elif args.workload == "cfg3":
-        run_hierarchy(args, rank, local_rank, world)
+        result = run_hierarchy(args, rank, local_rank, world)
     elif args.workload.startswith("cfg2"):
-        run_tgv(args, rank, local_rank, world)
+        result = run_tgv(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
+    if result is not None:
+        print(json.dumps(result), flush=True)
 
 
 if __name__ == "__main__":

@@ -50,6 +50,7 @@ OPT_CONDITIONER = 1
 OPT_FUSE = 2
 OPT_TIMING = 3
 OPT_RECOMPUTE = 4
+OPT_FLOW = 5
 
 _lib = None
 

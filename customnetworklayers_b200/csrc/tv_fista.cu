@@ -331,6 +331,7 @@ struct Slot {
     int opt_fuse = 0;
     int opt_timing = 0;
     int opt_recompute = 0;           // 1: keep only checkpoints and rebuild each segment's history in the backward pass
+    int opt_flow = 1;                // 1: all full time blocks of a sweep in one cooperative launch (tv_flow.cu)
     int pitch = 0;                   // row pitch (floats) of the arena planes of the stored forward pass
     bool staged = false;             // the temporally blocked kernels ran on zero-padded copies (pitch > w or unaligned tensors)
     bool recompute = false;          // mode the stored forward pass was run in
@@ -385,7 +386,7 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 // Layout of a slot's arena, in floats.  Every sub-buffer starts on a 256-byte boundary.
 struct ArenaLayout {
     size_t vol;       // n*ch*h*w rounded up to 64 floats
-    size_t y0, y1, xbuf, hist, ckpt, xck, ga, gb, acc, acc2, ybuf, total;
+    size_t y0, y1, xbuf, hist, ckpt, xck, ga, gb, acc, acc2, ybuf, sync, sync_words, total;
     size_t map;       // n*h*w rounded up to 64 floats (w = row pitch)
     size_t stage_map, stage_vol;     // 6 map-sized and 4 volume-sized staging buffers (staged mode only)
 };
@@ -406,6 +407,9 @@ static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t h
     L.acc2 = o; o += L.vol;
     L.xbuf = o; o += L.vol;
     L.ybuf = o; o += L.vol;
+    // progress counters of the single-launch sweeps: one per tile, then the abort word
+    L.sync_words = align_up((size_t)flow_tiles((int)h, (int)std::min<size_t>(w, 0x3fffffff), (int)n) + 1, 64);
+    L.sync = o; o += L.sync_words;
     L.ckpt = o; o += L.vol * nckpt;
     L.xck = o; o += L.vol * xck_planes;
     L.hist = o; o += L.vol * hist_planes;
@@ -504,6 +508,16 @@ static int ensure_cond(Slot& s) {
     return check_cuda(cudaMemset(s.cond, 0, kCondDoubles * sizeof(double)), "cudaMemset");
 }
 
+// Per-iteration tables of the single-launch sweeps: momentum factors and, per iteration, the checkpoint taken before it.
+static void fill_flow_tables(const Slot& s, int its_eff, FlowTables& tab) {
+    for (int g = 0; g < kFlowMaxIts; ++g) {
+        tab.t[g] = g < its_eff ? s.steps[g] : 0.0f;
+        tab.ckpt_slot[g] = -1;
+    }
+    for (size_t i = 0; i < s.sched.size(); ++i)
+        if (s.sched[i] < its_eff && s.sched[i] < kFlowMaxIts) tab.ckpt_slot[s.sched[i]] = (signed char)i;
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // host drivers
 // ---------------------------------------------------------------------------------------------------------------
@@ -517,6 +531,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
     if (!sp) return rc;
     Slot& s = *sp;
     s.have_forward = false;
+    CNL_TRY(flow_status_take());
     compute_schedule(its, s.sched, s.steps);
     const int its_eff = 2 * (its / 2);
     const void* aligned[] = {wx, wy, c, b, init, out};          // the arena itself is 256-byte aligned
@@ -580,7 +595,36 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
         const float* y_in = init;
         const float* x_in = init;
         size_t next_ckpt = 0;
-        for (int i = 0; i < nlaunch; ++i) {
+        int first_launch = 0;
+        // Single-launch sweep: every full time block of kFuseMax iterations in one cooperative launch whose tiles are
+        // ordered by progress counters; a shorter last block, if any, follows as an ordinary launch.
+        const int nfull = its_eff / kFuseMax;
+        if (!recompute && fuse == kFuseMax && s.opt_flow && nfull >= 1 && its_eff <= kFlowMaxIts && flow_enabled()) {
+            const bool rem = nfull < nlaunch;
+            FwdFlowParams fp{};
+            fp.init = init;
+            fp.ybuf[0] = y0; fp.ybuf[1] = y1;
+            // the primal iterate of the sweep's last launch has to land in the caller's buffer
+            fp.xbuf[(nfull - 1) & 1] = rem ? xbuf : out;
+            fp.xbuf[nfull & 1] = rem ? out : xbuf;
+            fp.b = b; fp.c = c; fp.wx = wx; fp.wy = wy;
+            fp.hist = s.arena + L.hist; fp.ckpt = s.arena + L.ckpt; fp.vol = L.vol;
+            int* sync = reinterpret_cast<int*>(s.arena + L.sync);
+            const int ntiles = flow_tiles(h, w, n);
+            fp.progress = sync; fp.abort = sync + ntiles; fp.status = flow_status_device_ptr();
+            fp.nblocks = nfull;
+            fp.N = n; fp.C = ch; fp.H = h; fp.W = w; fp.P = P;
+            fill_flow_tables(s, its_eff, fp.tab);
+            CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0, L.sync_words * sizeof(int), st), "zero progress counters"));
+            if (s.opt_flow == 2)      // self-test of the bounded waits: counters that no unit can ever bring up to what its neighbours need
+                CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0x80, (size_t)ntiles * sizeof(int), st), "poison progress counters"));
+            CNL_TRY(launch_tv_fwd_flow(fp, st));
+            first_launch = nfull;
+            y_in = fp.ybuf[(nfull - 1) & 1];
+            x_in = fp.xbuf[(nfull - 1) & 1];
+            while (next_ckpt < s.sched.size() && s.sched[next_ckpt] < nfull * kFuseMax) ++next_ckpt;
+        }
+        for (int i = first_launch; i < nlaunch; ++i) {
             const int g0 = plan[i].g0, K = plan[i].K;
             FwdFusedParams fp{};
             fp.y_in = y_in; fp.x_in = x_in;
@@ -666,6 +710,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
         return fail(CNL_ERR_NO_FORWARD, "backward(id=%d) needs a preceding forward(id=%d) with the same shape and its",
                     id, id);
     CNL_TRY(ensure_cond(s));
+    CNL_TRY(flow_status_take());
     const int its_eff = 2 * (its / 2);
     const bool staged = s.staged;
     const int P = s.pitch;                        // row pitch of the arena planes (w unless staged)
@@ -765,7 +810,31 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
         const float* acc_cur = acc;
         int flip = 0;
         int seg = nseg - 1;                       // segment the sweep is in (recompute mode)
-        for (int g0 = its_eff - 2; g0 >= 0;) {
+        int g_start = its_eff - 2;
+        const int nfull = (its_eff - 1) / kFuseMax;          // full time blocks of the reverse sweep
+        if (!s.recompute && fuse == kFuseMax && s.opt_flow && nfull >= 1 && its_eff <= kFlowMaxIts && flow_enabled()) {
+            RevFlowParams rp{};
+            rp.gbuf[0] = ga; rp.gbuf[1] = gb;                  // block 0 reads the seed in gb and writes ga
+            rp.abuf[0] = acc2; rp.abuf[1] = acc;
+            rp.b = b; rp.c = c; rp.wx = wx; rp.wy = wy;
+            rp.hist = hist; rp.ckpt = s.arena + L.ckpt; rp.vol = L.vol;
+            rp.g_c = g_c; rp.g_b = g_b; rp.g_wx = g_wx; rp.g_wy = g_wy;
+            rp.x1bar = g_init;
+            int* sync = reinterpret_cast<int*>(s.arena + L.sync);
+            const int ntiles = flow_tiles(h, w, n);
+            rp.progress = sync; rp.abort = sync + ntiles; rp.status = flow_status_device_ptr();
+            rp.g_first = its_eff - 2;
+            rp.nblocks = nfull;
+            rp.N = n; rp.C = ch; rp.H = h; rp.W = w; rp.P = P;
+            fill_flow_tables(s, its_eff, rp.tab);
+            CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0, L.sync_words * sizeof(int), st), "zero progress counters"));
+            CNL_TRY(launch_tv_rev_flow(rp, st));
+            g_cur = rp.gbuf[(nfull - 1) & 1];
+            acc_cur = rp.abuf[(nfull - 1) & 1];
+            flip = nfull & 1;
+            g_start -= nfull * kFuseMax;
+        }
+        for (int g0 = g_start; g0 >= 0;) {
             int K = std::min(fuse, g0 + 1);
             if (s.recompute) {
                 if (g0 < seg_begin(s.sched, seg)) {          // entering the next older segment: rebuild its history
@@ -880,8 +949,10 @@ extern "C" int cnl_tv_release(int id) {
         for (int i = 0; i < Slot::kRing; ++i)
             for (int j = 0; j < 2; ++j) { cudaEventDestroy(sp->ev_fwd[i][j]); cudaEventDestroy(sp->ev_rev[i][j]); }
     const int keep_cond = sp->opt_conditioner, keep_fuse = sp->opt_fuse, keep_rec = sp->opt_recompute, keep_gen = sp->generation;
+    const int keep_flow = sp->opt_flow;
     *sp = Slot();
     sp->generation = keep_gen;
+    sp->opt_flow = keep_flow;
     sp->opt_conditioner = keep_cond;
     sp->opt_fuse = keep_fuse;
     sp->opt_recompute = keep_rec;
@@ -929,7 +1000,7 @@ extern "C" int cnl_tv_num_checkpoints(int id) {
 
 extern "C" int cnl_tv_set_option(int id, int option, int value) {
     if (id < 0 || id >= CNL_NUM_IDS) return fail(CNL_ERR_BAD_ID, "id %d is outside 0..%d", id, CNL_NUM_IDS - 1);
-    if (option < CNL_OPT_CONDITIONER || option > CNL_OPT_RECOMPUTE)      // rejected before anything touches the device
+    if (option < CNL_OPT_CONDITIONER || option > CNL_OPT_FLOW)      // rejected before anything touches the device
         return fail(CNL_ERR_BAD_OPTION, "unknown option %d", option);
     std::lock_guard<std::mutex> lock(g_mutex);
     int rc;
@@ -942,6 +1013,7 @@ extern "C" int cnl_tv_set_option(int id, int option, int value) {
             sp->n_fwd = sp->n_rev = 0;
             return CNL_OK;
         case CNL_OPT_RECOMPUTE: sp->opt_recompute = value ? 1 : 0; return CNL_OK;
+        case CNL_OPT_FLOW: sp->opt_flow = (value == 2) ? 2 : (value ? 1 : 0); return CNL_OK;
         case CNL_OPT_FUSE:
             if (value < 0 || value > 4) return fail(CNL_ERR_BAD_OPTION, "fuse factor %d is outside 0..4", value);
             sp->opt_fuse = value;

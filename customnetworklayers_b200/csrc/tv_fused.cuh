@@ -55,6 +55,68 @@ struct RevFusedParams {
     int P;                      // row pitch in floats, as in FwdFusedParams
 };
 
+// ---- single-launch sweeps (tv_flow.cu) -------------------------------------------------------------------------------
+// All time blocks of kFuseMax iterations run in one cooperative launch; tiles of consecutive time blocks are ordered
+// through per-tile progress counters in global memory instead of launch boundaries.
+constexpr int kFlowMaxIts = 512;     // the per-iteration tables travel as kernel parameters
+
+struct FlowTables {
+    float t[kFlowMaxIts];                 // momentum factor of iteration g
+    signed char ckpt_slot[kFlowMaxIts];   // index of the checkpoint taken before iteration g, or -1
+};
+
+struct FwdFlowParams {
+    const float* init;          // y and x entering time block 0
+    float* ybuf[2];             // time block kb writes ybuf[kb & 1] and reads ybuf[(kb - 1) & 1]
+    float* xbuf[2];
+    const float* b;
+    const float* c;
+    const float* wx;
+    const float* wy;
+    float* hist;                // x^{g+1/2} of iteration g goes to hist + g * vol
+    float* ckpt;                // checkpoint k goes to ckpt + k * vol
+    size_t vol;                 // floats between consecutive stored iterates
+    int* progress;              // one counter per tile, zero at launch
+    int* abort;                 // device word, zero at launch; set when a wait gave up
+    int* status;                // host-mapped word that receives the reason
+    int nblocks;                // time blocks of kFuseMax iterations
+    int N, C, H, W;
+    int P;                      // row pitch in floats, as in FwdFusedParams
+    FlowTables tab;
+};
+
+struct RevFlowParams {
+    float* gbuf[2];             // time block kb reads gbuf[(kb + 1) & 1] (block 0: the seed) and writes gbuf[kb & 1]
+    float* abuf[2];             // same for the pending momentum term
+    const float* b;
+    const float* c;
+    const float* wx;
+    const float* wy;
+    const float* hist;
+    const float* ckpt;
+    size_t vol;
+    float* g_c;
+    float* g_b;
+    float* g_wx;
+    float* g_wy;
+    float* x1bar;               // written by the time block that ends at iteration 0, if this launch reaches it
+    int* progress;
+    int* abort;
+    int* status;
+    int g_first;                // iteration of the first reverse step of time block 0
+    int nblocks;
+    int N, C, H, W;
+    int P;
+    FlowTables tab;
+};
+
+bool flow_enabled();                       // cooperative launch available and CNL_TV_NO_FLOW not set
+int flow_status_take();                    // CNL_OK, or an error if an earlier single-launch sweep gave up a wait
+int* flow_status_device_ptr();             // device view of the host-mapped status word of the current device
+int flow_tiles(int H, int W, int N);       // tiles (= progress counters) of a launch
+int launch_tv_fwd_flow(const FwdFlowParams& p, cudaStream_t st);
+int launch_tv_rev_flow(const RevFlowParams& p, cudaStream_t st);
+
 // True if the fused kernels can run directly on these tensors: 16-byte vectors need a row pitch divisible by 4 and
 // aligned base pointers.  Otherwise the driver stages zero-padded copies with such a pitch.
 bool fused_supported(int W, const void* const* ptrs, int nptr);

@@ -1,11 +1,17 @@
 """Forward + backward of the TV layer for callers whose tensors live in (pinned) HOST memory.
 
-The batch is cut into chunks; the host->device copy of chunk k+1 and the device->host copy of chunk k-1 run on
-their own CUDA streams while chunk k is being solved, so PCIe traffic in both directions overlaps the kernels.
+Three CUDA streams work side by side: host->device copies, kernels, device->host copies.  Within one call the batch
+is cut into chunks, so that the kernels of chunk k run while chunk k+1 arrives and the results of chunk k-1 leave.
+Across calls nothing waits for the previous call to drain: the inputs land in one of `depth` (default 2) sets of
+device buffers owned by the pipeline, so the copies of the next call run under the kernels of the current one and
+the gradients of the current call leave under the kernels of the next.  A call returns as soon as its work is
+enqueued; `HostPipeline.join()` makes the current stream wait for every result copy issued so far (a host-side
+`torch.cuda.synchronize()` does as well), after which the pinned output tensors are valid.
+
 One id slot is enough: forward(k) and backward(k) are consecutive on the compute stream."""
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
 import torch
 
@@ -16,67 +22,138 @@ IN_KEYS = ("wx", "wy", "c", "b", "init", "grad")
 OUT_KEYS = ("sol", "g_wx", "g_wy", "g_c", "g_b", "g_init")
 
 
-class HostPipeline:
-    """Reusable streams for tv_fwd_bwd_from_host on one device."""
+class _InputSet:
+    """One set of device buffers for the six input tensors of a call, plus the event after which it may be refilled."""
 
-    def __init__(self, device):
+    def __init__(self):
+        self.buf: Dict[str, torch.Tensor] = {}
+        self.free: Optional[torch.cuda.Event] = None
+
+    def fit(self, host_in: Dict[str, torch.Tensor], device) -> None:
+        for k in IN_KEYS:
+            t = host_in[k]
+            if k not in self.buf or self.buf[k].shape != t.shape:
+                self.buf[k] = torch.empty(t.shape, dtype=torch.float32, device=device)
+
+
+class HostPipeline:
+    """Streams and device-side input buffers for tv_fwd_bwd_from_host on one device."""
+
+    def __init__(self, device, depth: int = 2):
         self.device = torch.device(device)
         self.s_in = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
+        self.sets: List[_InputSet] = [_InputSet() for _ in range(max(1, depth))]
+        self.turn = 0
+        self.last_out: Optional[torch.cuda.Event] = None
+        self.timeline = None            # set to a list to collect per-chunk CUDA events (see chunk_breakdown)
+
+    def join(self) -> None:
+        """The current stream waits for every device->host copy issued so far."""
+        if self.last_out is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.last_out)
+
+    def chunk_breakdown(self):
+        """After a synchronise: per recorded chunk, milliseconds from the start of the call to (inputs landed, forward
+        done, backward done, gradients back in host memory).  Needs `timeline = []` before the calls."""
+        rows = []
+        for t0, ev in self.timeline or []:
+            rows.append({k: t0.elapsed_time(e) for k, e in ev.items()})
+        return rows
+
+
+def _chunks(n: int, chunk) -> List[tuple]:
+    """[lo, hi) ranges: `chunk` is a size or a sequence of sizes (the last size repeats until the batch is covered)."""
+    sizes = [int(chunk)] if isinstance(chunk, int) else [int(c) for c in chunk]
+    if not sizes or min(sizes) < 1:
+        raise ValueError("chunk sizes must be >= 1")
+    out, lo, i = [], 0, 0
+    while lo < n:
+        hi = min(n, lo + sizes[min(i, len(sizes) - 1)])
+        out.append((lo, hi))
+        lo, i = hi, i + 1
+    return out
 
 
 def tv_fwd_bwd_from_host(pipe: HostPipeline, host_in: Dict[str, torch.Tensor], host_out: Dict[str, torch.Tensor],
-                         its: int, pid: int, lam: Optional[torch.Tensor] = None, chunk: int = 2,
+                         its: int, pid: int, lam: Optional[torch.Tensor] = None, chunk=2,
                          host_lam_grad: Optional[torch.Tensor] = None):
     """Solves c = lam * host_in["c"] problems from pinned host tensors and writes the solution and the five
     gradients into pinned host tensors (host_out), plus the all-reduced lambda gradient into host_lam_grad.
 
     host_in : wx, wy, c [N,1,H,W]; b, init, grad [N,C,H,W]  (grad = upstream gradient of the solution)
     host_out: sol, g_b, g_init [N,C,H,W]; g_wx, g_wy, g_c [N,1,H,W]
-    Returns the lambda gradient as a 1-element CUDA tensor.  The caller synchronises (e.g. torch.cuda.synchronize())
-    before reading host_out."""
+    Returns the lambda gradient as a 1-element CUDA tensor.  Nothing here blocks the host; the pinned outputs are
+    valid after pipe.join() followed by a synchronise of the current stream, or after torch.cuda.synchronize().
+    host_in must not be rewritten before its copies have run (an event on pipe.s_in or a synchronise tells)."""
     dev = pipe.device
     comp = torch.cuda.current_stream(dev)
     n = host_in["b"].shape[0]
-    keep = []
-    g_lam = torch.zeros(1, device=dev)
-    start = torch.cuda.Event()
-    start.record(comp)
-    pipe.s_in.wait_event(start)           # do not run ahead of work already queued on the compute stream
-    pipe.s_out.wait_event(start)
-    for lo in range(0, n, chunk):
-        hi = min(n, lo + chunk)
-        with torch.cuda.stream(pipe.s_in):
+    slot = pipe.sets[pipe.turn]
+    pipe.turn = (pipe.turn + 1) % len(pipe.sets)
+    slot.fit(host_in, dev)
+    ranges = _chunks(n, chunk)
+    record = pipe.timeline is not None
+    t0 = None
+    if record:
+        t0 = torch.cuda.Event(enable_timing=True)
+        t0.record(comp)
+        pipe.s_in.wait_event(t0)          # measured from a common origin; costs the overlap with the previous call
+    if slot.free is not None:
+        pipe.s_in.wait_event(slot.free)   # the kernels that read this set two calls ago are done
+    ev_in, ev_grad = [], []
+    with torch.cuda.stream(pipe.s_in):
+        for lo, hi in ranges:
             # what the forward pass needs first; the upstream gradient follows behind it
-            d = {k: host_in[k][lo:hi].to(dev, non_blocking=True) for k in IN_KEYS if k != "grad"}
-            ev_in = torch.cuda.Event()
-            ev_in.record(pipe.s_in)
-            d["grad"] = host_in["grad"][lo:hi].to(dev, non_blocking=True)
-            ev_grad = torch.cuda.Event()
-            ev_grad.record(pipe.s_in)
-        comp.wait_event(ev_in)
+            for k in IN_KEYS[:-1]:
+                slot.buf[k][lo:hi].copy_(host_in[k][lo:hi], non_blocking=True)
+            e = torch.cuda.Event(enable_timing=record)
+            e.record(pipe.s_in)
+            ev_in.append(e)
+            slot.buf["grad"][lo:hi].copy_(host_in["grad"][lo:hi], non_blocking=True)
+            e = torch.cuda.Event()
+            e.record(pipe.s_in)
+            ev_grad.append(e)
+    g_lam = torch.zeros(1, device=dev)
+    for i, (lo, hi) in enumerate(ranges):
+        d = {k: slot.buf[k][lo:hi] for k in IN_KEYS}
+        comp.wait_event(ev_in[i])
         c = d["c"] * lam if lam is not None else d["c"]
         sol = ext.forward(d["wx"], d["wy"], c, d["b"], d["init"], its, pid)[0]
-        ev_f = torch.cuda.Event()
+        ev_f = torch.cuda.Event(enable_timing=record)
         ev_f.record(comp)
         pipe.s_out.wait_event(ev_f)
+        sol.record_stream(pipe.s_out)
         with torch.cuda.stream(pipe.s_out):          # the solution goes back while the backward pass runs
             host_out["sol"][lo:hi].copy_(sol, non_blocking=True)
-        comp.wait_event(ev_grad)
+        comp.wait_event(ev_grad[i])
         grads = ext.backward(d["grad"], d["wx"], d["wy"], c, d["b"], its, pid)
         g_lam += ext.lambda_grad(grads[2], d["c"])
-        ev_c = torch.cuda.Event()
-        ev_c.record(comp)
-        pipe.s_out.wait_event(ev_c)
+        ev_b = torch.cuda.Event(enable_timing=record)
+        ev_b.record(comp)
+        pipe.s_out.wait_event(ev_b)
         with torch.cuda.stream(pipe.s_out):
             for key, t in zip(OUT_KEYS[1:], grads):
+                t.record_stream(pipe.s_out)
                 host_out[key][lo:hi].copy_(t, non_blocking=True)
-        keep.append((d, c, sol, grads))
+            ev_o = torch.cuda.Event(enable_timing=record)
+            ev_o.record(pipe.s_out)
+        pipe.last_out = ev_o
+        if record:
+            pipe.timeline.append((t0, {"inputs_landed": ev_in[i], "forward_done": ev_f, "backward_done": ev_b,
+                                       "gradients_in_host_memory": ev_o}))
+    slot.free = torch.cuda.Event()
+    slot.free.record(comp)
     allreduce_scalar_grads(g_lam)
-    done = torch.cuda.Event()
-    done.record(pipe.s_out)
-    comp.wait_event(done)                 # the compute stream now covers the copies too
     if host_lam_grad is not None:
-        host_lam_grad.copy_(g_lam, non_blocking=True)
-    pipe._keep = keep                     # keep device tensors alive until the next call / a synchronise
+        # on the copy stream: a device->host copy issued on the compute stream would queue behind the gradient copies
+        # in the copy engine and hold the next call's kernels back for as long as those take
+        ev_l = torch.cuda.Event()
+        ev_l.record(comp)
+        pipe.s_out.wait_event(ev_l)
+        g_lam.record_stream(pipe.s_out)
+        with torch.cuda.stream(pipe.s_out):
+            host_lam_grad.copy_(g_lam, non_blocking=True)
+            pipe.last_out = torch.cuda.Event()
+            pipe.last_out.record(pipe.s_out)
     return g_lam

@@ -46,6 +46,14 @@ extern "C" {
                                    segment at a time, as the reference does (cudaTV/cudaCode/TVInpaintFista.cu:1690-1760).
                                    Costs one extra forward sweep per backward pass; not available with
                                    CNL_OPT_FUSE = 1 */
+#define CNL_OPT_FLOW 5          /* 1 (default): a sweep of 4-iteration time blocks runs as ONE cooperative launch whose tiles are
+                                   ordered by per-tile progress counters in device memory (no launch boundary, no idle tail
+                                   between time blocks); 0: one launch per time block.  Both give the same bits.  Applies with
+                                   CNL_OPT_FUSE = 0 or 4, every iterate resident and at most 512 iterations; environment
+                                   variable CNL_TV_NO_FLOW=1 switches it off for the whole process.  A wait on a neighbouring
+                                   tile that does not end within about a second makes the sweep stop; the next call on the
+                                   device then returns CNL_ERR_CUDA with that reason.  Value 2 is a self-test of exactly that: the next
+                                   forward sweep starts from counters no tile can satisfy, so its waits run out */
 
 /*
  * Forward pass of the unrolled FISTA TV-inpainting layer: 2*floor(its/2) iterations starting from x = y = init.

@@ -118,9 +118,16 @@ def test_tgv_full_size_image_matches_oracle():
         assert_close(cky, r_cky, "checkpointed y")
         del r_hist
         ref = G.tgv_backward(I["dx"], I["dy"], I["c"], I["b"], I["grad"], its, hist, cky)
-        for name, g, r in zip(TGV_NAMES, grads, ref):
-            print(name, "reverse sweep on device iterates", rel_errors(g, r))
-            assert_close(g, r, name)
+        # Even on identical stored iterates the sweep decides its Huber branches from a y it rebuilds, in fp32 on the
+        # device and in fp64 in the oracle: at this size (446,464 pixels x 100 steps) a pixel within an ulp of a
+        # threshold can take the other branch.  The oracle's own fp32 run on the same iterates measures that.
+        ref32 = G.tgv_backward(I["dx"], I["dy"], I["c"], I["b"], I["grad"], its, hist, cky, dtype=torch.float32)
+        for name, g, r, r32 in zip(TGV_NAMES, grads, ref, ref32):
+            e, gap = rel_errors(g, r), rel_errors(r32, r)
+            print(f"{name}: reverse sweep on device iterates max {e[0]:.2e} l2 {e[1]:.2e} | oracle fp32-vs-fp64 on the "
+                  f"same iterates max {gap[0]:.2e} l2 {gap[1]:.2e}")
+            assert e[1] <= REL_TOL, f"{name}: l2 {e[1]:.2e}"
+            _bounded_in_both_norms("reverse sweep on device iterates", name, e, gap)
     finally:
         ext.set_option(pid, 1, 1)
         ext.release(pid)

@@ -297,11 +297,11 @@ def test_conditioner_kill_branch_matches_oracle_state_machine(ext):
 
 
 def test_nonfinite_returned_gradient_after_ten_runs_is_killed(ext):
-    """A confidence of -1 at one pixel makes 1/(1+c) infinite there, so NaNs spread through a patch of the iterates and
-    into the returned gradients.  The sanitiser zeroes them; after ten runs the conditioner treats such a gradient as a
-    spike (running mean restarted from 1000 x its value, TVInpaintFista.cu:171) and zeroes the whole tensor.  The
-    reference's mean then depends on where the entry sits; here it does not, so only the outcome is checked: finite
-    outputs, the affected tensors zeroed, and ordinary gradients again on the next clean run."""
+    """A NaN in the data term at one pixel spreads through a patch of the iterates and into the returned gradients.
+    The sanitiser zeroes such entries; after ten runs the conditioner treats a gradient that contained one as a spike
+    (running mean restarted from 1000 x its value, TVInpaintFista.cu:171) and zeroes the whole tensor.  The reference's
+    mean then depends on where the entry sits; here it does not, so only the outcome is checked: finite outputs, the
+    affected tensors zeroed, and ordinary gradients again on the next clean run."""
     n, ch, h, w, its = 1, 2, 16, 24, 6
     I = R.make_inputs(n, ch, h, w, seed=14)
     D = _dev(I)
@@ -311,12 +311,12 @@ def test_nonfinite_returned_gradient_after_ten_runs_is_killed(ext):
     for r in range(11):
         ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, 0)
         clean = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], D["b"], its, 0)
-    bad_c = D["c"].clone()
-    bad_c[0, 0, 12, 17] = -1.0
-    ext.forward(D["wx"], D["wy"], bad_c, D["b"], D["init"], its, 0)
+    bad_b = D["b"].clone()
+    bad_b[0, 0, 12, 17] = float("nan")
+    ext.forward(D["wx"], D["wy"], D["c"], bad_b, D["init"], its, 0)
     hist, _ = ext.read_history(0, D["b"], its)
     assert not bool(torch.isfinite(hist).all()), "the iterates must contain non-finite values for this test to bite"
-    grads = ext.backward(D["grad"], D["wx"], D["wy"], bad_c, D["b"], its, 0)
+    grads = ext.backward(D["grad"], D["wx"], D["wy"], D["c"], bad_b, its, 0)
     assert all(bool(torch.isfinite(g).all()) for g in grads)
     assert float(grads[2].abs().max()) == 0.0 and float(grads[3].abs().max()) == 0.0, "g_c and g_b carried NaNs: killed"
     ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], its, 0)
@@ -324,6 +324,67 @@ def test_nonfinite_returned_gradient_after_ten_runs_is_killed(ext):
     for name, a, b2 in zip(GRAD_NAMES, again, clean):
         assert torch.equal(a, b2), name + ": a clean run after the spike is an ordinary run"
     ext.release(0)
+
+
+FLOW_CASES = [(2, 2, 40, 72, 20), (1, 3, 33, 64, 21), (1, 2, 100, 260, 14), (3, 1, 50, 128, 8), (1, 2, 384, 1280, 100),
+              (5, 2, 384, 1280, 12)]
+
+
+@pytest.mark.parametrize("split", ["auto", "0", "1"])
+@pytest.mark.parametrize("case", FLOW_CASES, ids=lambda c: "n%d_c%d_%dx%d_its%d" % c)
+def test_single_launch_sweep_gives_the_bits_of_one_launch_per_time_block(ext, case, split, monkeypatch):
+    """The cooperative single-launch sweeps (tiles ordered by progress counters) and the one-launch-per-time-block path
+    run the same arithmetic on the same tiles, so every stored iterate, checkpoint, solution and gradient must be equal
+    bit for bit; work units of whole tiles and of single (tile, channel) pairs alike."""
+    from customnetworklayers_b200 import _lib
+    n, ch, h, w, its = case
+    if split != "auto":
+        if h * w > 100000:
+            pytest.skip("forced unit shapes are exercised on the small cases")
+        monkeypatch.setenv("CNL_TV_FLOW_SPLIT", split)
+    D = _dev(R.make_inputs(n, ch, h, w, seed=31 + h + w))
+    a_id, b_id = 2, 3
+    res = {}
+    for pid, flow in ((a_id, 1), (b_id, 0)):
+        ext.release(pid)
+        ext.set_option(pid, _lib.OPT_CONDITIONER, 0)
+        ext.set_option(pid, _lib.OPT_FLOW, flow)
+        try:
+            res[flow] = _run_cuda(ext, D, its, pid)
+        finally:
+            ext.set_option(pid, _lib.OPT_FLOW, 1)
+            ext.set_option(pid, _lib.OPT_CONDITIONER, 1)
+    for name, a, b2 in zip(("solution", "history", "checkpoints"), res[1][:3], res[0][:3]):
+        assert torch.equal(a, b2), name
+    for name, a, b2 in zip(GRAD_NAMES, res[1][3], res[0][3]):
+        assert torch.equal(a, b2), name
+    ext.release(a_id)
+    ext.release(b_id)
+
+
+def test_a_wait_that_cannot_end_stops_the_sweep_and_is_reported(ext):
+    """Bounded waits: with progress counters that no tile can satisfy (self-test value of the option) the sweep's waits
+    run out after about a second, every CTA leaves, the context stays usable and the next call reports what happened."""
+    from customnetworklayers_b200 import _lib
+    D = _dev(R.make_inputs(1, 2, 40, 72, seed=5))
+    pid = 2
+    ext.release(pid)
+    ext.set_option(pid, _lib.OPT_FLOW, 2)
+    try:
+        ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], 12, pid)
+        torch.cuda.synchronize()                     # returns: nothing hangs
+    finally:
+        ext.set_option(pid, _lib.OPT_FLOW, 1)
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], 12, pid)
+    # reported once; the library works as before afterwards
+    sol = ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], 12, pid)[0]
+    ext.set_option(3, _lib.OPT_FLOW, 0)
+    ref = ext.forward(D["wx"], D["wy"], D["c"], D["b"], D["init"], 12, 3)[0]
+    ext.set_option(3, _lib.OPT_FLOW, 1)
+    assert torch.equal(sol, ref)
+    ext.release(pid)
+    ext.release(3)
 
 
 def test_host_pipeline_matches_direct_calls(ext):
