@@ -304,9 +304,13 @@ def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, war
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         launches0 = _lib.load().cnl_launch_count()
+        marks = []
         e0.record()
         for _ in range(nsteps):
             fn()
+            m = torch.cuda.Event(enable_timing=True)
+            m.record()
+            marks.append(m)
         if finish:
             finish()                  # the timed stream waits for the last result copy before the closing event
         e1.record()
@@ -315,6 +319,8 @@ def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, war
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         launches = _lib.load().cnl_launch_count() - launches0
+        per_step = [a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks)]      # compute-stream time between steps
+        timed.last_per_step = per_step
         return float(ms.item()), launches, (sampler.stop() if sampler else None)
 
     for _ in range(warmup):
@@ -326,6 +332,7 @@ def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, war
     for _ in range(max(3, min(3, warmup))):
         step_e2e()
     ms_e2e, _, _ = timed(step_e2e, steps, finish=pipe.join)
+    e2e_steps = sorted(timed.last_per_step)
     # where an end-to-end step spends its time: one call alone, CUDA events per chunk from the call's start
     breakdown = None
     if rank == 0:
@@ -338,7 +345,8 @@ def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, war
     barrier()
     res = {"nb": nb, "ms": ms, "launches": launches, "clocks": clocks, "tm": tm, "ms_e2e": ms_e2e, "chunk": chunk,
            "h2d": sum(host[k].numel() * 4 for k in keys), "d2h": sum(t.numel() * 4 for t in host_res.values()) + 4,
-           "breakdown": breakdown}
+           "breakdown": breakdown,
+           "e2e_step_ms": {"min": e2e_steps[0], "median": e2e_steps[len(e2e_steps) // 2], "max": e2e_steps[-1]}}
     del D, host, host_res, pipe
     ext.release(pid)
     torch.cuda.empty_cache()
@@ -421,6 +429,7 @@ def run_ours(args, rank, local_rank, world):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": M["h2d"], "d2h_bytes_per_step": M["d2h"],
                     "ms_per_step": ms_e2e / args.steps, "api": "host_pipeline.tv_fwd_bwd_from_host",
                     "chunk_images": M["chunk"],
+                    "step_ms_on_compute_stream": M["e2e_step_ms"],
                     "single_call_ms_since_start": M["breakdown"]},
             "gpu_launches": int(M["launches"]),
             "clocks": M["clocks"],

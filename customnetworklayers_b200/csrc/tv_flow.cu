@@ -165,16 +165,18 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
         float* const x_out = p.xbuf[cur.kb & 1];
         const int g0 = cur.kb * K;
         float4 c[kRows], wx[kRows], wy[kRows];
+        // Is the CTA's next unit ready?  Warp 0 fetches the counters of its neighbourhood (acquire loads) at the start of
+        // the unit's last channel and looks at them before the second barrier of the first fused step, so that the round
+        // trip to L2 hides behind the arithmetic in between.  (A relaxed load followed by a fence costs 6 % of the sweep:
+        // the fence waits for the stores the whole CTA has in flight.)
         bool next_issued = false;
         for (int ch = 0; ch < p.C; ++ch) {
             const bool last_ch = ch + 1 == p.C;
-            // Readiness of the next unit: the counters are fetched here, looked at only before the second barrier of
-            // the first fused step, so that the round trip to L2 hides behind the arithmetic in between.
             int seen = INT_MAX;
             if (last_ch && has_next && warp == 0 && nxt.kb > 0) {
                 bool valid;
                 const int* addr = neighbour_counter(sync.progress, nxt.tc, tiles_x, tiles_y, valid);
-                if (valid) seen = ld_relaxed_gpu(addr);
+                if (valid) seen = ld_acquire_gpu(addr);
             }
             cp_async_wait_all();
             if (ch == 0) {
@@ -215,7 +217,6 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
                 sh_f[g.warp][g.lane] = fyl;
                 if (j == 0 && last_ch && has_next && warp == 0) {
                     const int ok = __all_sync(kFull, seen >= nxt.kb);
-                    if (ok) __threadfence();           // acquire side of the hand-over: the counters were read relaxed
                     if (lane == 0) sh_ctl[1] = ok;
                 }
                 __syncthreads();
@@ -265,21 +266,26 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
 // ---------------------------------------------------------------------------------------------------------------
 // reverse sweep: p.nblocks time blocks of K reverse iterations in one launch; a unit is one tile with all its channels
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kRevFlowSmemBytes = (5 * kRows * kThreads + 3 * kWarps * 32) * (int)sizeof(float4);
+// Per-step inputs of one time block: addresses and factors follow from the iteration number.
+struct FlowSteps {
+    const RevFlowParams& p;
+    int gfirst;                 // iteration of the block's first reverse step
+    __device__ __forceinline__ const float* hist(int j) const {
+        return gfirst - j >= 0 ? p.hist + (size_t)(gfirst - j) * p.vol : nullptr;
+    }
+    __device__ __forceinline__ const float* ckpt(int j) const {
+        const int slot = p.tab.ckpt_slot[gfirst - j];
+        return slot >= 0 ? p.ckpt + (size_t)slot * p.vol : nullptr;
+    }
+    __device__ __forceinline__ float t(int j) const { return p.tab.t[gfirst - j]; }
+};
 
 template <int K>
 __global__ void __launch_bounds__(kThreads, 1)
 tv_rev_flow_kernel(const __grid_constant__ RevFlowParams p, int tiles_x, int tiles_y) {
     extern __shared__ float4 smem[];
     __shared__ int sh_ctl[2];
-    float4* sh_dc = smem;                                  // [kRows][kThreads] per-thread accumulators over channels
-    float4* sh_dwx = sh_dc + kRows * kThreads;
-    float4* sh_dwy = sh_dwx + kRows * kThreads;
-    float4* sh_db = sh_dwy + kRows * kThreads;             // per channel
-    float4* sh_xn = sh_db + kRows * kThreads;              // private landing slots of the prefetched pre-prox iterate
-    float4(*sh_y)[32] = reinterpret_cast<float4(*)[32]>(sh_xn + kRows * kThreads);    // first rows of y
-    float4(*sh_g)[32] = sh_y + kWarps;                                               // first rows of g
-    float4(*sh_p)[32] = sh_g + kWarps;                                               // last-row vertical adjoint flux
+    const RevSmem sh = rev_smem(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntiles = tiles_x * tiles_y * p.N;
     const int total = ntiles * p.nblocks;
@@ -308,12 +314,7 @@ tv_rev_flow_kernel(const __grid_constant__ RevFlowParams p, int tiles_x, int til
             const TileGeom g = make_geom_at<K>(tc.tx, tc.ty, p.H, p.W);
             load_maps(p, g, (size_t)tc.n, c, wx, wy);
         }
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            sh_dc[r * kThreads + threadIdx.x] = zero4();
-            sh_dwx[r * kThreads + threadIdx.x] = zero4();
-            sh_dwy[r * kThreads + threadIdx.x] = zero4();
-        }
+        rev_tile_begin(sh, c);
         int seen = INT_MAX;
         for (int ch = 0; ch < p.C; ++ch) {
             const int uo = opaque(u);
@@ -329,141 +330,32 @@ tv_rev_flow_kernel(const __grid_constant__ RevFlowParams p, int tiles_x, int til
                     bool valid;
                     const int* addr = neighbour_counter(sync.progress, tile_coord(un - kb_next * ntiles, tiles_x, tiles_y),
                                                         tiles_x, tiles_y, valid);
-                    if (valid) seen = ld_relaxed_gpu(addr);
+                    if (valid) seen = ld_acquire_gpu(addr);
                 }
             }
-            const float* const g_in = p.gbuf[(kb + 1) & 1];
-            const float* const acc_in = p.abuf[(kb + 1) & 1];
-            const int gfirst = p.g_first - K * kb;              // iteration of this block's first reverse step
-            float4 gq[kRows], acc[kRows], b[kRows], xh[kRows], xhm[kRows];
+            const FlowSteps steps{p, p.g_first - K * kb};
             size_t off[kRows];
-            const float* const h0 = p.hist + (size_t)gfirst * p.vol;
-            const bool has_h1 = gfirst - 1 >= 0;
 #pragma unroll
-            for (int r = 0; r < kRows; ++r) {
-                off[r] = ((size_t)tc.n * p.C + ch) * plane + (size_t)g.gy[r] * p.P + g.gx;
-                gq[r] = ld4_l2(g_in + off[r], g.ok[r]);
-                acc[r] = ld4_l2(acc_in + off[r], g.ok[r]);
-                b[r] = ld4(p.b + off[r], g.ok[r]);
-                xh[r] = ld4(h0 + off[r], g.ok[r]);
-                xhm[r] = ld4(h0 - p.vol + off[r], g.ok[r] && has_h1);
-                sh_db[r * kThreads + threadIdx.x] = zero4();
-            }
-#pragma unroll
-            for (int j = 0; j < K; ++j) {
-                const int gi = gfirst - j;
-                const float t = p.tab.t[gi];
-                const int slot = p.tab.ckpt_slot[gi];
-                // prefetch the pre-prox iterate the next fused step needs
-                if (j + 2 <= K) {
-                    const bool have = gi - 2 >= 0;
-                    const float* src = p.hist + (size_t)(have ? gi - 2 : 0) * p.vol;
-#pragma unroll
-                    for (int r = 0; r < kRows; ++r) {
-                        const bool okr = g.ok[r] && have;
-                        cp_async16(sh_xn + r * kThreads + threadIdx.x, okr ? src + off[r] : p.b, okr);
-                    }
-                    cp_async_commit();
-                }
-                float4 y[kRows];
-                if (slot >= 0) {
-                    const float* ck = p.ckpt + (size_t)slot * p.vol;
-#pragma unroll
-                    for (int r = 0; r < kRows; ++r) y[r] = ld4(ck + off[r], g.ok[r]);
-                } else {
-#pragma unroll
-                    for (int r = 0; r < kRows; ++r) y[r] = rederive_row(xh[r], xhm[r], b[r], c[r], t);
-                }
-                sh_y[g.warp][g.lane] = y[0];
-                sh_g[g.warp][g.lane] = gq[0];
-                __syncthreads();
-                const bool has_below = g.warp + 1 < kWarps;
-                const float4 ybelow = has_below ? sh_y[g.warp + 1][g.lane] : zero4();
-                const float4 gbelow = has_below ? sh_g[g.warp + 1][g.lane] : zero4();
-                float4 p1l, p2l, dwxl, dwyl;
-                adjoint_row(y[kRows - 1], ybelow, gq[kRows - 1], gbelow, wx[kRows - 1], wy[kRows - 1], p1l, p2l, dwxl, dwyl);
-                sh_p[g.warp][g.lane] = p2l;
-                add4(sh_dwx[(kRows - 1) * kThreads + threadIdx.x], dwxl);
-                add4(sh_dwy[(kRows - 1) * kThreads + threadIdx.x], dwyl);
-                __syncthreads();
-                float4 p2c = (g.warp > 0) ? sh_p[g.warp - 1][g.lane] : zero4();
-#pragma unroll
-                for (int r = 0; r < kRows; ++r) {
-                    float4 p1, p2;
-                    if (r == kRows - 1) { p1 = p1l; p2 = p2l; }
-                    else {
-                        float4 ax, ay;
-                        adjoint_row(y[r], y[r + 1], gq[r], gq[r + 1], wx[r], wy[r], p1, p2, ax, ay);
-                        add4(sh_dwx[r * kThreads + threadIdx.x], ax);
-                        add4(sh_dwy[r * kThreads + threadIdx.x], ay);
-                    }
-                    const float p1_left = __shfl_up_sync(kFull, p1.w, 1);
-                    const float4 ybar = divergence_row(gq[r], p1, p2, p1_left, p2c);
-                    p2c = p2;
-                    float4 xb;
-                    float4 dc = sh_dc[r * kThreads + threadIdx.x];
-                    float4 db = sh_db[r * kThreads + threadIdx.x];
-                    gq[r] = reverse_row(ybar, acc[r], xh[r], b[r], c[r], t, dc, db, xb);
-                    sh_dc[r * kThreads + threadIdx.x] = dc;
-                    sh_db[r * kThreads + threadIdx.x] = db;
-                    if (j == K - 1 && gi == 0 && p.x1bar != nullptr && g.store[r]) st4(p.x1bar + off[r], xb);
-                }
-                cp_async_wait_all();
-#pragma unroll
-                for (int r = 0; r < kRows; ++r) {
-                    xh[r] = xhm[r];
-                    xhm[r] = (j + 2 <= K) ? sh_xn[r * kThreads + threadIdx.x] : zero4();
-                }
-            }
-            {
-                const int kbo = opaque(u) / ntiles;
-                float* const g_out = p.gbuf[kbo & 1];
-                float* const acc_out = p.abuf[kbo & 1];
-#pragma unroll
-                for (int r = 0; r < kRows; ++r) {
-                    if (g.store[r]) {
-                        st4(g_out + off[r], gq[r]);
-                        st4(acc_out + off[r], acc[r]);
-                        red_add4(p.g_b + off[r], sh_db[r * kThreads + threadIdx.x]);
-                    }
-                }
-            }
+            for (int r = 0; r < kRows; ++r) off[r] = ((size_t)tc.n * p.C + ch) * plane + (size_t)g.gy[r] * p.P + g.gx;
+            rev_channel<K, true>(sh, g, off, p.gbuf[(kb + 1) & 1], p.abuf[(kb + 1) & 1], p.b, p.gbuf[kb & 1], p.abuf[kb & 1],
+                                 p.g_b, steps.gfirst - K + 1 == 0 ? p.x1bar : nullptr, c, wx, wy, steps, [](int) {});
         }
-        // per-pixel gradients shared by all channels
         const int ue = opaque(u);
         const int kbe = ue / ntiles;
         const int tile = ue - kbe * ntiles;
         {
             const TileCoord tc = tile_coord(tile, tiles_x, tiles_y);
-            const TileGeom g = make_geom_at<K>(tc.tx, tc.ty, p.H, p.W);
-#pragma unroll
-            for (int r = 0; r < kRows; ++r) {
-                if (!g.store[r]) continue;
-                const size_t o = (size_t)tc.n * plane + (size_t)g.gy[r] * p.P + g.gx;
-                const float4 dc = sh_dc[r * kThreads + threadIdx.x];
-                float4 ax = sh_dwx[r * kThreads + threadIdx.x];
-                float4 ay = sh_dwy[r * kThreads + threadIdx.x];
-                const int last = p.W - 1 - g.gx;          // no edge leaves the last column / last row
-                if (last == 0) ax.x = 0.f;
-                if (last == 1) ax.y = 0.f;
-                if (last == 2) ax.z = 0.f;
-                if (last == 3) ax.w = 0.f;
-                if (g.gy[r] == p.H - 1) ay = zero4();
-                red_add4(p.g_c + o, dc);
-                red_add4(p.g_wx + o, ax);
-                red_add4(p.g_wy + o, ay);
-            }
+            rev_tile_end(sh, p, make_geom_at<K>(tc.tx, tc.ty, p.H, p.W), (size_t)tc.n);
         }
         if (warp == 0) {
             const int un = ue + (int)gridDim.x;
             const int ok = un < total ? __all_sync(kFull, seen >= un / ntiles) : 0;
-            if (ok) __threadfence();               // acquire side of the hand-over: the counters were read relaxed
             if (lane == 0) sh_ctl[1] = ok;
         }
         // publish: the barrier orders every thread's stores and reductions before the release that moves the counter
         __syncthreads();
-        if (threadIdx.x == 0) red_release_gpu(p.progress + tile, 1);
         next_ready = sh_ctl[1];
+        if (threadIdx.x == 0) red_release_gpu(p.progress + tile, 1);
     }
 }
 
@@ -563,7 +455,7 @@ int launch_tv_rev_flow(const RevFlowParams& p, cudaStream_t st) {
     const int tiles_x = (p.W + kTileW - 1) / kTileW, tiles_y = (p.H + TH - 1) / TH;
     const long long units = (long long)tiles_x * tiles_y * p.N * p.nblocks;
     if (units <= 0 || units >= (1ll << 30)) return fail(CNL_ERR_BAD_SHAPE, "too many work units for a single-launch sweep");
-    return launch_flow(tv_rev_flow_kernel<K>, p, kRevFlowSmemBytes, units, tiles_x, tiles_y, st, "tv_rev_flow_kernel");
+    return launch_flow(tv_rev_flow_kernel<K>, p, kRevSmemBytes, units, tiles_x, tiles_y, st, "tv_rev_flow_kernel");
 }
 
 int flow_tiles(int H, int W, int N) {

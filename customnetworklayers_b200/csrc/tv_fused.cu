@@ -230,133 +230,33 @@ int launch_tv_fwd_fused(const FwdFusedParams& p, int K, cudaStream_t st) {
 // reverse: K reverse iterations per launch
 // ---------------------------------------------------------------------------------------------------------------
 
-constexpr int kRevSmemBytes = (5 * kRows * kThreads + 3 * kWarps * 32) * (int)sizeof(float4);
+// Per-step inputs of a launch that fuses K reverse iterations: straight from the launch parameters.
+struct FusedSteps {
+    const RevFusedParams& p;
+    __device__ __forceinline__ const float* hist(int j) const { return p.hist[j]; }
+    __device__ __forceinline__ const float* ckpt(int j) const { return p.ckpt[j]; }
+    __device__ __forceinline__ float t(int j) const { return p.t[j]; }
+};
 
 template <int K>
 __global__ void __launch_bounds__(kThreads, 1)
 tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
     extern __shared__ float4 smem[];
-    float4* sh_dc = smem;                                  // [kRows][kThreads] per-thread accumulators over channels
-    float4* sh_dwx = sh_dc + kRows * kThreads;
-    float4* sh_dwy = sh_dwx + kRows * kThreads;
-    float4* sh_db = sh_dwy + kRows * kThreads;             // per channel
-    float4* sh_xn = sh_db + kRows * kThreads;              // private landing slots of the prefetched pre-prox iterate
-    float4(*sh_y)[32] = reinterpret_cast<float4(*)[32]>(sh_xn + kRows * kThreads);    // first rows of y
-    float4(*sh_g)[32] = sh_y + kWarps;                                               // first rows of g
-    float4(*sh_p)[32] = sh_g + kWarps;                                               // last-row vertical adjoint flux
+    const RevSmem sh = rev_smem(smem);
     const TileGeom g = make_geom<K>(p.H, p.W);
     const size_t n = blockIdx.z;
     const size_t plane = (size_t)p.H * p.P;
     float4 c[kRows], wx[kRows], wy[kRows];
     load_maps(p, g, n, c, wx, wy);
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-        sh_dc[r * kThreads + threadIdx.x] = zero4();
-        sh_dwx[r * kThreads + threadIdx.x] = zero4();
-        sh_dwy[r * kThreads + threadIdx.x] = zero4();
-    }
+    rev_tile_begin(sh, c);
+    const FusedSteps steps{p};
     for (int ch = 0; ch < p.C; ++ch) {
-        float4 gq[kRows], acc[kRows], b[kRows], xh[kRows], xhm[kRows];
         size_t off[kRows];
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            off[r] = (n * p.C + ch) * plane + (size_t)g.gy[r] * p.P + g.gx;
-            gq[r] = ld4(p.g_in + off[r], g.ok[r]);
-            acc[r] = ld4(p.acc_in + off[r], g.ok[r]);
-            b[r] = ld4(p.b + off[r], g.ok[r]);
-            xh[r] = ld4(p.hist[0] + off[r], g.ok[r]);
-            xhm[r] = ld4(p.hist[1] + off[r], g.ok[r] && p.hist[1] != nullptr);
-            sh_db[r * kThreads + threadIdx.x] = zero4();
-        }
-#pragma unroll
-        for (int j = 0; j < K; ++j) {
-            const float t = p.t[j];
-            // prefetch the pre-prox iterate the next fused step needs
-            if (j + 2 <= K) {
-                const float* src = p.hist[j + 2 <= K ? j + 2 : K];
-#pragma unroll
-                for (int r = 0; r < kRows; ++r) {
-                    const bool okr = g.ok[r] && src != nullptr;
-                    cp_async16(sh_xn + r * kThreads + threadIdx.x, okr ? src + off[r] : p.b, okr);
-                }
-                cp_async_commit();
-            }
-            float4 y[kRows];
-            if (p.ckpt[j]) {
-#pragma unroll
-                for (int r = 0; r < kRows; ++r) y[r] = ld4(p.ckpt[j] + off[r], g.ok[r]);
-            } else {
-#pragma unroll
-                for (int r = 0; r < kRows; ++r) y[r] = rederive_row(xh[r], xhm[r], b[r], c[r], t);
-            }
-            sh_y[g.warp][g.lane] = y[0];
-            sh_g[g.warp][g.lane] = gq[0];
-            __syncthreads();
-            const bool has_below = g.warp + 1 < kWarps;
-            const float4 ybelow = has_below ? sh_y[g.warp + 1][g.lane] : zero4();
-            const float4 gbelow = has_below ? sh_g[g.warp + 1][g.lane] : zero4();
-            float4 p1l, p2l, dwxl, dwyl;
-            adjoint_row(y[kRows - 1], ybelow, gq[kRows - 1], gbelow, wx[kRows - 1], wy[kRows - 1], p1l, p2l, dwxl, dwyl);
-            sh_p[g.warp][g.lane] = p2l;
-            add4(sh_dwx[(kRows - 1) * kThreads + threadIdx.x], dwxl);
-            add4(sh_dwy[(kRows - 1) * kThreads + threadIdx.x], dwyl);
-            __syncthreads();
-            float4 p2c = (g.warp > 0) ? sh_p[g.warp - 1][g.lane] : zero4();
-#pragma unroll
-            for (int r = 0; r < kRows; ++r) {
-                float4 p1, p2;
-                if (r == kRows - 1) { p1 = p1l; p2 = p2l; }
-                else {
-                    float4 ax, ay;
-                    adjoint_row(y[r], y[r + 1], gq[r], gq[r + 1], wx[r], wy[r], p1, p2, ax, ay);
-                    add4(sh_dwx[r * kThreads + threadIdx.x], ax);
-                    add4(sh_dwy[r * kThreads + threadIdx.x], ay);
-                }
-                const float p1_left = __shfl_up_sync(kFull, p1.w, 1);
-                const float4 ybar = divergence_row(gq[r], p1, p2, p1_left, p2c);
-                p2c = p2;
-                float4 xb;
-                float4 dc = sh_dc[r * kThreads + threadIdx.x];
-                float4 db = sh_db[r * kThreads + threadIdx.x];
-                gq[r] = reverse_row(ybar, acc[r], xh[r], b[r], c[r], t, dc, db, xb);
-                sh_dc[r * kThreads + threadIdx.x] = dc;
-                sh_db[r * kThreads + threadIdx.x] = db;
-                if (j == K - 1 && p.x1bar != nullptr && g.store[r]) st4(p.x1bar + off[r], xb);
-            }
-            cp_async_wait_all();
-#pragma unroll
-            for (int r = 0; r < kRows; ++r) {
-                xh[r] = xhm[r];
-                xhm[r] = (j + 2 <= K) ? sh_xn[r * kThreads + threadIdx.x] : zero4();
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            if (g.store[r]) {
-                st4(p.g_out + off[r], gq[r]);
-                st4(p.acc_out + off[r], acc[r]);
-                red_add4(p.g_b + off[r], sh_db[r * kThreads + threadIdx.x]);
-            }
-        }
+        for (int r = 0; r < kRows; ++r) off[r] = (n * p.C + ch) * plane + (size_t)g.gy[r] * p.P + g.gx;
+        rev_channel<K, false>(sh, g, off, p.g_in, p.acc_in, p.b, p.g_out, p.acc_out, p.g_b, p.x1bar, c, wx, wy, steps, [](int) {});
     }
-    // per-pixel gradients shared by all channels
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-        if (!g.store[r]) continue;
-        const size_t o = n * plane + (size_t)g.gy[r] * p.P + g.gx;
-        const float4 dc = sh_dc[r * kThreads + threadIdx.x];
-        float4 ax = sh_dwx[r * kThreads + threadIdx.x];
-        float4 ay = sh_dwy[r * kThreads + threadIdx.x];
-        const int last = p.W - 1 - g.gx;          // no edge leaves the last column / last row
-        if (last == 0) ax.x = 0.f;
-        if (last == 1) ax.y = 0.f;
-        if (last == 2) ax.z = 0.f;
-        if (last == 3) ax.w = 0.f;
-        if (g.gy[r] == p.H - 1) ay = zero4();
-        red_add4(p.g_c + o, dc);
-        red_add4(p.g_wx + o, ax);
-        red_add4(p.g_wy + o, ay);
-    }
+    rev_tile_end(sh, p, g, n);
 }
 
 

@@ -264,3 +264,93 @@ __device__ __forceinline__ float2 reverse_point2(float2 ybar, float2& acc, float
 }
 
 }  // namespace cnl
+
+// ---------------------------------------------------------------------------------------------------------------
+// Leaner forms used by the temporally blocked reverse kernels.  The reciprocal of 1 + c is the same in every fused
+// step and every channel of a tile, so the caller computes it once; constant factors of the accumulated gradients
+// (kLocalGC, kLocalGB, -kLocalGX) are applied once when the sums leave the CTA instead of in every step.
+// ---------------------------------------------------------------------------------------------------------------
+namespace cnl {
+
+// y_{k+1} rebuilt from two stored pre-prox iterates for two pixels, 1/(1+c) supplied (see rederive_y_fast)
+__device__ __forceinline__ float2 rederive_y2i(float2 x05, float2 x05m, float2 b, float2 c, float2 inv, float t) {
+    const float2 opc = add2(c, f2(1.0f));
+    const float2 cb = mul2(c, b);
+    const float2 diff = sub2(b, x05);
+    const float2 diff2 = sub2(b, x05m);
+    const float2 xq = mul2(add2(cb, x05), inv);
+    const float2 xqm = mul2(add2(cb, x05m), inv);
+    float2 xk, xkm;
+    {
+        const bool quad = opc.x >= fabsf(diff.x);
+        const float xl = x05.x + copysignf(c.x, diff.x);
+        const float xlm = (c.x <= fabsf(diff2.x)) ? x05m.x + copysignf(c.x, diff2.x) : b.x;
+        xk.x = quad ? xq.x : xl;
+        xkm.x = quad ? xqm.x : xlm;
+    }
+    {
+        const bool quad = opc.y >= fabsf(diff.y);
+        const float xl = x05.y + copysignf(c.y, diff.y);
+        const float xlm = (c.y <= fabsf(diff2.y)) ? x05m.y + copysignf(c.y, diff2.y) : b.y;
+        xk.y = quad ? xq.y : xl;
+        xkm.y = quad ? xqm.y : xlm;
+    }
+    return fma2(f2(t), sub2(xk, xkm), xk);
+}
+
+// Adjoint fluxes of two triangles; the edge-weight gradients are ACCUMULATED without their factor -kLocalGX:
+//   awx += d1 (nom e1 - den S d1),  awy += d2 (nom e2 - den S d2)        (see tri_adjoint for the full expressions)
+__device__ __forceinline__ void tri_adjoint2_acc(float2 d1, float2 d2, float2 e1, float2 e2, float2 wx, float2 wy,
+                                                 float2& phi1, float2& phi2, float2& awx, float2& awy) {
+    const float2 wd1 = mul2(wx, d1);
+    const float2 wd2 = mul2(wy, d2);
+    const float2 A = fma2(wd1, d1, mul2(wd2, d2));
+    const float2 r = f2(rsqrt_approx(A.x), rsqrt_approx(A.y));
+    const float2 dr = mul2(f2(kDelta), r);
+    const bool bx = dr.x < 1.0f, by = dr.y < 1.0f;
+    const float2 nom = f2(bx ? dr.x : 1.0f, by ? dr.y : 1.0f);
+    const float2 hr = mul2(mul2(f2(-0.5f), nom), mul2(r, r));
+    const float2 nden = f2(bx ? hr.x : 0.0f, by ? hr.y : 0.0f);        // -den
+    const float2 S = fma2(wd1, e1, mul2(wd2, e2));
+    const float2 ndS = mul2(nden, S);                                    // -den S
+    const float2 r1 = mul2(ndS, d1);                                     // -den S d1
+    const float2 r2 = mul2(ndS, d2);
+    const float2 u1 = fma2(nom, e1, r1);                                 // nom e1 - den S d1
+    const float2 u2 = fma2(nom, e2, r2);
+    phi1 = mul2(wx, add2(u1, r1));                                       // wx (nom e1 - 2 den S d1)
+    phi2 = mul2(wy, add2(u2, r2));
+    awx = fma2(d1, u1, awx);
+    awy = fma2(d2, u2, awy);
+}
+
+// Momentum reverse + prox Jacobian for two pixels with 1/(1+c) supplied.  The confidence and data-term gradients are
+// ACCUMULATED without their constant factors:  agc += quad ? xi (b - xq) : sign(diff) xbar   (times kLocalGC later),
+//                                              agb += quad ? xi : 0                          (times c kLocalGB later).
+__device__ __forceinline__ float2 reverse_point2i(float2 ybar, float2& acc, float2 x05, float2 b, float2 c, float2 inv,
+                                                  float t, float2& agc, float2& agb, float2& xbar_out) {
+    float2 xbar = fma2(f2(1.0f + t), ybar, acc);
+    xbar = f2(clampf(xbar.x, -kClipLocal, kClipLocal), clampf(xbar.y, -kClipLocal, kClipLocal));
+    acc = mul2(f2(-t), ybar);
+    xbar_out = xbar;
+    const float2 opc = add2(c, f2(1.0f));
+    const float2 diff = sub2(b, x05);
+    const float2 xq = mul2(fma2(c, b, x05), inv);
+    const float2 xi = mul2(xbar, inv);
+    const float2 gq = mul2(xi, sub2(b, xq));
+    float2 out;
+    {
+        const bool quad = opc.x >= fabsf(diff.x);
+        agc.x += quad ? gq.x : copysignf(1.0f, diff.x) * xbar.x;
+        agb.x += quad ? xi.x : 0.0f;
+        out.x = quad ? xi.x : xbar.x;
+    }
+    {
+        const bool quad = opc.y >= fabsf(diff.y);
+        agc.y += quad ? gq.y : copysignf(1.0f, diff.y) * xbar.y;
+        agb.y += quad ? xi.y : 0.0f;
+        out.y = quad ? xi.y : xbar.y;
+    }
+    return out;
+}
+
+}  // namespace cnl

@@ -22,18 +22,28 @@ IN_KEYS = ("wx", "wy", "c", "b", "init", "grad")
 OUT_KEYS = ("sol", "g_wx", "g_wy", "g_c", "g_b", "g_init")
 
 
-class _InputSet:
-    """One set of device buffers for the six input tensors of a call, plus the event after which it may be refilled."""
+class _BufferSet:
+    """One set of device buffers for a call -- the six inputs, the scaled confidence, the solution and the five
+    gradients -- plus the events after which its inputs may be refilled and its outputs overwritten.  Owning these
+    keeps the caching allocator (and its cross-stream bookkeeping) out of the steady state entirely."""
 
     def __init__(self):
         self.buf: Dict[str, torch.Tensor] = {}
-        self.free: Optional[torch.cuda.Event] = None
+        self.inputs_free: Optional[torch.cuda.Event] = None      # kernels that read the inputs are done
+        self.outputs_free: Optional[torch.cuda.Event] = None     # result copies to the host are done
 
     def fit(self, host_in: Dict[str, torch.Tensor], device) -> None:
-        for k in IN_KEYS:
-            t = host_in[k]
-            if k not in self.buf or self.buf[k].shape != t.shape:
-                self.buf[k] = torch.empty(t.shape, dtype=torch.float32, device=device)
+        shapes = {k: host_in[k].shape for k in IN_KEYS}
+        shapes.update({"c_scaled": shapes["c"], "sol": shapes["b"], "g_wx": shapes["wx"], "g_wy": shapes["wy"],
+                       "g_c": shapes["c"], "g_b": shapes["b"], "g_init": shapes["b"]})
+        for k, shp in shapes.items():
+            if k not in self.buf or self.buf[k].shape != shp:
+                self.buf[k] = torch.empty(shp, dtype=torch.float32, device=device)
+        if "lam" not in self.buf:
+            self.buf["lam"] = torch.empty(1, dtype=torch.float32, device=device)
+            self.buf["lam_part"] = torch.empty(1, dtype=torch.float32, device=device)
+            from . import _lib
+            self.buf["scratch"] = torch.empty(_lib.load().cnl_dot_scratch_floats(), dtype=torch.float32, device=device)
 
 
 class HostPipeline:
@@ -43,7 +53,7 @@ class HostPipeline:
         self.device = torch.device(device)
         self.s_in = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
-        self.sets: List[_InputSet] = [_InputSet() for _ in range(max(1, depth))]
+        self.sets: List[_BufferSet] = [_BufferSet() for _ in range(max(1, depth))]
         self.turn = 0
         self.last_out: Optional[torch.cuda.Event] = None
         self.timeline = None            # set to a list to collect per-chunk CUDA events (see chunk_breakdown)
@@ -83,7 +93,8 @@ def tv_fwd_bwd_from_host(pipe: HostPipeline, host_in: Dict[str, torch.Tensor], h
 
     host_in : wx, wy, c [N,1,H,W]; b, init, grad [N,C,H,W]  (grad = upstream gradient of the solution)
     host_out: sol, g_b, g_init [N,C,H,W]; g_wx, g_wy, g_c [N,1,H,W]
-    Returns the lambda gradient as a 1-element CUDA tensor.  Nothing here blocks the host; the pinned outputs are
+    Returns the lambda gradient as a 1-element CUDA tensor (a buffer of the pipeline: valid until the call after next).
+    Nothing here blocks the host; the pinned outputs are
     valid after pipe.join() followed by a synchronise of the current stream, or after torch.cuda.synchronize().
     host_in must not be rewritten before its copies have run (an event on pipe.s_in or a synchronise tells)."""
     dev = pipe.device
@@ -99,8 +110,8 @@ def tv_fwd_bwd_from_host(pipe: HostPipeline, host_in: Dict[str, torch.Tensor], h
         t0 = torch.cuda.Event(enable_timing=True)
         t0.record(comp)
         pipe.s_in.wait_event(t0)          # measured from a common origin; costs the overlap with the previous call
-    if slot.free is not None:
-        pipe.s_in.wait_event(slot.free)   # the kernels that read this set two calls ago are done
+    if slot.inputs_free is not None:
+        pipe.s_in.wait_event(slot.inputs_free)    # the kernels that read this set two calls ago are done
     ev_in, ev_grad = [], []
     with torch.cuda.stream(pipe.s_in):
         for lo, hi in ranges:
@@ -114,27 +125,33 @@ def tv_fwd_bwd_from_host(pipe: HostPipeline, host_in: Dict[str, torch.Tensor], h
             e = torch.cuda.Event()
             e.record(pipe.s_in)
             ev_grad.append(e)
-    g_lam = torch.zeros(1, device=dev)
+    if slot.outputs_free is not None:
+        comp.wait_event(slot.outputs_free)        # the results this set held two calls ago have reached the host
+    g_lam = slot.buf["lam"]
+    g_lam.zero_()
+    B = slot.buf
     for i, (lo, hi) in enumerate(ranges):
-        d = {k: slot.buf[k][lo:hi] for k in IN_KEYS}
+        d = {k: B[k][lo:hi] for k in IN_KEYS}
         comp.wait_event(ev_in[i])
-        c = d["c"] * lam if lam is not None else d["c"]
-        sol = ext.forward(d["wx"], d["wy"], c, d["b"], d["init"], its, pid)[0]
+        if lam is not None:
+            c = torch.mul(d["c"], lam, out=B["c_scaled"][lo:hi])
+        else:
+            c = d["c"]
+        sol = ext.forward(d["wx"], d["wy"], c, d["b"], d["init"], its, pid, out=B["sol"][lo:hi])[0]
         ev_f = torch.cuda.Event(enable_timing=record)
         ev_f.record(comp)
         pipe.s_out.wait_event(ev_f)
-        sol.record_stream(pipe.s_out)
         with torch.cuda.stream(pipe.s_out):          # the solution goes back while the backward pass runs
             host_out["sol"][lo:hi].copy_(sol, non_blocking=True)
         comp.wait_event(ev_grad[i])
-        grads = ext.backward(d["grad"], d["wx"], d["wy"], c, d["b"], its, pid)
-        g_lam += ext.lambda_grad(grads[2], d["c"])
+        grads = ext.backward(d["grad"], d["wx"], d["wy"], c, d["b"], its, pid,
+                             out=[B[k][lo:hi] for k in OUT_KEYS[1:]])
+        g_lam += ext.lambda_grad(grads[2], d["c"], out=B["lam_part"], scratch=B["scratch"])
         ev_b = torch.cuda.Event(enable_timing=record)
         ev_b.record(comp)
         pipe.s_out.wait_event(ev_b)
         with torch.cuda.stream(pipe.s_out):
             for key, t in zip(OUT_KEYS[1:], grads):
-                t.record_stream(pipe.s_out)
                 host_out[key][lo:hi].copy_(t, non_blocking=True)
             ev_o = torch.cuda.Event(enable_timing=record)
             ev_o.record(pipe.s_out)
@@ -142,18 +159,18 @@ def tv_fwd_bwd_from_host(pipe: HostPipeline, host_in: Dict[str, torch.Tensor], h
         if record:
             pipe.timeline.append((t0, {"inputs_landed": ev_in[i], "forward_done": ev_f, "backward_done": ev_b,
                                        "gradients_in_host_memory": ev_o}))
-    slot.free = torch.cuda.Event()
-    slot.free.record(comp)
+    slot.inputs_free = torch.cuda.Event()
+    slot.inputs_free.record(comp)
     allreduce_scalar_grads(g_lam)
-    if host_lam_grad is not None:
-        # on the copy stream: a device->host copy issued on the compute stream would queue behind the gradient copies
-        # in the copy engine and hold the next call's kernels back for as long as those take
-        ev_l = torch.cuda.Event()
-        ev_l.record(comp)
-        pipe.s_out.wait_event(ev_l)
-        g_lam.record_stream(pipe.s_out)
-        with torch.cuda.stream(pipe.s_out):
+    # On the copy stream: a device->host copy issued on the compute stream would queue behind the gradient copies in the
+    # copy engine and hold the next call's kernels back for as long as those take.
+    ev_l = torch.cuda.Event()
+    ev_l.record(comp)
+    pipe.s_out.wait_event(ev_l)
+    with torch.cuda.stream(pipe.s_out):
+        if host_lam_grad is not None:
             host_lam_grad.copy_(g_lam, non_blocking=True)
-            pipe.last_out = torch.cuda.Event()
-            pipe.last_out.record(pipe.s_out)
+        slot.outputs_free = torch.cuda.Event()
+        slot.outputs_free.record(pipe.s_out)
+    pipe.last_out = slot.outputs_free
     return g_lam

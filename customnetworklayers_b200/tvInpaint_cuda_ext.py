@@ -28,8 +28,17 @@ def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def forward(d_x, d_y, d_c, d_b, d_i, its: int, id: int):
-    """tvInpaint_forward (TVInpaintFista_cuda.cpp:47-88): returns [solution] with the shape of d_b."""
+def _check_out(t, like, name):
+    _check_input(t, name)
+    if t.shape != like.shape or t.device != like.device:
+        raise RuntimeError(f"{name} must have the shape and device of the tensor it mirrors")
+
+
+def forward(d_x, d_y, d_c, d_b, d_i, its: int, id: int, out=None):
+    """tvInpaint_forward (TVInpaintFista_cuda.cpp:47-88): returns [solution] with the shape of d_b.
+
+    `out` (optional, no reference counterpart): a tensor to receive the solution instead of a fresh allocation, for
+    callers that keep their own buffers (the host-buffer pipeline does)."""
     for t, name in ((d_x, "d_x"), (d_y, "d_y"), (d_c, "d_c"), (d_b, "d_b"), (d_i, "d_i")):
         _check_input(t, name)
     n, ch, h, w = d_b.shape
@@ -39,7 +48,11 @@ def forward(d_x, d_y, d_c, d_b, d_i, its: int, id: int):
         if tuple(t.shape) != (n, 1, h, w):
             raise RuntimeError(f"{name} must have shape [N,1,H,W] matching d_b")
     lib = _lib.load()
-    solution = torch.empty_like(d_b)
+    if out is None:
+        solution = torch.empty_like(d_b)
+    else:
+        _check_out(out, d_b, "out")
+        solution = out
     with torch.cuda.device(d_b.device):
         rc = lib.cnl_tv_forward(d_x.data_ptr(), d_y.data_ptr(), d_c.data_ptr(), d_b.data_ptr(), d_i.data_ptr(),
                                 solution.data_ptr(), n, ch, h, w, int(its), int(id), _stream_ptr(d_b.device))
@@ -47,12 +60,13 @@ def forward(d_x, d_y, d_c, d_b, d_i, its: int, id: int):
     return [solution]
 
 
-def backward(d_iGf, d_x, d_y, d_c, d_b, its: int, id: int, generation=None):
+def backward(d_iGf, d_x, d_y, d_c, d_b, its: int, id: int, generation=None, out=None):
     """tvInpaint_backward (TVInpaintFista_cuda.cpp:99-143): returns [gX, gY, gC, gB, gI].
 
     `generation` (optional, no reference counterpart): the value forward_count(id) had right after the forward pass
     this call belongs to; if another forward pass has replaced the slot's history since, the call raises instead of
-    returning gradients of the wrong problem."""
+    returning gradients of the wrong problem.
+    `out` (optional, no reference counterpart): five tensors [gX, gY, gC, gB, gI] to fill instead of fresh allocations."""
     for t, name in ((d_x, "d_x"), (d_y, "d_y"), (d_c, "d_c"), (d_b, "d_b"), (d_iGf, "d_iGf")):
         _check_input(t, name)
     n, ch, h, w = d_b.shape
@@ -68,11 +82,17 @@ def backward(d_iGf, d_x, d_y, d_c, d_b, its: int, id: int, generation=None):
         if now != int(generation):
             raise RuntimeError(f"tvInpaint backward: slot {id} holds forward pass {now}, not {generation}: another forward "
                                f"call on this id replaced the history (give each live layer its own id)")
-    g_x = torch.empty_like(d_x)
-    g_y = torch.empty_like(d_y)
-    g_c = torch.empty_like(d_c)
-    g_b = torch.empty_like(d_b)
-    g_i = torch.empty_like(d_b)
+    if out is None:
+        g_x = torch.empty_like(d_x)
+        g_y = torch.empty_like(d_y)
+        g_c = torch.empty_like(d_c)
+        g_b = torch.empty_like(d_b)
+        g_i = torch.empty_like(d_b)
+    else:
+        g_x, g_y, g_c, g_b, g_i = out
+        for t, like, name in ((g_x, d_x, "out[0]"), (g_y, d_y, "out[1]"), (g_c, d_c, "out[2]"), (g_b, d_b, "out[3]"),
+                              (g_i, d_b, "out[4]")):
+            _check_out(t, like, name)
     with torch.cuda.device(d_b.device):
         rc = lib.cnl_tv_backward(d_x.data_ptr(), d_y.data_ptr(), d_c.data_ptr(), d_b.data_ptr(), d_iGf.data_ptr(),
                                  g_x.data_ptr(), g_y.data_ptr(), g_c.data_ptr(), g_b.data_ptr(), g_i.data_ptr(),
@@ -112,15 +132,20 @@ def set_option(id: int, option: int, value: int) -> None:
     _lib.check(_lib.load().cnl_tv_set_option(int(id), int(option), int(value)), "tvInpaint set_option")
 
 
-def lambda_grad(g_c: torch.Tensor, c_raw: torch.Tensor) -> torch.Tensor:
-    """sum(g_c * c_raw) as a 1-element CUDA tensor: the gradient of a learned scalar lambda in c = lambda * c_raw."""
+def lambda_grad(g_c: torch.Tensor, c_raw: torch.Tensor, out=None, scratch=None) -> torch.Tensor:
+    """sum(g_c * c_raw) as a 1-element CUDA tensor: the gradient of a learned scalar lambda in c = lambda * c_raw.
+    `out` (1 float) and `scratch` (cnl_dot_scratch_floats() floats) may be supplied by callers that keep their own."""
     _check_input(g_c, "g_c")
     _check_input(c_raw, "c_raw")
     if g_c.numel() != c_raw.numel():
         raise RuntimeError("g_c and c_raw must have the same number of elements")
     lib = _lib.load()
-    out = torch.empty(1, dtype=torch.float32, device=g_c.device)
-    scratch = torch.empty(lib.cnl_dot_scratch_floats(), dtype=torch.float32, device=g_c.device)
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=g_c.device)
+    if scratch is None:
+        scratch = torch.empty(lib.cnl_dot_scratch_floats(), dtype=torch.float32, device=g_c.device)
+    elif scratch.numel() < lib.cnl_dot_scratch_floats() or scratch.dtype != torch.float32 or not scratch.is_cuda:
+        raise RuntimeError("scratch must be a CUDA float tensor of at least cnl_dot_scratch_floats() elements")
     with torch.cuda.device(g_c.device):
         rc = lib.cnl_tv_lambda_grad(g_c.data_ptr(), c_raw.data_ptr(), g_c.numel(), out.data_ptr(),
                                     scratch.data_ptr(), _stream_ptr(g_c.device))
