@@ -12,6 +12,7 @@ Rank 0 prints one JSON line.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -36,6 +37,7 @@ WORKLOADS = {
     "cfg2small": (2, 2, 436, 1024, 10),  # TGV profiling case
     "cfg2prof": (8, 2, 436, 1024, 6),    # TGV profiling case with the launch geometry of cfg2 (persistent kernels)
     "cfg4": (32, 2, 384, 1280, 0),        # learnable 7x7 weighted-median filter (no iterations)
+    "cfg4small": (2, 2, 384, 1280, 0),    # weighted-median profiling case
     "median": (4, 49, 384, 1280, 0),      # the reference's selection layer on a materialised [N,H,W,K] weight volume
     "quadfit": (4, 32, 384, 1280, 0),     # the reference's quadratic fit on two feature maps and a flow
     "cfg3": (16, 2, 512, 960, 50),       # coarse-to-fine stack of three TV layers (ids 0,1,2) with quadratic-fit refinement
@@ -334,14 +336,12 @@ def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, war
     ms_e2e, _, _ = timed(step_e2e, steps, finish=pipe.join)
     e2e_steps = sorted(timed.last_per_step)
     # where an end-to-end step spends its time: one call alone, CUDA events per chunk from the call's start
-    breakdown = None
-    if rank == 0:
-        torch.cuda.synchronize()
-        pipe.timeline = []
-        step_e2e()
-        torch.cuda.synchronize()
-        breakdown = [{k: round(v, 3) for k, v in row.items()} for row in pipe.chunk_breakdown()]
-        pipe.timeline = None
+    barrier()
+    pipe.timeline = []
+    step_e2e()                        # on every rank: the call contains the all-reduce
+    torch.cuda.synchronize()
+    breakdown = [{k: round(v, 3) for k, v in row.items()} for row in pipe.chunk_breakdown()]
+    pipe.timeline = None
     barrier()
     res = {"nb": nb, "ms": ms, "launches": launches, "clocks": clocks, "tm": tm, "ms_e2e": ms_e2e, "chunk": chunk,
            "h2d": sum(host[k].numel() * 4 for k in keys), "d2h": sum(t.numel() * 4 for t in host_res.values()) + 4,
@@ -363,7 +363,7 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     _lib.load()
 
     nb_full, ch, h, w, its = WORKLOADS[args.workload]
@@ -483,7 +483,7 @@ def run_tgv(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     nb, ch, h, w, its = WORKLOADS[args.workload]
     its_eff = 2 * (its // 2)
     I = make_tgv_inputs(nb, ch, h, w, seed=1236 + 1000 * rank)
@@ -558,7 +558,7 @@ def run_hierarchy(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     nb, ch, h, w, its = WORKLOADS[args.workload]
     its_eff = 2 * (its // 2)
     levels, grad = make_hierarchy_inputs(nb, h, w, seed=1237 + 1000 * rank)
@@ -630,7 +630,7 @@ def run_wmedian(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     nb, ch, h, w, _ = WORKLOADS[args.workload]
     flow, wts, grad = make_median_filter_inputs(nb, ch, h, w, seed=1238 + 1000 * rank)
     flow, grad = flow.to(dev), grad.to(dev)
@@ -783,7 +783,7 @@ def main():
     if args.workload in ("median", "quadfit"):
         if rank == 0:
             result = run_layer_micro(args, rank, local_rank, world)
-    elif args.workload == "cfg4":
+    elif args.workload.startswith("cfg4"):
         result = run_wmedian(args, rank, local_rank, world)
     elif args.workload == "cfg3":
         result = run_hierarchy(args, rank, local_rank, world)

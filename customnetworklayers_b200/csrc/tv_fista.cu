@@ -92,10 +92,12 @@ tv_fwd_iter_kernel(const float* __restrict__ y_in, float* __restrict__ y_out, fl
 }
 
 // Seeds the reverse sweep at the last iteration (TVInpaintFista.cu:222-287): prox Jacobian on the upstream gradient.
+// Also clears what the sweep accumulates into: the pending momentum term and the two edge-weight gradients.
 __global__ void __launch_bounds__(256)
 tv_rev_seed_kernel(const float* __restrict__ grad_out, const float* __restrict__ hist_g, const float* __restrict__ b,
                    const float* __restrict__ c, float* __restrict__ g_out, float* __restrict__ g_c,
-                   float* __restrict__ g_b, int C, size_t plane) {
+                   float* __restrict__ g_b, float* __restrict__ acc, float* __restrict__ g_wx, float* __restrict__ g_wy,
+                   int C, size_t plane) {
     const size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (pix >= plane) return;
     const size_t n = blockIdx.y;
@@ -108,8 +110,11 @@ tv_rev_seed_kernel(const float* __restrict__ grad_out, const float* __restrict__
         float dgb = 0.0f;
         g_out[i] = prox_reverse(up, hist_g[i], __ldg(b + i), conf, dgc, dgb);
         g_b[i] = dgb;
+        acc[i] = 0.0f;
     }
     g_c[n * plane + pix] = dgc;
+    g_wx[n * plane + pix] = 0.0f;
+    g_wy[n * plane + pix] = 0.0f;
 }
 
 // y_{g+1} from hist[g], hist[g-1] (TVInpaintFista.cu:1130-1189).
@@ -407,8 +412,8 @@ static ArenaLayout make_layout(size_t n, size_t ch, size_t h, size_t w, size_t h
     L.acc2 = o; o += L.vol;
     L.xbuf = o; o += L.vol;
     L.ybuf = o; o += L.vol;
-    // progress counters of the single-launch sweeps: one per tile, then the abort word
-    L.sync_words = align_up((size_t)flow_tiles((int)h, (int)std::min<size_t>(w, 0x3fffffff), (int)n) + 1, 64);
+    // progress counters of the single-launch sweeps: one per tile, then the abort word and the ticket counter
+    L.sync_words = align_up((size_t)flow_tiles((int)h, (int)std::min<size_t>(w, 0x3fffffff), (int)n) + 2, 64);
     L.sync = o; o += L.sync_words;
     L.ckpt = o; o += L.vol * nckpt;
     L.xck = o; o += L.vol * xck_planes;
@@ -717,8 +722,6 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     const ArenaLayout L = slot_layout(n, ch, h, P, its_eff, s.sched, s.recompute, staged);
     const size_t plane = (size_t)h * P;
     const size_t uplane = (size_t)h * w;          // plane of the caller's tensors
-    const size_t vol_bytes = (size_t)n * ch * plane * sizeof(float);
-    const size_t map_bytes = (size_t)n * plane * sizeof(float);
     const void* aligned[] = {wx, wy, c, b, grad_out, g_wx, g_wy, g_c, g_b, g_init};
     const int fuse = s.opt_fuse == 0 ? kFuseMax : s.opt_fuse;
     const bool fused = fuse > 1 && (staged || fused_supported(w, aligned, 10));
@@ -745,9 +748,6 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     float* acc = s.arena + L.acc;
     float* ybuf = s.arena + L.ybuf;
     const float* hist = s.arena + L.hist;
-    CNL_TRY(check_cuda(cudaMemsetAsync(acc, 0, vol_bytes, st), "zero acc"));
-    CNL_TRY(check_cuda(cudaMemsetAsync(g_wx, 0, map_bytes, st), "zero g_wx"));
-    CNL_TRY(check_cuda(cudaMemsetAsync(g_wy, 0, map_bytes, st), "zero g_wy"));
 
     const dim3 block(kBX, kBY);
     const dim3 grid((w + kBX - 1) / kBX, (h + kBY - 1) / kBY, n);
@@ -801,7 +801,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     // seed at the last iteration (its_eff - 1 is odd, so the seed lands in the "odd" buffer like the reference's)
     {
         const int g = its_eff - 1;
-        tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hist_of(g), b, c, gb, g_c, g_b, ch, plane);
+        tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hist_of(g), b, c, gb, g_c, g_b, acc, g_wx, g_wy, ch, plane);
         CNL_TRY(after_launch("tv_rev_seed_kernel"));
     }
     if (fused) {

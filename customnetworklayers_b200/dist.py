@@ -48,3 +48,29 @@ def bind_to_gpu_numa_node(device_index: int) -> Optional[List[int]]:
         return cpus
     except Exception:
         return None
+
+
+class RankLeft(RuntimeError):
+    """Raised by StepGuard.check() when another rank has announced that it stopped taking part."""
+
+
+class StepGuard:
+    """Host-side failure detection between steps for the batch-sharded layer.
+
+    The only collective of the path is a tiny all-reduce per step, so a rank that stops (an exception in its data
+    loader, a scale-down) would leave the others blocked in that all-reduce until the process-group timeout.  A rank
+    that leaves cleanly calls leave() between steps, with none of its kernels or collectives in flight; every rank
+    calls check() before it launches a step and gets RankLeft instead of a hang.  A rank that dies without saying so is
+    caught by the process-group timeout of the next all-reduce (pass a short `timeout` to init_process_group).
+    Uses a key-value store (torch.distributed.TCPStore or the like); no GPU is involved."""
+
+    def __init__(self, store, rank: int, world: int):
+        self.store, self.rank, self.world = store, rank, world
+
+    def leave(self) -> None:
+        self.store.set(f"cnl/left/{self.rank}", "1")
+
+    def check(self) -> None:
+        for r in range(self.world):
+            if r != self.rank and self.store.check([f"cnl/left/{r}"]):
+                raise RankLeft(f"rank {r} has left: stop before the next all-reduce")
