@@ -125,19 +125,21 @@ def cpu_fwd_bwd(I, its):
     return sol
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the 4-iteration kernels at batch 8,
-# 2x384x1280 (1408 tiles), from an `ncu --set full` capture of one launch each, NOT measured in this run
-# (profiles/tv_fused_kernels_prof_and_cfg1.md).  Traffic grows in proportion to the images of a launch, so other batch
-# sizes of the same image scale it; other image sizes have no capture and report null.
-NCU_TRAFFIC_BATCH8 = {(2, 384, 1280): {"reverse": 523.0e6, "forward": 307.7e6}}
-TRAFFIC_SOURCE = "ncu capture of one launch (profiles/tv_fused_kernels_prof_and_cfg1.md), scaled by batch/8 and iterations/4; not measured in this run"
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per image and iteration of the single-launch sweeps at
+# 2x384x1280, from an `ncu --set full` capture of one launch each on the `prof` workload (batch 8, 20 iterations:
+# reverse 2143 MB for 16 iterations, forward 1695 MB for 20), NOT measured in this run
+# (profiles/tv_flow_kernels_prof_and_cfg1.md).  Traffic grows in proportion to images and iterations of a launch, so
+# other batch sizes and iteration counts of the same image scale it; other image sizes have no capture and report null.
+NCU_TRAFFIC_PER_IMAGE_ITER = {(2, 384, 1280): {"reverse": 2143.1e6 / 16 / 8, "forward": 1694.5e6 / 20 / 8}}
+TRAFFIC_SOURCE = ("ncu capture of one single-launch sweep on the prof workload (profiles/tv_flow_kernels_prof_and_cfg1.md), "
+                  "scaled by images and iterations of the launch; not measured in this run")
 
 
 def ncu_traffic_per_launch(nb, ch, h, w, rev_ipl, fwd_ipl):
-    t = NCU_TRAFFIC_BATCH8.get((ch, h, w))
+    t = NCU_TRAFFIC_PER_IMAGE_ITER.get((ch, h, w))
     if not t:
         return None
-    return {"reverse": t["reverse"] * nb / 8.0 * rev_ipl / 4.0, "forward": t["forward"] * nb / 8.0 * fwd_ipl / 4.0}
+    return {"reverse": t["reverse"] * nb * rev_ipl, "forward": t["forward"] * nb * fwd_ipl}
 
 
 def cpu_baseline_sample(ch, h, w, its, budget_s=20.0):
@@ -392,11 +394,11 @@ def run_ours(args, rank, local_rank, world):
         # dominant kernel: the reverse iteration.  Average launch duration from CUDA events bracketing the reverse
         # loop of every timed step, on the stream the kernels run on.
         rev_launch_ms = tm["rev_ms"] / max(1, tm["rev_launches"])
-        iters_per_launch = its_eff * tm["rev_calls"] / max(1, tm["rev_launches"])
+        iters_per_launch = tm["rev_iters"] / max(1, tm["rev_launches"])
         bytes_per_launch = rev_b * nb * h * w * iters_per_launch
         achieved = bytes_per_launch / (rev_launch_ms * 1e-3) / 1e9 if rev_launch_ms > 0 else 0.0
         fwd_launch_ms = tm["fwd_ms"] / max(1, tm["fwd_launches"])
-        fwd_ipl = its_eff * tm["fwd_calls"] / max(1, tm["fwd_launches"])
+        fwd_ipl = tm["fwd_iters"] / max(1, tm["fwd_launches"])
         fwd_achieved = fwd_b * nb * h * w * fwd_ipl / (fwd_launch_ms * 1e-3) / 1e9 if fwd_launch_ms > 0 else 0.0
         whole = (fwd_b + rev_b) * pixel_iters / world * args.steps / (ms * 1e-3) / 1e9
         traffic = ncu_traffic_per_launch(nb, ch, h, w, iters_per_launch, fwd_ipl) if args.fuse in (0, 4) else None
@@ -410,7 +412,7 @@ def run_ours(args, rank, local_rank, world):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
-            "roofline": {"bound": "hbm", "kernel": "reverse iteration", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "reverse sweep (tv_rev_flow_kernel: every full 4-iteration time block in one launch)" if iters_per_launch > 4 else "reverse iteration kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic["reverse"] if traffic else None,
                          "frac_traffic": (traffic["reverse"] / (rev_launch_ms * 1e-3) / 1e9 / peak) if traffic and rev_launch_ms > 0 else None,

@@ -224,41 +224,40 @@ tv_grad_stats_kernel(FinalizeArgs a, double* __restrict__ partial) {
     }
 }
 
-// One warp: combines the partials in a fixed order (lane-strided sums + shuffle tree, so the result does not depend
-// on timing), updates the running means and writes one factor per output.
+// One warp per output: combines the partials in a fixed order (lane-strided sums + shuffle tree, so the result does not
+// depend on timing), updates the running mean and writes the factor of that output.
 // state[0..4] = running means (av_GC, av_GX, av_GY, av_GB, av_GI), factor[0..4] = multiplier for this call.
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(32 * kNumOutputs)
 tv_conditioner_kernel(const double* __restrict__ partial, FinalizeArgs a, double* __restrict__ state,
                       float* __restrict__ factor, int run) {
     const double run_step = fmin(0.975, (double)run / (double)(run + 1));       // :1761
-    for (int o = 0; o < kNumOutputs; ++o) {
-        double s = 0.0, bad = 0.0;
-        for (int i = threadIdx.x; i < kStatBlocks; i += 32) {
-            s += partial[(o * kStatBlocks + i) * 2];
-            bad += partial[(o * kStatBlocks + i) * 2 + 1];
-        }
-        for (int off = 16; off > 0; off >>= 1) {
-            s += __shfl_down_sync(0xffffffffu, s, off);
-            bad += __shfl_down_sync(0xffffffffu, bad, off);
-        }
-        if (threadIdx.x != 0) continue;
-        double av = state[o];
-        // mean |g|; a non-finite entry makes the reference restart its mean from 1000 x the running mean (:171)
-        const double av_gc = (bad > 0.0) ? av * 1000.0 : (a.count[o] ? s / (double)a.count[o] : 0.0);
-        float f = 1.0f;
-        if (run >= 10 && av * 50.0 < av_gc) {                 // kill (:132-140)
-            f = 0.0f;
-            av = av * run_step + (1.0 - run_step) * 10.0 * av;
-        } else if (run >= 10 && av * 10.0 < av_gc) {          // rescale (:142-150)
-            const double mult = 10.0 * av / av_gc;
-            f = (float)mult;
-            av = av * run_step + (1.0 - run_step) * av_gc * mult;
-        } else {
-            av = av * run_step + (1.0 - run_step) * av_gc;
-        }
-        state[o] = av;
-        factor[o] = f;
+    const int o = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    double s = 0.0, bad = 0.0;
+    for (int i = lane; i < kStatBlocks; i += 32) {
+        s += partial[(o * kStatBlocks + i) * 2];
+        bad += partial[(o * kStatBlocks + i) * 2 + 1];
     }
+    for (int off = 16; off > 0; off >>= 1) {
+        s += __shfl_down_sync(0xffffffffu, s, off);
+        bad += __shfl_down_sync(0xffffffffu, bad, off);
+    }
+    if (lane != 0) return;
+    double av = state[o];
+    // mean |g|; a non-finite entry makes the reference restart its mean from 1000 x the running mean (:171)
+    const double av_gc = (bad > 0.0) ? av * 1000.0 : (a.count[o] ? s / (double)a.count[o] : 0.0);
+    float f = 1.0f;
+    if (run >= 10 && av * 50.0 < av_gc) {                 // kill (:132-140)
+        f = 0.0f;
+        av = av * run_step + (1.0 - run_step) * 10.0 * av;
+    } else if (run >= 10 && av * 10.0 < av_gc) {          // rescale (:142-150)
+        const double mult = 10.0 * av / av_gc;
+        f = (float)mult;
+        av = av * run_step + (1.0 - run_step) * av_gc * mult;
+    } else {
+        av = av * run_step + (1.0 - run_step) * av_gc;
+    }
+    state[o] = av;
+    factor[o] = f;
 }
 
 // g = (finite and |g| <= 1e7 ? g : 0) * factor * scale      (:160-171, :1795-1818)
@@ -345,6 +344,7 @@ struct Slot {
     static constexpr int kRing = 64;
     cudaEvent_t ev_fwd[kRing][2] = {}, ev_rev[kRing][2] = {};
     int launches_fwd[kRing] = {}, launches_rev[kRing] = {};
+    int iters_fwd[kRing] = {}, iters_rev[kRing] = {};       // iterations the timed launches cover
     int n_fwd = 0, n_rev = 0;
     bool events_ready = false;
     std::vector<int> sched;
@@ -579,7 +579,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
         // CTA reads a halo another CTA is writing, and the last launch writes x into the caller's buffer.  In
         // recompute mode launches do not straddle checkpoints, the primal iterate is saved beside every checkpoint
         // and only the last segment's history is written (the backward pass starts there).
-        const bool timing = s.opt_timing && s.n_fwd < Slot::kRing;
+        bool timing = s.opt_timing && s.n_fwd < Slot::kRing;
         const unsigned long long launches0 = g_launches.load();
         if (timing) {
             CNL_TRY(ensure_events(s));
@@ -623,7 +623,15 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
             CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0, L.sync_words * sizeof(int), st), "zero progress counters"));
             if (s.opt_flow == 2)      // self-test of the bounded waits: counters that no unit can ever bring up to what its neighbours need
                 CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0x80, (size_t)ntiles * sizeof(int), st), "poison progress counters"));
+            if (timing) CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][0], st), "cudaEventRecord"));
             CNL_TRY(launch_tv_fwd_flow(fp, st));
+            if (timing) {          // the record covers the single-launch sweep alone
+                CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][1], st), "cudaEventRecord"));
+                s.launches_fwd[s.n_fwd] = 1;
+                s.iters_fwd[s.n_fwd] = nfull * kFuseMax;
+                s.n_fwd += 1;
+                timing = false;
+            }
             first_launch = nfull;
             y_in = fp.ybuf[(nfull - 1) & 1];
             x_in = fp.xbuf[(nfull - 1) & 1];
@@ -658,6 +666,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
         if (timing) {
             CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][1], st), "cudaEventRecord"));
             s.launches_fwd[s.n_fwd] = (int)(g_launches.load() - launches0);
+            s.iters_fwd[s.n_fwd] = its_eff;
             s.n_fwd += 1;
         }
         if (staged) CNL_TRY(unpad_rows(user_out, out, (size_t)n * ch * h, w, P, st));
@@ -693,6 +702,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
     if (timing) {
         CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][1], st), "cudaEventRecord"));
         s.launches_fwd[s.n_fwd] = (int)(g_launches.load() - launches0);
+        s.iters_fwd[s.n_fwd] = its_eff;
         s.n_fwd += 1;
     }
     s.n = n; s.ch = ch; s.h = h; s.w = w; s.its = its;
@@ -752,12 +762,9 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     const dim3 block(kBX, kBY);
     const dim3 grid((w + kBX - 1) / kBX, (h + kBY - 1) / kBY, n);
     const dim3 pgrid((unsigned)((plane + 255) / 256), n);
-    const bool timing = s.opt_timing && s.n_rev < Slot::kRing;
-    const unsigned long long launches0 = g_launches.load();
-    if (timing) {
-        CNL_TRY(ensure_events(s));
-        CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][0], st), "cudaEventRecord"));
-    }
+    bool timing = s.opt_timing && s.n_rev < Slot::kRing;
+    unsigned long long launches0 = g_launches.load();
+    if (timing) CNL_TRY(ensure_events(s));
     auto ckpt_of = [&](int g) -> const float* {
         for (size_t i = 0; i < s.sched.size(); ++i)
             if (s.sched[i] == g) return s.arena + L.ckpt + i * L.vol;      // segment start: the checkpointed y_g (:1724-1727)
@@ -804,6 +811,10 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
         tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hist_of(g), b, c, gb, g_c, g_b, acc, g_wx, g_wy, ch, plane);
         CNL_TRY(after_launch("tv_rev_seed_kernel"));
     }
+    if (timing) {          // after the seed: the record covers the iteration kernels
+        launches0 = g_launches.load();
+        CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][0], st), "cudaEventRecord"));
+    }
     if (fused) {
         float* acc2 = s.arena + L.acc2;
         const float* g_cur = gb;
@@ -828,7 +839,15 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
             rp.N = n; rp.C = ch; rp.H = h; rp.W = w; rp.P = P;
             fill_flow_tables(s, its_eff, rp.tab);
             CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0, L.sync_words * sizeof(int), st), "zero progress counters"));
+            if (timing) CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][0], st), "cudaEventRecord"));
             CNL_TRY(launch_tv_rev_flow(rp, st));
+            if (timing) {          // the record covers the single-launch sweep alone
+                CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][1], st), "cudaEventRecord"));
+                s.launches_rev[s.n_rev] = 1;
+                s.iters_rev[s.n_rev] = nfull * kFuseMax;
+                s.n_rev += 1;
+                timing = false;
+            }
             g_cur = rp.gbuf[(nfull - 1) & 1];
             acc_cur = rp.abuf[(nfull - 1) & 1];
             flip = nfull & 1;
@@ -886,6 +905,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     if (timing) {
         CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][1], st), "cudaEventRecord"));
         s.launches_rev[s.n_rev] = (int)(g_launches.load() - launches0);
+        s.iters_rev[s.n_rev] = its_eff - 1;
         s.n_rev += 1;
     }
 
@@ -908,7 +928,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     if (s.opt_conditioner) {
         tv_grad_stats_kernel<<<dim3(kStatBlocks, kNumOutputs), 256, 0, st>>>(fa, partial);
         CNL_TRY(after_launch("tv_grad_stats_kernel"));
-        tv_conditioner_kernel<<<1, 32, 0, st>>>(partial, fa, state, factor, s.run);
+        tv_conditioner_kernel<<<1, 32 * kNumOutputs, 0, st>>>(partial, fa, state, factor, s.run);
         CNL_TRY(after_launch("tv_conditioner_kernel"));
     }
     tv_grad_apply_kernel<<<dim3(296, kNumOutputs), 256, 0, st>>>(fa, s.opt_conditioner ? factor : nullptr);
@@ -1029,21 +1049,22 @@ extern "C" int cnl_tv_get_timing(int id, double* out_host) {
     int rc;
     Slot* sp = get_slot(id, &rc);
     if (!sp) return rc;
-    double ms_f = 0, ms_r = 0, lf = 0, lr = 0;
+    double ms_f = 0, ms_r = 0, lf = 0, lr = 0, itf = 0, itr = 0;
     for (int i = 0; i < sp->n_fwd; ++i) {
         float ms = 0;
         CNL_TRY(check_cuda(cudaEventSynchronize(sp->ev_fwd[i][1]), "cudaEventSynchronize"));
         CNL_TRY(check_cuda(cudaEventElapsedTime(&ms, sp->ev_fwd[i][0], sp->ev_fwd[i][1]), "cudaEventElapsedTime"));
-        ms_f += ms; lf += sp->launches_fwd[i];
+        ms_f += ms; lf += sp->launches_fwd[i]; itf += sp->iters_fwd[i];
     }
     for (int i = 0; i < sp->n_rev; ++i) {
         float ms = 0;
         CNL_TRY(check_cuda(cudaEventSynchronize(sp->ev_rev[i][1]), "cudaEventSynchronize"));
         CNL_TRY(check_cuda(cudaEventElapsedTime(&ms, sp->ev_rev[i][0], sp->ev_rev[i][1]), "cudaEventElapsedTime"));
-        ms_r += ms; lr += sp->launches_rev[i];
+        ms_r += ms; lr += sp->launches_rev[i]; itr += sp->iters_rev[i];
     }
     out_host[0] = ms_f; out_host[1] = lf; out_host[2] = sp->n_fwd;
     out_host[3] = ms_r; out_host[4] = lr; out_host[5] = sp->n_rev;
+    out_host[6] = itf; out_host[7] = itr;
     sp->n_fwd = sp->n_rev = 0;
     return CNL_OK;
 }

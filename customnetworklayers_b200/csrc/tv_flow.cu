@@ -110,20 +110,11 @@ __device__ __forceinline__ Unit decode_unit(int u, int ntiles, int tiles_x, int 
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kFwdFlowSmemBytes = (2 * kWarps * 32 + 6 * kRows * kThreads) * (int)sizeof(float4);
 
-// kPair: the two exchanges of a fused step are ordered warp to warp (each warp only waits for the neighbour whose row
-// it reads) instead of by CTA-wide barriers, so that warps may drift apart by a step and do not all hit the same pipe
-// at the same time.
-template <int K, bool kPair>
+template <int K>
 __global__ void __launch_bounds__(kThreads, 1)
 tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int tiles_y) {
     extern __shared__ float4 smem4[];
     __shared__ int sh_ctl[2];
-    __shared__ unsigned long long sh_bar[2][kWarps];      // [0][w]: row of warp w+1 ready for w; [1][w]: flux of w ready for w+1
-    unsigned phase = 0;
-    if (kPair) {
-        if (threadIdx.x < 2 * kWarps) mbar_init(&sh_bar[0][0] + threadIdx.x, 1);
-        __syncthreads();
-    }
     float4(*sh_y)[32] = reinterpret_cast<float4(*)[32]>(smem4);
     float4(*sh_f)[32] = sh_y + kWarps;
     float4* buf_item = smem4 + 2 * kWarps * 32;                 // y, x, b of the next (unit, channel)
@@ -213,13 +204,7 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
                 const float t = p.tab.t[g0 + j];
                 const int slot = p.tab.ckpt_slot[g0 + j];
                 sh_y[g.warp][g.lane] = y[0];
-                if (kPair) {
-                    __syncwarp();
-                    if (g.warp > 0 && g.lane == 0) mbar_arrive(&sh_bar[0][g.warp - 1]);
-                    if (g.warp + 1 < kWarps && !mbar_wait(&sh_bar[0][g.warp], phase)) *reinterpret_cast<volatile int*>(p.status) = 2;
-                } else {
-                    __syncthreads();
-                }
+                __syncthreads();
                 const float4 ybelow = (g.warp + 1 < kWarps) ? sh_y[g.warp + 1][g.lane] : zero4();
                 if (slot >= 0) {
                     float* ck = p.ckpt + (size_t)slot * p.vol;
@@ -234,15 +219,7 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
                     const int ok = __all_sync(kFull, seen >= nxt.kb);
                     if (lane == 0) sh_ctl[1] = ok;
                 }
-                if (kPair) {
-                    __syncwarp();
-                    if (g.warp + 1 < kWarps && g.lane == 0) mbar_arrive(&sh_bar[1][g.warp]);
-                    if (g.warp > 0 && !mbar_wait(&sh_bar[1][g.warp - 1], phase)) *reinterpret_cast<volatile int*>(p.status) = 2;
-                    phase ^= 1;
-                    if (j == 0 && last_ch && has_next) __syncthreads();      // the whole CTA needs warp 0's verdict
-                } else {
-                    __syncthreads();
-                }
+                __syncthreads();
                 if (j == 0 && last_ch && has_next && sh_ctl[1]) {
                     issue(nxt, 0, true);
                     next_issued = true;
@@ -469,10 +446,7 @@ int launch_tv_fwd_flow(const FwdFlowParams& p, cudaStream_t st) {
     const int tiles_x = (p.W + kTileW - 1) / kTileW, tiles_y = (p.H + TH - 1) / TH;
     const long long units = (long long)tiles_x * tiles_y * p.N * p.nblocks;
     if (units <= 0 || units >= (1ll << 30)) return fail(CNL_ERR_BAD_SHAPE, "too many work units for a single-launch sweep");
-    static int pair = -1;
-    if (pair < 0) { const char* e = std::getenv("CNL_TV_PAIRSYNC"); pair = (e && e[0] == '1') ? 1 : 0; }
-    if (pair) return launch_flow(tv_fwd_flow_kernel<K, true>, p, kFwdFlowSmemBytes, units, tiles_x, tiles_y, st, "tv_fwd_flow_kernel");
-    return launch_flow(tv_fwd_flow_kernel<K, false>, p, kFwdFlowSmemBytes, units, tiles_x, tiles_y, st, "tv_fwd_flow_kernel");
+    return launch_flow(tv_fwd_flow_kernel<K>, p, kFwdFlowSmemBytes, units, tiles_x, tiles_y, st, "tv_fwd_flow_kernel");
 }
 
 int launch_tv_rev_flow(const RevFlowParams& p, cudaStream_t st) {

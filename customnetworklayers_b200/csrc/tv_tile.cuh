@@ -103,31 +103,6 @@ __device__ __forceinline__ void prox_extrapolate_row(const float4& x05, const fl
     x = xn;
 }
 
-// ---- warp-to-warp hand-over through shared-memory mbarriers -------------------------------------------------------
-// A producer warp writes a row, its lane 0 arrives (release) once the warp's writes are ordered by __syncwarp; the
-// consumer warp waits (acquire) on the phase parity.  Each barrier expects one arrival per phase.
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"((unsigned)__cvta_generic_to_shared(bar)) : "memory");
-}
-// Bounded: gives up (returns false) after kMbarTries unsuccessful tries, each of which may itself sleep for a while.
-constexpr int kMbarTries = 1 << 22;
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    const unsigned addr = (unsigned)__cvta_generic_to_shared(bar);
-    for (int i = 0; i < kMbarTries; ++i) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.acquire.cta.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
 struct TileGeom {
     int lane, warp;
     int gx;                 // image column of the lane's first pixel (multiple of 4, may be outside the image)

@@ -174,7 +174,8 @@ def read_history(id: int, like: torch.Tensor, its: int):
 def get_timing(id: int) -> dict:
     """CUDA-event records made while option OPT_TIMING was on (see cnl_tv_get_timing); clears them."""
     import ctypes
-    buf = (ctypes.c_double * 6)()
+    buf = (ctypes.c_double * 8)()
     _lib.check(_lib.load().cnl_tv_get_timing(int(id), ctypes.cast(buf, ctypes.c_void_p)), "get_timing")
     return {"fwd_ms": buf[0], "fwd_launches": int(buf[1]), "fwd_calls": int(buf[2]),
-            "rev_ms": buf[3], "rev_launches": int(buf[4]), "rev_calls": int(buf[5])}
+            "rev_ms": buf[3], "rev_launches": int(buf[4]), "rev_calls": int(buf[5]),
+            "fwd_iters": int(buf[6]), "rev_iters": int(buf[7])}

@@ -101,10 +101,12 @@ int cnl_tv_num_checkpoints(int id);
 int cnl_tv_set_option(int id, int option, int value);
 
 /*
- * Reads and clears the CUDA-event records made under CNL_OPT_TIMING.  out_host (HOST memory, 6 doubles) receives
- * {forward loop ms (summed over recorded calls), kernel launches inside those loops, recorded forward calls,
- *  reverse loop ms, launches, recorded backward calls}.  Waits for the recorded events.  No reference counterpart
- * (the reference has no timing code).
+ * Reads and clears the CUDA-event records made under CNL_OPT_TIMING.  out_host (HOST memory, 8 doubles) receives
+ * {forward ms (summed over recorded calls), kernel launches timed, recorded forward calls,
+ *  reverse ms, launches timed, recorded backward calls, forward iterations the timed launches cover, reverse ditto}.
+ * A record brackets the iteration kernels of a sweep: the single-launch sweep alone where it runs (a shorter last time
+ * block then follows outside the record), otherwise the whole loop of launches.  Waits for the recorded events.
+ * No reference counterpart (the reference has no timing code).
  */
 int cnl_tv_get_timing(int id, double* out_host);
 
