@@ -603,9 +603,9 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
         int first_launch = 0;
         // Single-launch sweep: every full time block of kFuseMax iterations in one cooperative launch whose tiles are
         // ordered by progress counters; a shorter last block, if any, follows as an ordinary launch.
-        const int nfull = its_eff / kFuseMax;
-        if (!recompute && fuse == kFuseMax && s.opt_flow && nfull >= 1 && its_eff <= kFlowMaxIts && flow_enabled()) {
-            const bool rem = nfull < nlaunch;
+        const int nfull = (its_eff + kFuseMax - 1) / kFuseMax;       // the last time block may be shorter
+        if (!recompute && fuse == kFuseMax && s.opt_flow && its_eff <= kFlowMaxIts && flow_enabled()) {
+            const bool rem = false;
             FwdFlowParams fp{};
             fp.init = init;
             fp.ybuf[0] = y0; fp.ybuf[1] = y1;
@@ -618,6 +618,7 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
             const int ntiles = flow_tiles(h, w, n);
             fp.progress = sync; fp.abort = sync + ntiles; fp.status = flow_status_device_ptr();
             fp.nblocks = nfull;
+            fp.its = its_eff;
             fp.N = n; fp.C = ch; fp.H = h; fp.W = w; fp.P = P;
             fill_flow_tables(s, its_eff, fp.tab);
             CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0, L.sync_words * sizeof(int), st), "zero progress counters"));
@@ -628,14 +629,11 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
             if (timing) {          // the record covers the single-launch sweep alone
                 CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][1], st), "cudaEventRecord"));
                 s.launches_fwd[s.n_fwd] = 1;
-                s.iters_fwd[s.n_fwd] = nfull * kFuseMax;
+                s.iters_fwd[s.n_fwd] = its_eff;
                 s.n_fwd += 1;
                 timing = false;
             }
-            first_launch = nfull;
-            y_in = fp.ybuf[(nfull - 1) & 1];
-            x_in = fp.xbuf[(nfull - 1) & 1];
-            while (next_ckpt < s.sched.size() && s.sched[next_ckpt] < nfull * kFuseMax) ++next_ckpt;
+            first_launch = nlaunch;          // nothing is left for the per-time-block launches
         }
         for (int i = first_launch; i < nlaunch; ++i) {
             const int g0 = plan[i].g0, K = plan[i].K;
@@ -822,7 +820,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
         int flip = 0;
         int seg = nseg - 1;                       // segment the sweep is in (recompute mode)
         int g_start = its_eff - 2;
-        const int nfull = (its_eff - 1) / kFuseMax;          // full time blocks of the reverse sweep
+        const int nfull = (its_eff - 1 + kFuseMax - 1) / kFuseMax;      // time blocks of the reverse sweep, the last one may be shorter
         if (!s.recompute && fuse == kFuseMax && s.opt_flow && nfull >= 1 && its_eff <= kFlowMaxIts && flow_enabled()) {
             RevFlowParams rp{};
             rp.gbuf[0] = ga; rp.gbuf[1] = gb;                  // block 0 reads the seed in gb and writes ga
@@ -844,14 +842,11 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
             if (timing) {          // the record covers the single-launch sweep alone
                 CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][1], st), "cudaEventRecord"));
                 s.launches_rev[s.n_rev] = 1;
-                s.iters_rev[s.n_rev] = nfull * kFuseMax;
+                s.iters_rev[s.n_rev] = its_eff - 1;
                 s.n_rev += 1;
                 timing = false;
             }
-            g_cur = rp.gbuf[(nfull - 1) & 1];
-            acc_cur = rp.abuf[(nfull - 1) & 1];
-            flip = nfull & 1;
-            g_start -= nfull * kFuseMax;
+            g_start = -1;                    // nothing is left for the per-time-block launches
         }
         for (int g0 = g_start; g0 >= 0;) {
             int K = std::min(fuse, g0 + 1);

@@ -49,9 +49,6 @@ __device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
 __device__ __forceinline__ void red_release_gpu(int* p, int v) {
     asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ float4 ld4_l2(const float* p, bool ok) {
-    return ok ? __ldcg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
-}
 
 // Address of the progress counter this lane watches: lanes 0..8 take the 3 x 3 tiles around (tx, ty) of image n;
 // `valid` is false for lanes beyond 8 and for neighbours outside the image.
@@ -110,7 +107,8 @@ __device__ __forceinline__ Unit decode_unit(int u, int ntiles, int tiles_x, int 
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kFwdFlowSmemBytes = (2 * kWarps * 32 + 6 * kRows * kThreads) * (int)sizeof(float4);
 
-template <int K>
+// kShort: the sweep's last time block has fewer than K iterations (the iteration count is not a multiple of K).
+template <int K, bool kShort>
 __global__ void __launch_bounds__(kThreads, 1)
 tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int tiles_y) {
     extern __shared__ float4 smem4[];
@@ -201,6 +199,7 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
             if (!last_ch) issue(cur, ch + 1, false);
 #pragma unroll
             for (int j = 0; j < K; ++j) {
+                if (kShort && g0 + j >= p.its) continue;       // a shorter last time block; uniform over the CTA
                 const float t = p.tab.t[g0 + j];
                 const int slot = p.tab.ckpt_slot[g0 + j];
                 sh_y[g.warp][g.lane] = y[0];
@@ -278,6 +277,8 @@ struct FlowSteps {
         return slot >= 0 ? p.ckpt + (size_t)slot * p.vol : nullptr;
     }
     __device__ __forceinline__ float t(int j) const { return p.tab.t[gfirst - j]; }
+    __device__ __forceinline__ bool active(int j) const { return gfirst - j >= 0; }      // the last time block may be short
+    __device__ __forceinline__ bool last(int j) const { return gfirst - j == 0; }
 };
 
 template <int K>
@@ -338,7 +339,7 @@ tv_rev_flow_kernel(const __grid_constant__ RevFlowParams p, int tiles_x, int til
 #pragma unroll
             for (int r = 0; r < kRows; ++r) off[r] = ((size_t)tc.n * p.C + ch) * plane + (size_t)g.gy[r] * p.P + g.gx;
             rev_channel<K, true>(sh, g, off, p.gbuf[(kb + 1) & 1], p.abuf[(kb + 1) & 1], p.b, p.gbuf[kb & 1], p.abuf[kb & 1],
-                                 p.g_b, steps.gfirst - K + 1 == 0 ? p.x1bar : nullptr, c, wx, wy, steps, [](int) {});
+                                 p.g_b, p.x1bar, c, wx, wy, steps, [](int) {});
         }
         const int ue = opaque(u);
         const int kbe = ue / ntiles;
@@ -446,7 +447,9 @@ int launch_tv_fwd_flow(const FwdFlowParams& p, cudaStream_t st) {
     const int tiles_x = (p.W + kTileW - 1) / kTileW, tiles_y = (p.H + TH - 1) / TH;
     const long long units = (long long)tiles_x * tiles_y * p.N * p.nblocks;
     if (units <= 0 || units >= (1ll << 30)) return fail(CNL_ERR_BAD_SHAPE, "too many work units for a single-launch sweep");
-    return launch_flow(tv_fwd_flow_kernel<K>, p, kFwdFlowSmemBytes, units, tiles_x, tiles_y, st, "tv_fwd_flow_kernel");
+    if (p.its % K != 0)
+        return launch_flow(tv_fwd_flow_kernel<K, true>, p, kFwdFlowSmemBytes, units, tiles_x, tiles_y, st, "tv_fwd_flow_kernel");
+    return launch_flow(tv_fwd_flow_kernel<K, false>, p, kFwdFlowSmemBytes, units, tiles_x, tiles_y, st, "tv_fwd_flow_kernel");
 }
 
 int launch_tv_rev_flow(const RevFlowParams& p, cudaStream_t st) {

@@ -231,11 +231,14 @@ int launch_tv_fwd_fused(const FwdFusedParams& p, int K, cudaStream_t st) {
 // ---------------------------------------------------------------------------------------------------------------
 
 // Per-step inputs of a launch that fuses K reverse iterations: straight from the launch parameters.
+template <int K>
 struct FusedSteps {
     const RevFusedParams& p;
     __device__ __forceinline__ const float* hist(int j) const { return p.hist[j]; }
     __device__ __forceinline__ const float* ckpt(int j) const { return p.ckpt[j]; }
     __device__ __forceinline__ float t(int j) const { return p.t[j]; }
+    __device__ __forceinline__ constexpr bool active(int) const { return true; }
+    __device__ __forceinline__ constexpr bool last(int j) const { return j == K - 1; }     // the driver passes x1bar only in the sweep's last launch
 };
 
 template <int K>
@@ -249,7 +252,7 @@ tv_rev_fused_kernel(const __grid_constant__ RevFusedParams p) {
     float4 c[kRows], wx[kRows], wy[kRows];
     load_maps(p, g, n, c, wx, wy);
     rev_tile_begin(sh, c);
-    const FusedSteps steps{p};
+    const FusedSteps<K> steps{p};
     for (int ch = 0; ch < p.C; ++ch) {
         size_t off[kRows];
 #pragma unroll

@@ -79,7 +79,8 @@ struct FwdFlowParams {
     int* progress;              // one counter per tile, zero at launch
     int* abort;                 // device word, zero at launch; set when a wait gave up
     int* status;                // host-mapped word that receives the reason
-    int nblocks;                // time blocks of kFuseMax iterations
+    int nblocks;                // time blocks of kFuseMax iterations (the last one may be shorter)
+    int its;                    // iterations of the sweep
     int N, C, H, W;
     int P;                      // row pitch in floats, as in FwdFusedParams
     FlowTables tab;
@@ -104,7 +105,7 @@ struct RevFlowParams {
     int* abort;
     int* status;
     int g_first;                // iteration of the first reverse step of time block 0
-    int nblocks;
+    int nblocks;                // time blocks of kFuseMax reverse steps; the last one ends at iteration 0 and may be shorter
     int N, C, H, W;
     int P;
     FlowTables tab;

@@ -303,7 +303,9 @@ __device__ __forceinline__ void rev_tile_end(const RevSmem& sh, const P& p, cons
 }
 
 // K reverse steps of one channel of one tile.  `st` supplies, per fused step j, the stored iterate hist(j) (j = 0..K;
-// null where there is none), the checkpointed y ckpt(j) (null: y is rebuilt) and the momentum factor t(j).
+// null where there is none), the checkpointed y ckpt(j) (null: y is rebuilt), the momentum factor t(j), whether the step
+// exists at all (active(j): the last time block of a sweep may be shorter than K) and whether it is the sweep's last
+// one (last(j): dL/dx of that step is the init gradient).
 // kCoherent: g_in / acc_in are written by other CTAs of the same launch and must come from L2.
 // `hook(j)` runs in every thread right after the first barrier of step j (the single-launch sweep publishes there).
 template <int K, bool kCoherent, typename Steps, typename Hook>
@@ -334,6 +336,7 @@ __device__ __forceinline__ void rev_channel(const RevSmem& sh, const TileGeom& g
     }
 #pragma unroll
     for (int j = 0; j < K; ++j) {
+        if (!st.active(j)) continue;         // uniform over the CTA: the barriers below are skipped by all or none
         const float t = st.t(j);
         // prefetch the pre-prox iterate the next fused step needs
         if (j + 2 <= K) {
@@ -390,7 +393,7 @@ __device__ __forceinline__ void rev_channel(const RevSmem& sh, const TileGeom& g
             gq[r] = reverse_row(ybar, acc[r], xh[r], b[r], c[r], sh.inv[r * kThreads + tid], t, dc, db, xb);
             sh.dc[r * kThreads + tid] = dc;
             sh.db[r * kThreads + tid] = db;
-            if (j == K - 1 && x1bar != nullptr && g.store[r]) st4(x1bar + off[r], xb);
+            if (st.last(j) && x1bar != nullptr && g.store[r]) st4(x1bar + off[r], xb);
         }
         cp_async_wait_all();
 #pragma unroll
