@@ -338,6 +338,37 @@ def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, war
     ms_e2e, _, _ = timed(step_e2e, steps, finish=pipe.join)
     e2e_steps = sorted(timed.last_per_step)
     # where an end-to-end step spends its time: one call alone, CUDA events per chunk from the call's start
+    # The same copies without any kernel: what the host memory / PCIe side of the box sustains when every rank streams
+    # at once (the ceiling of the end-to-end figure on more than one GPU).
+    copies_ms = None
+    if world > 1:
+        dbuf = {k: torch.empty_like(host[k], device=dev) for k in keys}
+        obuf = {k: torch.empty_like(host_res[k], device=dev) for k in out_keys}
+
+        def copies():
+            with torch.cuda.stream(pipe.s_in):
+                for k in keys:
+                    dbuf[k].copy_(host[k], non_blocking=True)
+            with torch.cuda.stream(pipe.s_out):
+                for k in out_keys:
+                    host_res[k].copy_(obuf[k], non_blocking=True)
+
+        for _ in range(3):
+            copies()
+        barrier()
+        c0, c1, c2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        c0.record()
+        pipe.s_in.wait_event(c0)
+        pipe.s_out.wait_event(c0)
+        for _ in range(steps):
+            copies()
+        c1.record(pipe.s_in)
+        c2.record(pipe.s_out)
+        barrier()
+        t = torch.tensor([max(c0.elapsed_time(c1), c0.elapsed_time(c2))], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        copies_ms = float(t.item()) / steps
+        del dbuf, obuf
     barrier()
     pipe.timeline = []
     step_e2e()                        # on every rank: the call contains the all-reduce
@@ -347,7 +378,7 @@ def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, war
     barrier()
     res = {"nb": nb, "ms": ms, "launches": launches, "clocks": clocks, "tm": tm, "ms_e2e": ms_e2e, "chunk": chunk,
            "h2d": sum(host[k].numel() * 4 for k in keys), "d2h": sum(t.numel() * 4 for t in host_res.values()) + 4,
-           "breakdown": breakdown,
+           "breakdown": breakdown, "copies_ms": copies_ms,
            "e2e_step_ms": {"min": e2e_steps[0], "median": e2e_steps[len(e2e_steps) // 2], "max": e2e_steps[-1]}}
     del D, host, host_res, pipe
     ext.release(pid)
@@ -432,6 +463,8 @@ def run_ours(args, rank, local_rank, world):
                     "ms_per_step": ms_e2e / args.steps, "api": "host_pipeline.tv_fwd_bwd_from_host",
                     "chunk_images": M["chunk"],
                     "step_ms_on_compute_stream": M["e2e_step_ms"],
+                    "copies_only_ms_per_step": M["copies_ms"],
+                    "copies_only_aggregate_gbs": ((M["h2d"] + M["d2h"]) * world / (M["copies_ms"] * 1e-3) / 1e9) if M["copies_ms"] else None,
                     "single_call_ms_since_start": M["breakdown"]},
             "gpu_launches": int(M["launches"]),
             "clocks": M["clocks"],
