@@ -127,10 +127,10 @@ def cpu_fwd_bwd(I, its):
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per image and iteration of the single-launch sweeps at
 # 2x384x1280, from an `ncu --set full` capture of one launch each on the `prof` workload (batch 8, 20 iterations:
-# reverse 2143 MB for 16 iterations, forward 1695 MB for 20), NOT measured in this run
+# reverse 2654 MB for 19 iterations, forward 1693 MB for 20), NOT measured in this run
 # (summary under profiles/).  Traffic grows in proportion to images and iterations of a launch, so
 # other batch sizes and iteration counts of the same image scale it; other image sizes have no capture and report null.
-NCU_TRAFFIC_PER_IMAGE_ITER = {(2, 384, 1280): {"reverse": 2143.1e6 / 16 / 8, "forward": 1694.5e6 / 20 / 8}}
+NCU_TRAFFIC_PER_IMAGE_ITER = {(2, 384, 1280): {"reverse": 2653.8e6 / 19 / 8, "forward": 1693.2e6 / 20 / 8}}
 TRAFFIC_SOURCE = ("ncu capture of one single-launch sweep on the prof workload (summary under profiles/), "
                   "scaled by images and iterations of the launch; not measured in this run")
 

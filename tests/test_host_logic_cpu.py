@@ -46,7 +46,7 @@ def test_traffic_figure_scales_with_images_and_iterations():
     assert abs(t8["reverse"] / t1["reverse"] - 8.0) < 1e-9 and abs(t8["forward"] / t1["forward"] - 8.0) < 1e-9
     # one time block (four iterations) of the batch of 8: what the capture showed
     blk = b.ncu_traffic_per_launch(8, 2, 384, 1280, 4, 4)
-    assert 500e6 < blk["reverse"] < 570e6 and 300e6 < blk["forward"] < 360e6
+    assert 500e6 < blk["reverse"] < 600e6 and 300e6 < blk["forward"] < 360e6
     assert b.ncu_traffic_per_launch(8, 2, 100, 100, 4, 4) is None
     fwd_b, rev_b = b.algorithmic_bytes_per_pixel_iter(2)
     assert (fwd_b, rev_b) == (60, 108)
