@@ -105,7 +105,7 @@ __device__ __forceinline__ Unit decode_unit(int u, int ntiles, int tiles_x, int 
 // ---------------------------------------------------------------------------------------------------------------
 // forward sweep: p.nblocks time blocks of K iterations in one launch
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kFwdFlowSmemBytes = (2 * kWarps * 32 + 6 * kRows * kThreads) * (int)sizeof(float4);
+constexpr int kFwdFlowSmemBytes = (2 * kWarps * 32 + 7 * kRows * kThreads) * (int)sizeof(float4);
 
 // kShort: the sweep's last time block has fewer than K iterations (the iteration count is not a multiple of K).
 template <int K, bool kShort>
@@ -117,6 +117,7 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
     float4(*sh_f)[32] = sh_y + kWarps;
     float4* buf_item = smem4 + 2 * kWarps * 32;                 // y, x, b of the next (unit, channel)
     float4* buf_maps = buf_item + 3 * kRows * kThreads;         // c, wx, wy of the next unit
+    float4* sh_inv = buf_maps + 3 * kRows * kThreads;           // 1 / (1 + c) of the current unit, one slot per thread and row
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ntiles = tiles_x * tiles_y * p.N;
     const int total = ntiles * p.nblocks;
@@ -185,6 +186,10 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
                     wy[r] = buf_maps[(2 * kRows + r) * kThreads + tid];
                 }
                 finish_maps(g, p.H, p.W, wx, wy);
+#pragma unroll
+                for (int r = 0; r < kRows; ++r)
+                    sh_inv[r * kThreads + tid] = make_float4(rcp_approx(1.0f + c[r].x), rcp_approx(1.0f + c[r].y),
+                                                             rcp_approx(1.0f + c[r].z), rcp_approx(1.0f + c[r].w));
             }
             float4 y[kRows], x[kRows], b[kRows];
             size_t off[kRows];
@@ -234,7 +239,7 @@ tv_fwd_flow_kernel(const __grid_constant__ FwdFlowParams p, int tiles_x, int til
                     const float4 x05 = divergence_row_fwd(y[r], fx, fy, fx_left, fyc);
                     fyc = fy;
                     if (g.store[r]) st4(hj + off[r], x05);
-                    prox_extrapolate_row(x05, b[r], c[r], t, x[r], y[r]);
+                    prox_extrapolate_row_inv(x05, b[r], c[r], sh_inv[r * kThreads + tid], t, x[r], y[r]);
                 }
             }
 #pragma unroll

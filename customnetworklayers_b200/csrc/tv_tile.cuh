@@ -88,6 +88,27 @@ __device__ __forceinline__ float prox_point(float x05, float b, float c) {
     if (hi < b - 1.0f) x = hi;
     return x;
 }
+// the same with 1/(1+c) supplied (it is the same in every iteration of a tile)
+__device__ __forceinline__ float prox_point_inv(float x05, float b, float c, float inv) {
+    float x = fmaf(c, b, x05) * inv;
+    const float lo = x05 - c, hi = x05 + c;
+    if (lo > 1.0f + b) x = lo;
+    if (hi < b - 1.0f) x = hi;
+    return x;
+}
+__device__ __forceinline__ void prox_extrapolate_row_inv(const float4& x05, const float4& b, const float4& c, const float4& inv,
+                                                         float t, float4& x, float4& y) {
+    float4 xn;
+    xn.x = prox_point_inv(x05.x, b.x, c.x, inv.x);
+    xn.y = prox_point_inv(x05.y, b.y, c.y, inv.y);
+    xn.z = prox_point_inv(x05.z, b.z, c.z, inv.z);
+    xn.w = prox_point_inv(x05.w, b.w, c.w, inv.w);
+    y.x = fmaf(t, xn.x - x.x, xn.x);
+    y.y = fmaf(t, xn.y - x.y, xn.y);
+    y.z = fmaf(t, xn.z - x.z, xn.z);
+    y.w = fmaf(t, xn.w - x.w, xn.w);
+    x = xn;
+}
 // prox + momentum extrapolation of one row: updates x (primal) and y (momentum variable)
 __device__ __forceinline__ void prox_extrapolate_row(const float4& x05, const float4& b, const float4& c, float t,
                                                      float4& x, float4& y) {
