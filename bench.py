@@ -437,12 +437,12 @@ def run_ours(args, rank, local_rank, world):
         if args.per_gpu_batch:
             cfg["workload"] += f" [one GPU timing a shard of {nb} image(s)]"
             cfg["global_batch"] = nb
-        cfg.update({"per_gpu_batch": nb, "fuse": args.fuse,
-                    "history": "checkpoints only, segments recomputed in the backward pass" if args.recompute else "every iterate resident"})
+        arm = {"what": "this library on the GPU(s)", "per_gpu_batch": nb, "fuse": args.fuse,
+               "history": "checkpoints only, segments recomputed in the backward pass" if args.recompute else "every iterate resident"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+            "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg, "arm": arm,
             "roofline": {"bound": "hbm", "kernel": "reverse sweep (tv_rev_flow_kernel: every full 4-iteration time block in one launch)" if iters_per_launch > 4 else "reverse iteration kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic["reverse"] if traffic else None,
