@@ -252,7 +252,7 @@ def run_reference_arm(args, rank, world):
 # ---------------------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------------------
-def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, warmup, sample_clocks):
+def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, warmup, sample_clocks, peer=None):
     """Times `steps` forward+backward steps of a per-GPU batch of nb images, inputs resident, then the same through the
     host-buffer API.  Returns a dict of raw figures (times are the maximum over ranks)."""
     import torch
@@ -280,8 +280,11 @@ def measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, steps, war
         c = c_raw * lam                                   # c = lambda * c_raw, lambda is the learned scalar
         sol = ext.forward(D["wx"], D["wy"], c, D["b"], D["init"], its, pid)[0]
         grads = ext.backward(D["grad"], D["wx"], D["wy"], c, D["b"], its, pid)
-        g_lam = ext.lambda_grad(grads[2], c_raw)
-        allreduce_scalar_grads(g_lam)
+        if peer is not None:                              # local reduction + exchange over peer memory, fused
+            g_lam = peer.lambda_grad(grads[2], c_raw)
+        else:
+            g_lam = ext.lambda_grad(grads[2], c_raw)
+            allreduce_scalar_grads(g_lam)
         return sol, grads, g_lam
 
     host_lam = torch.empty(1).pin_memory()
@@ -409,10 +412,27 @@ def run_ours(args, rank, local_rank, world):
     if args.per_gpu_batch:
         nb = args.per_gpu_batch          # one GPU standing in for one rank of a larger job (development aid)
     its_eff = 2 * (its // 2)
-    M = measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, args.steps, args.warmup, True)
+    peer, collective = None, "none (one GPU)"
+    if world > 1:
+        collective = "NCCL all-reduce of the lambda gradient (1 float)"
+        if args.collective == "peer":
+            try:
+                from customnetworklayers_b200.dist import PeerAllReduce
+                peer = PeerAllReduce()
+                collective = "lambda-gradient reduction fused with a one-shot exchange over NVLink peer memory (cnl_tv_lambda_grad_allreduce)"
+            except Exception as e:          # e.g. no symmetric-memory support: NCCL does the same job
+                peer = None
+                if rank == 0:
+                    print(f"peer all-reduce unavailable ({str(e)[:160]}); using NCCL", file=sys.stderr, flush=True)
+        # every rank must take the same path
+        flag = torch.tensor([1 if peer is not None else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            peer, collective = None, "NCCL all-reduce of the lambda gradient (1 float)"
+    M = measure_tv(args, dev, rank, local_rank, world, nb, ch, h, w, its, args.steps, args.warmup, True, peer=peer)
     weak = None
     if world > 1 and scaling == "strong" and not args.per_gpu_batch:
-        weak = measure_tv(args, dev, rank, local_rank, world, nb_full, ch, h, w, its, args.steps, args.warmup, False)
+        weak = measure_tv(args, dev, rank, local_rank, world, nb_full, ch, h, w, its, args.steps, args.warmup, False, peer=peer)
 
     ms, ms_e2e, tm = M["ms"], M["ms_e2e"], M["tm"]
     pixel_iters = world * nb * h * w * its_eff
@@ -437,7 +457,7 @@ def run_ours(args, rank, local_rank, world):
         if args.per_gpu_batch:
             cfg["workload"] += f" [one GPU timing a shard of {nb} image(s)]"
             cfg["global_batch"] = nb
-        arm = {"what": "this library on the GPU(s)", "per_gpu_batch": nb, "fuse": args.fuse,
+        arm = {"what": "this library on the GPU(s)", "per_gpu_batch": nb, "fuse": args.fuse, "collective": collective,
                "history": "checkpoints only, segments recomputed in the backward pass" if args.recompute else "every iterate resident"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -792,6 +812,8 @@ def main():
                     help="strong (default): the batch of the workload is sharded over the GPUs; weak: that batch per GPU")
     ap.add_argument("--per-gpu-batch", type=int, default=0,
                     help="development aid: time this many images on the GPU(s) given, as one rank of a larger job would")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="how the lambda gradient is summed over GPUs: fused reduction + exchange over peer memory, or NCCL")
     ap.add_argument("--no-secondary", action="store_true", help="skip the compact records of the other configurations")
     ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
     ap.add_argument("--fuse", type=int, default=0)

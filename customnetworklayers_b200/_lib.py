@@ -22,6 +22,10 @@ SIGNATURES = {
     "cnl_tv_get_timing": (c_int, [c_int, c_void_p]),
     "cnl_tv_run_count": (c_int, [c_int]),
     "cnl_tv_forward_count": (c_int, [c_int]),
+    "cnl_peer_allreduce_bytes": (c_longlong, []),
+    "cnl_peer_allreduce_sum": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_ulonglong, c_void_p]),
+    "cnl_peer_allreduce_status": (c_int, []),
+    "cnl_tv_lambda_grad_allreduce": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_ulonglong, c_void_p]),
     "cnl_launch_count": (c_ulonglong, []),
     "cnl_tv_lambda_grad": (c_int, [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]),
     "cnl_dot_scratch_floats": (c_int, []),

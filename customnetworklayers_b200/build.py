@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libcnl_b200.so")
-SOURCES = ["common.cu", "tv_fista.cu", "tv_fused.cu", "tv_flow.cu", "tv_noalloc.cu", "median.cu", "quadfit.cu", "tgv.cu", "tgv_vec.cu", "wmedian.cu"]
+SOURCES = ["common.cu", "tv_fista.cu", "tv_fused.cu", "tv_flow.cu", "peer_allreduce.cu", "tv_noalloc.cu", "median.cu", "quadfit.cu", "tgv.cu", "tgv_vec.cu", "wmedian.cu"]
 HEADERS = ["common.h", "tv_math.cuh", "tv_fused.cuh", "tv_tile.cuh", "tgv_vec.cuh", os.path.join("..", "..", "include", "cnl_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--cudart", "shared"]

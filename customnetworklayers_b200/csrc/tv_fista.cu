@@ -1093,3 +1093,14 @@ extern "C" int cnl_tv_lambda_grad(const float* g_c, const float* c_raw, long lon
     tv_dot_final_kernel<<<1, 32, 0, st>>>(scratch, kDotBlocks, out);
     return after_launch("tv_dot_final_kernel");
 }
+
+extern "C" int cnl_tv_lambda_grad_allreduce(const float* g_c, const float* c_raw, long long count, float* out, float* scratch,
+                                            void* const* peer_bufs, int rank, int world, unsigned long long seq, void* stream) {
+    if (!g_c || !c_raw || !out || !scratch) return fail(CNL_ERR_NULL, "null pointer argument");
+    if (count < 0) return fail(CNL_ERR_BAD_SHAPE, "negative element count");
+    if ((reinterpret_cast<size_t>(scratch) & 7) != 0) return fail(CNL_ERR_BAD_SHAPE, "scratch must be 8-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    tv_dot_partial_kernel<<<kDotBlocks, 256, 0, st>>>(g_c, c_raw, count, scratch);
+    CNL_TRY(after_launch("tv_dot_partial_kernel"));
+    return launch_tv_dot_final_allreduce(scratch, kDotBlocks, out, peer_bufs, rank, world, seq, st);
+}

@@ -135,6 +135,27 @@ int cnl_tv_lambda_grad(const float* g_c, const float* c_raw, long long count, fl
 int cnl_dot_scratch_floats(void);
 
 /*
+ * Sum of `count` (<= 64) floats over the `world` (<= 16) GPUs of one node through peer memory (NVLink / NVSwitch): the
+ * all-reduce of the learned-scalar gradients, which at this size is pure latency.  Every rank stores its values straight
+ * into every peer's exchange buffer (value and call number in one 8-byte store) and sums, in rank order, what the peers
+ * stored into its own; the result is identical on all ranks.  No counterpart in the reference (it is single-GPU); the
+ * plain alternative is an NCCL all-reduce of the same vector.
+ *   peer_bufs: HOST array of `world` device pointers; peer_bufs[r] is rank r's exchange buffer as mapped into THIS
+ *              process (symmetric / IPC memory), cnl_peer_allreduce_bytes() bytes each, zeroed before the first call;
+ *   seq:       call number, 1, 2, 3, ... and the same on every rank for the same call.
+ * Every rank must make the same calls in the same order.  Waits are bounded (about a second): a rank whose peers do not
+ * answer gets NaN, and cnl_peer_allreduce_status() then returns that call's number (0: none gave up).
+ * cnl_tv_lambda_grad_allreduce is cnl_tv_lambda_grad with this exchange fused into its final kernel: out[0] is the sum
+ * over all ranks.
+ */
+long long cnl_peer_allreduce_bytes(void);
+int cnl_peer_allreduce_sum(float* values, int count, void* const* peer_bufs, int rank, int world, unsigned long long seq,
+                           void* stream);
+int cnl_peer_allreduce_status(void);
+int cnl_tv_lambda_grad_allreduce(const float* g_c, const float* c_raw, long long count, float* out, float* scratch,
+                                 void* const* peer_bufs, int rank, int world, unsigned long long seq, void* stream);
+
+/*
  * The same reduction for callers that must not allocate device memory (real-time loops, plugins inside an engine
  * that owns all device memory): no scratch argument; the block partials live in a 32 KiB array inside the library
  * that every GPU loading the library holds until exit.  No counterpart in the reference.
