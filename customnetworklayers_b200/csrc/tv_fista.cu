@@ -6,6 +6,8 @@
 //             reference's segment-start evaluation point, cudaTV/cudaCode/TVInpaintFista.cu:1724-1727).
 //   backward: walks g = last .. 0; y_{g+1} is rebuilt from hist[g], hist[g-1] like the reference does (:1130-1189);
 //             per-pixel gradient accumulators live in the caller's output buffers.
+#include <cooperative_groups.h>
+
 #include <cmath>
 #include <cstdlib>
 #include <mutex>
@@ -92,13 +94,17 @@ tv_fwd_iter_kernel(const float* __restrict__ y_in, float* __restrict__ y_out, fl
 }
 
 // Seeds the reverse sweep at the last iteration (TVInpaintFista.cu:222-287): prox Jacobian on the upstream gradient.
-// Also clears what the sweep accumulates into: the pending momentum term and the two edge-weight gradients.
+// Also clears what the sweep accumulates into (the pending momentum term, the two edge-weight gradients) and the
+// progress counters of the single-launch reverse sweep.
 __global__ void __launch_bounds__(256)
 tv_rev_seed_kernel(const float* __restrict__ grad_out, const float* __restrict__ hist_g, const float* __restrict__ b,
                    const float* __restrict__ c, float* __restrict__ g_out, float* __restrict__ g_c,
                    float* __restrict__ g_b, float* __restrict__ acc, float* __restrict__ g_wx, float* __restrict__ g_wy,
-                   int C, size_t plane) {
+                   int C, size_t plane, int* __restrict__ sync, int sync_words) {
     const size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // the progress counters of the reverse sweep that follows start at zero
+    if (sync != nullptr && blockIdx.y == 0)
+        for (size_t i = pix; i < (size_t)sync_words; i += (size_t)gridDim.x * blockDim.x) sync[i] = 0;
     if (pix >= plane) return;
     const size_t n = blockIdx.y;
     const float conf = __ldg(c + n * plane + pix);
@@ -185,8 +191,7 @@ struct FinalizeArgs {
 };
 
 // partial[o][blk] = (sum of |g| over finite entries, number of non-finite entries)
-__global__ void __launch_bounds__(256)
-tv_grad_stats_kernel(FinalizeArgs a, double* __restrict__ partial) {
+__device__ __forceinline__ void grad_stats_block(const FinalizeArgs& a, double* __restrict__ partial) {
     const int o = blockIdx.y;
     const float* p = a.ptr[o];
     const unsigned long long cnt = a.count[o];
@@ -224,14 +229,15 @@ tv_grad_stats_kernel(FinalizeArgs a, double* __restrict__ partial) {
     }
 }
 
-// One warp per output: combines the partials in a fixed order (lane-strided sums + shuffle tree, so the result does not
-// depend on timing), updates the running mean and writes the factor of that output.
-// state[0..4] = running means (av_GC, av_GX, av_GY, av_GB, av_GI), factor[0..4] = multiplier for this call.
-__global__ void __launch_bounds__(32 * kNumOutputs)
-tv_conditioner_kernel(const double* __restrict__ partial, FinalizeArgs a, double* __restrict__ state,
-                      float* __restrict__ factor, int run) {
+__global__ void __launch_bounds__(256)
+tv_grad_stats_kernel(FinalizeArgs a, double* __restrict__ partial) { grad_stats_block(a, partial); }
+
+// One warp: combines the partials of output o in a fixed order (lane-strided sums + shuffle tree, so the result does not
+// depend on timing) and applies the running-mean rules.  Returns (in lane 0) the factor of this call and the new mean.
+__device__ __forceinline__ float conditioner_warp(const double* __restrict__ partial, const FinalizeArgs& a, int o, double av,
+                                                  int run, double& av_out) {
     const double run_step = fmin(0.975, (double)run / (double)(run + 1));       // :1761
-    const int o = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31;
     double s = 0.0, bad = 0.0;
     for (int i = lane; i < kStatBlocks; i += 32) {
         s += partial[(o * kStatBlocks + i) * 2];
@@ -241,8 +247,6 @@ tv_conditioner_kernel(const double* __restrict__ partial, FinalizeArgs a, double
         s += __shfl_down_sync(0xffffffffu, s, off);
         bad += __shfl_down_sync(0xffffffffu, bad, off);
     }
-    if (lane != 0) return;
-    double av = state[o];
     // mean |g|; a non-finite entry makes the reference restart its mean from 1000 x the running mean (:171)
     const double av_gc = (bad > 0.0) ? av * 1000.0 : (a.count[o] ? s / (double)a.count[o] : 0.0);
     float f = 1.0f;
@@ -256,17 +260,28 @@ tv_conditioner_kernel(const double* __restrict__ partial, FinalizeArgs a, double
     } else {
         av = av * run_step + (1.0 - run_step) * av_gc;
     }
-    state[o] = av;
+    av_out = av;
+    return f;
+}
+
+// One warp per output.  state[0..4] = running means (av_GC, av_GX, av_GY, av_GB, av_GI), factor[0..4] = multiplier for
+// this call.
+__global__ void __launch_bounds__(32 * kNumOutputs)
+tv_conditioner_kernel(const double* __restrict__ partial, FinalizeArgs a, double* __restrict__ state,
+                      float* __restrict__ factor, int run) {
+    const int o = threadIdx.x >> 5;
+    double av_new;
+    const float f = conditioner_warp(partial, a, o, state[o], run, av_new);
+    if ((threadIdx.x & 31) != 0) return;
+    state[o] = av_new;
     factor[o] = f;
 }
 
 // g = (finite and |g| <= 1e7 ? g : 0) * factor * scale      (:160-171, :1795-1818)
-__global__ void __launch_bounds__(256)
-tv_grad_apply_kernel(FinalizeArgs a, const float* __restrict__ factor) {
+__device__ __forceinline__ void grad_apply_block(const FinalizeArgs& a, float f) {
     const int o = blockIdx.y;
     float* p = a.ptr[o];
     const unsigned long long cnt = a.count[o];
-    const float f = (factor ? factor[o] : 1.0f);
     const float sc = a.scale[o];
     auto fix = [&](float v) { return (!finite_f(v) || fabsf(v) > 10000000.0f) ? 0.0f : v * f * sc; };
     const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -286,6 +301,40 @@ tv_grad_apply_kernel(FinalizeArgs a, const float* __restrict__ factor) {
         p4[i] = a0;
     }
     for (i = nvec * 4 + tid; i < cnt; i += nthreads) p[i] = fix(p[i]);
+}
+
+__global__ void __launch_bounds__(256)
+tv_grad_apply_kernel(FinalizeArgs a, const float* __restrict__ factor) {
+    grad_apply_block(a, factor ? factor[blockIdx.y] : 1.0f);
+}
+
+// Statistics, conditioner and scaling in one cooperative launch (grid kStatBlocks x kNumOutputs): the partials of every
+// block, a grid-wide barrier, then every block derives the factor of its output from the same partials in the same order
+// (block 0 of each output also stores the new running mean) and applies it.  The running means are double-buffered:
+// read from state_in, written to state_out, so that no block reads a mean another block has already replaced.
+__global__ void __launch_bounds__(256, 5)          // 640 blocks must be resident together: at least five per SM
+tv_finalize_kernel(FinalizeArgs a, double* __restrict__ partial, const double* __restrict__ state_in,
+                   double* __restrict__ state_out, float* __restrict__ factor, int run, int* __restrict__ sync, int sync_words) {
+    if (blockIdx.x == 0 && blockIdx.y == 0)          // the sweeps are over: the next one finds its progress counters at zero
+        for (int i = threadIdx.x; i < sync_words; i += blockDim.x) sync[i] = 0;
+    grad_stats_block(a, partial);
+    __threadfence();
+    cooperative_groups::this_grid().sync();
+    __shared__ float sh_f;
+    const int o = blockIdx.y;
+    if (threadIdx.x < 32) {
+        double av_new;
+        const float f = conditioner_warp(partial, a, o, state_in[o], run, av_new);
+        if (threadIdx.x == 0) {
+            sh_f = f;
+            if (blockIdx.x == 0) {
+                state_out[o] = av_new;
+                factor[o] = f;
+            }
+        }
+    }
+    __syncthreads();
+    grad_apply_block(a, sh_f);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -330,6 +379,8 @@ struct Slot {
     int n = 0, ch = 0, h = 0, w = 0, its = 0;
     bool have_forward = false;
     int run = 0;
+    int cond_flip = 0;               // which of the two copies of the running means is current
+    bool sync_clean = false;         // the arena's progress counters are known to be zero
     int generation = 0;              // forward passes stored on this slot so far; survives release
     int opt_conditioner = 1;
     int opt_fuse = 0;
@@ -499,10 +550,11 @@ static int ensure_arena(Slot& s, size_t floats) {
     }
     s.arena = static_cast<float*>(p);
     s.arena_floats = floats;
+    s.sync_clean = false;
     return CNL_OK;
 }
 
-constexpr size_t kCondDoubles = kNumOutputs + (size_t)kNumOutputs * kStatBlocks * 2 + 4;   // means, partials, factors
+constexpr size_t kCondDoubles = 2 * kNumOutputs + (size_t)kNumOutputs * kStatBlocks * 2 + 4;   // means (two copies), partials, factors
 
 static int ensure_cond(Slot& s) {
     if (s.cond) return CNL_OK;
@@ -521,6 +573,20 @@ static void fill_flow_tables(const Slot& s, int its_eff, FlowTables& tab) {
     }
     for (size_t i = 0; i < s.sched.size(); ++i)
         if (s.sched[i] < its_eff && s.sched[i] < kFlowMaxIts) tab.ckpt_slot[s.sched[i]] = (signed char)i;
+}
+
+// The fused finalisation is a cooperative launch of kStatBlocks x kNumOutputs blocks: usable where they are all resident.
+static bool finalize_grid_fits() {
+    static int fits[64] = {};          // per device: 0 unknown, 1 yes, -1 no
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (fits[dev] == 0) {
+        int per_sm = 0, sms = 0;
+        const bool ok = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tv_finalize_kernel, 256, 0) == cudaSuccess &&
+                        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess;
+        fits[dev] = (ok && per_sm * sms >= kStatBlocks * kNumOutputs) ? 1 : -1;
+    }
+    return fits[dev] == 1;
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -554,6 +620,9 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
     const bool recompute = fused && (s.opt_recompute || L.total > arena_budget_floats());
     if (recompute) L = slot_layout(n, ch, h, P, its_eff, s.sched, true, staged);
     CNL_TRY(ensure_arena(s, L.total));
+    // a different problem lays the arena out differently: the counters of the single-launch sweeps sit elsewhere
+    if (s.n != n || s.ch != ch || s.h != h || s.w != w || s.its != its || s.pitch != P || s.staged != staged || s.recompute != recompute)
+        s.sync_clean = false;
     s.recompute = recompute;
     s.staged = staged;
     s.pitch = P;
@@ -621,7 +690,9 @@ static int tv_forward_impl(const float* wx, const float* wy, const float* c, con
             fp.its = its_eff;
             fp.N = n; fp.C = ch; fp.H = h; fp.W = w; fp.P = P;
             fill_flow_tables(s, its_eff, fp.tab);
-            CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0, L.sync_words * sizeof(int), st), "zero progress counters"));
+            if (!s.sync_clean || s.opt_flow == 2)
+                CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0, L.sync_words * sizeof(int), st), "zero progress counters"));
+            s.sync_clean = false;
             if (s.opt_flow == 2)      // self-test of the bounded waits: counters that no unit can ever bring up to what its neighbours need
                 CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0x80, (size_t)ntiles * sizeof(int), st), "poison progress counters"));
             if (timing) CNL_TRY(check_cuda(cudaEventRecord(s.ev_fwd[s.n_fwd][0], st), "cudaEventRecord"));
@@ -763,6 +834,7 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     bool timing = s.opt_timing && s.n_rev < Slot::kRing;
     unsigned long long launches0 = g_launches.load();
     if (timing) CNL_TRY(ensure_events(s));
+    bool sync_dirty = false;           // the reverse sweep has used the progress counters
     auto ckpt_of = [&](int g) -> const float* {
         for (size_t i = 0; i < s.sched.size(); ++i)
             if (s.sched[i] == g) return s.arena + L.ckpt + i * L.vol;      // segment start: the checkpointed y_g (:1724-1727)
@@ -806,7 +878,8 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     // seed at the last iteration (its_eff - 1 is odd, so the seed lands in the "odd" buffer like the reference's)
     {
         const int g = its_eff - 1;
-        tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hist_of(g), b, c, gb, g_c, g_b, acc, g_wx, g_wy, ch, plane);
+        tv_rev_seed_kernel<<<pgrid, 256, 0, st>>>(grad_out, hist_of(g), b, c, gb, g_c, g_b, acc, g_wx, g_wy, ch, plane,
+                                                  reinterpret_cast<int*>(s.arena + L.sync), (int)L.sync_words);
         CNL_TRY(after_launch("tv_rev_seed_kernel"));
     }
     if (timing) {          // after the seed: the record covers the iteration kernels
@@ -835,10 +908,10 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
             rp.g_first = its_eff - 2;
             rp.nblocks = nfull;
             rp.N = n; rp.C = ch; rp.H = h; rp.W = w; rp.P = P;
-            fill_flow_tables(s, its_eff, rp.tab);
-            CNL_TRY(check_cuda(cudaMemsetAsync(sync, 0, L.sync_words * sizeof(int), st), "zero progress counters"));
+            fill_flow_tables(s, its_eff, rp.tab);          // (the seed kernel has zeroed the progress counters)
             if (timing) CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][0], st), "cudaEventRecord"));
             CNL_TRY(launch_tv_rev_flow(rp, st));
+            sync_dirty = true;
             if (timing) {          // the record covers the single-launch sweep alone
                 CNL_TRY(check_cuda(cudaEventRecord(s.ev_rev[s.n_rev][1], st), "cudaEventRecord"));
                 s.launches_rev[s.n_rev] = 1;
@@ -917,17 +990,34 @@ static int tv_backward_impl(const float* wx, const float* wy, const float* c, co
     fa.ptr[2] = u_gwy; fa.count[2] = (unsigned long long)n * uplane;      fa.scale[2] = kGlobalG * kLip;
     fa.ptr[3] = u_gb;  fa.count[3] = (unsigned long long)n * ch * uplane; fa.scale[3] = kGlobalG;
     fa.ptr[4] = u_ginit; fa.count[4] = (unsigned long long)n * ch * uplane; fa.scale[4] = 1.0f;
-    double* state = s.cond;
-    double* partial = s.cond + kNumOutputs;
-    float* factor = reinterpret_cast<float*>(s.cond + kNumOutputs + (size_t)kNumOutputs * kStatBlocks * 2);
-    if (s.opt_conditioner) {
-        tv_grad_stats_kernel<<<dim3(kStatBlocks, kNumOutputs), 256, 0, st>>>(fa, partial);
-        CNL_TRY(after_launch("tv_grad_stats_kernel"));
-        tv_conditioner_kernel<<<1, 32 * kNumOutputs, 0, st>>>(partial, fa, state, factor, s.run);
-        CNL_TRY(after_launch("tv_conditioner_kernel"));
+    double* state = s.cond + (size_t)s.cond_flip * kNumOutputs;
+    double* state_next = s.cond + (size_t)(s.cond_flip ^ 1) * kNumOutputs;
+    double* partial = s.cond + 2 * kNumOutputs;
+    float* factor = reinterpret_cast<float*>(s.cond + 2 * kNumOutputs + (size_t)kNumOutputs * kStatBlocks * 2);
+    if (s.opt_conditioner && flow_enabled() && finalize_grid_fits()) {
+        // one cooperative launch: statistics, grid barrier, conditioner, scaling
+        const double* state_in = state;
+        int run = s.run;
+        int* sync = reinterpret_cast<int*>(s.arena + L.sync);        // left at zero for the next forward sweep
+        int sync_words = (int)L.sync_words;
+        void* args[] = {&fa, &partial, &state_in, &state_next, &factor, &run, &sync, &sync_words};
+        CNL_TRY(check_cuda(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(tv_finalize_kernel),
+                                                       dim3(kStatBlocks, kNumOutputs), dim3(256), args, 0, st), "tv_finalize_kernel"));
+        CNL_TRY(after_launch("tv_finalize_kernel"));
+        s.cond_flip ^= 1;
+        s.sync_clean = true;
+        sync_dirty = false;
+    } else {
+        if (s.opt_conditioner) {
+            tv_grad_stats_kernel<<<dim3(kStatBlocks, kNumOutputs), 256, 0, st>>>(fa, partial);
+            CNL_TRY(after_launch("tv_grad_stats_kernel"));
+            tv_conditioner_kernel<<<1, 32 * kNumOutputs, 0, st>>>(partial, fa, state, factor, s.run);
+            CNL_TRY(after_launch("tv_conditioner_kernel"));
+        }
+        tv_grad_apply_kernel<<<dim3(296, kNumOutputs), 256, 0, st>>>(fa, s.opt_conditioner ? factor : nullptr);
+        CNL_TRY(after_launch("tv_grad_apply_kernel"));
     }
-    tv_grad_apply_kernel<<<dim3(296, kNumOutputs), 256, 0, st>>>(fa, s.opt_conditioner ? factor : nullptr);
-    CNL_TRY(after_launch("tv_grad_apply_kernel"));
+    if (sync_dirty) s.sync_clean = false;
     s.run += 1;
     return CNL_OK;
 }

@@ -384,6 +384,49 @@ wmedian_input_grad_kernel(const int* __restrict__ tap, const float* __restrict__
     g_flow[idx] = s;
 }
 
+// The same sum from a shared-memory tile: a block of 32 x 8 pixels first resolves, for every window centre of its tile
+// and halo, which pixel that window selected (one division per centre instead of one per centre and neighbour), then
+// every pixel scans the K centres around it in the order of the kernel above, so the two give the same bits.
+template <int KS>
+__global__ void __launch_bounds__(256)
+wmedian_input_grad_tiled_kernel(const int* __restrict__ tap, const float* __restrict__ grad, float* __restrict__ g_flow,
+                                int H, int W) {
+    constexpr int R = KS / 2, BW = 32, BH = 8, TW = BW + 2 * R, TH = BH + 2 * R;
+    __shared__ int s_target[TH][TW];          // linear index of the pixel the window centred here selected, -1 outside the image
+    __shared__ float s_grad[TH][TW];
+    const size_t plane = (size_t)H * W;
+    const int* tp = tap + (size_t)blockIdx.z * plane;
+    const float* gp = grad + (size_t)blockIdx.z * plane;
+    const int h0 = blockIdx.y * BH - R, w0 = blockIdx.x * BW - R;
+    for (int i = threadIdx.x; i < TH * TW; i += 256) {
+        const int r = i / TW, c = i - r * TW;
+        const int ph = h0 + r, pw = w0 + c;
+        int target = -1;
+        float g = 0.0f;
+        if (ph >= 0 && ph < H && pw >= 0 && pw < W) {
+            int t = __ldg(tp + (size_t)ph * W + pw);
+            if (t < 0) t = (KS * KS - 1) / 2;                       // no crossing: the centre passed through
+            const int th = min(max(ph + t / KS - R, 0), H - 1), tw = min(max(pw + t % KS - R, 0), W - 1);
+            target = th * W + tw;
+            g = __ldg(gp + (size_t)ph * W + pw);
+        }
+        s_target[r][c] = target;
+        s_grad[r][c] = g;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & (BW - 1), ty = threadIdx.x / BW;
+    const int qh = blockIdx.y * BH + ty, qw = blockIdx.x * BW + tx;
+    if (qh >= H || qw >= W) return;
+    const int me = qh * W + qw;
+    float s = 0.0f;
+#pragma unroll
+    for (int dy = 0; dy < KS; ++dy)
+#pragma unroll
+        for (int dx = 0; dx < KS; ++dx)
+            if (s_target[ty + dy][tx + dx] == me) s += s_grad[ty + dy][tx + dx];
+    g_flow[(size_t)blockIdx.z * plane + me] = s;
+}
+
 constexpr int kGradBlocks = 592;
 
 // CNL_WMEDIAN_NO_SLIDE=1 selects the one-thread-per-pixel forward kernel (read at every call)
@@ -432,6 +475,12 @@ static int run_backward(const float* flow, const float* wts, const int* tap, con
     }
     wmedian_weight_grad_final_kernel<<<1, 64, 0, st>>>(scratch, blocks, K, g_p);
     CNL_TRY(after_launch("wmedian_weight_grad_final_kernel"));
+    const long long images = total / ((long long)H * W);
+    if (images <= 65535) {
+        const dim3 grid((W + 31) / 32, (H + 7) / 8, (unsigned)images);
+        wmedian_input_grad_tiled_kernel<KS><<<grid, 256, 0, st>>>(tap, grad, g_flow, H, W);
+        return after_launch("wmedian_input_grad_tiled_kernel");
+    }
     wmedian_input_grad_kernel<KS><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(tap, grad, g_flow, total, H, W);
     return after_launch("wmedian_input_grad_kernel");
 }
