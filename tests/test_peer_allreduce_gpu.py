@@ -92,3 +92,57 @@ def test_argument_checks():
     assert lib.cnl_peer_allreduce_sum(v.data_ptr(), 1, ptrs, 1, 1, 1, None) == 2      # rank outside the world
     assert lib.cnl_peer_allreduce_sum(v.data_ptr(), 1, ptrs, 0, 1, 0, None) == 2      # call numbers start at 1
     assert lib.cnl_peer_allreduce_sum(None, 1, ptrs, 0, 1, 1, None) == 7
+
+
+def _two_rank_worker(rank, world, port, q):
+    import os
+    import sys
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import datetime
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
+    from customnetworklayers_b200 import tvInpaint_cuda_ext as ext
+    from customnetworklayers_b200.dist import PeerAllReduce
+    peer = PeerAllReduce()
+    gen = torch.Generator().manual_seed(100 + rank)
+    ok = True
+    for it in range(5):
+        v = torch.randn(49, generator=gen).cuda()
+        ref = v.clone()
+        dist.all_reduce(ref)                                  # NCCL as the reference sum
+        peer.sum_(v)
+        ok = ok and bool(torch.allclose(v, ref, rtol=1e-6, atol=1e-6))
+        g = torch.randn(100000, generator=gen).cuda()
+        c = torch.rand(100000, generator=gen).cuda()
+        ref1 = ext.lambda_grad(g, c)
+        dist.all_reduce(ref1)
+        out = peer.lambda_grad(g, c)
+        ok = ok and bool(torch.allclose(out, ref1, rtol=1e-6, atol=1e-5))
+    torch.cuda.synchronize()
+    q.put((rank, ok, peer.status()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs of one node")
+def test_two_real_ranks_agree_with_nccl():
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert res == [(0, True, 0), (1, True, 0)]
