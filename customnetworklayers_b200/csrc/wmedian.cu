@@ -115,25 +115,64 @@ wmedian_forward_kernel(const float* __restrict__ flow, const float* __restrict__
     }
 }
 
-// Sliding-window variant of the forward kernel.  A thread walks along kRun consecutive pixels of one image row and
-// keeps the window values AND their ranks in registers: moving one pixel to the right removes the left column
-// (every kept rank drops by the number of removed taps below it), shifts the columns, and inserts the new right
-// column (one compare per (kept, new) pair decides both ranks), i.e. about K*2*KS compares per pixel instead of
-// K*(K-1).  The stable order breaks ties by window index (row-major), which is invariant under the shift; a new tap
-// sits in the last column, so it precedes an equal kept tap exactly when its window row is smaller.  Lanes of a
-// warp take consecutive image rows, so the column loads of neighbouring lanes share cache lines.
-constexpr int kRun = 32;
+// Sliding-window variant of the forward kernel.  A thread walks along a run of consecutive pixels of one image row and
+// keeps, per window tap, its value and ONE packed word: bits 0-5 the tap's rank in the stable ascending order of the
+// window, then one 3-bit field per older window column holding how many taps of that column precede it.  Moving one
+// pixel to the right
+//   * removes the left column: a kept tap's rank drops by its field for that column, and its fields move down one place
+//     (five integer instructions per tap, no compares: the counts were found when the tap entered the window);
+//   * inserts the new right column: one float compare per (kept, new) pair decides which of the two precedes the other
+//     and adds either 1 to the kept tap's rank or (1 + one count in the kept tap's column field) to the new tap's word.
+// The stable order breaks ties by window index (row-major), which is invariant under the shift; a new tap sits in the
+// last column, so it precedes an equal kept tap exactly when its window row is smaller.  A run starts from a window of
+// equal sentinel values, whose ranks and counts are compile-time constants, and slides the k real columns in before the
+// first output: the start-up shares the code of the steady state, which keeps the unrolled body inside the instruction
+// caches.  Lanes of a warp take consecutive image rows, so the column loads of neighbouring lanes share cache lines.
+constexpr int kRun = 32;                  // pixels per thread of the weight-gradient walk
+constexpr int kRkBits = 6, kCntBits = 3;
+constexpr unsigned kRkMask = (1u << kRkBits) - 1u;
+
+struct WeightTap {        // staged per block: the normalised weight of a tap and the tap's window index
+    float p;
+    int index;
+};
+
+template <int K>
+__device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restrict__ sw, int& index) {
+    Crossing c;
+    c.rank = -1; c.pmid = 1.0f; c.alpha = 0.0f;
+    index = -1;
+    float score = 0.0f;
+    for (int r = 0; r < K; ++r) {
+        const float p = sw[r * NT].p;
+        const float nxt = score + p;
+        if (score < 0.5f && nxt >= 0.5f) {                       // medimax.cu:30
+            c.rank = r;
+            c.pmid = p;
+            c.alpha = (float)((1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p));     // :33
+            index = sw[r * NT].index;
+            break;
+        }
+        score = nxt;
+    }
+    return c;
+}
 
 template <int KS>
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NT, 3)
 wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __restrict__ weights, float* __restrict__ out,
-                             int* __restrict__ tap, float* __restrict__ alpha, long long nthreads, int H, int W, int runs) {
+                             int* __restrict__ tap, float* __restrict__ alpha, long long nthreads, int H, int W, int runs,
+                             int run_len) {
     constexpr int K = KS * KS, R = KS / 2;
+    static_assert(K <= (1 << kRkBits) && KS < (1 << kCntBits) && kRkBits + kCntBits * (KS - 1) <= 32, "packed word too small");
     extern __shared__ unsigned char smem_raw[];
-    __shared__ float sp[K];
-    stage_weights<K>(weights, sp);
-    float* sw = reinterpret_cast<float*>(smem_raw) + threadIdx.x;                      // sw[r * NT]
-    unsigned char* sidx = smem_raw + (size_t)K * NT * sizeof(float) + threadIdx.x;     // sidx[r * NT]
+    __shared__ WeightTap sp[K];
+    if (threadIdx.x < K) {
+        sp[threadIdx.x].p = weights[threadIdx.x];
+        sp[threadIdx.x].index = threadIdx.x;
+    }
+    __syncthreads();
+    WeightTap* sw = reinterpret_cast<WeightTap*>(smem_raw) + threadIdx.x;             // sw[r * NT]
     const long long plane = (long long)H * W;
     for (long long tix = (long long)blockIdx.x * NT + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * NT) {
         const int h = (int)(tix % H);
@@ -141,64 +180,62 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
         const int run = (int)(q % runs);
         const long long img = q / runs;
         const float* src = flow + img * plane;
-        const int w0 = run * kRun;
+        const int w0 = run * run_len;
+        const int len = min(run_len, W - w0);
         int rowoff[KS];
 #pragma unroll
         for (int dy = 0; dy < KS; ++dy) rowoff[dy] = min(max(h + dy - R, 0), H - 1) * W;
+        // the sentinel window: equal values, so a tap is preceded by the taps of smaller window index
         float v[K];
-        int rk[K];
+        unsigned wd[K];
 #pragma unroll
         for (int dy = 0; dy < KS; ++dy)
 #pragma unroll
-            for (int dx = 0; dx < KS; ++dx) v[dy * KS + dx] = __ldg(src + rowoff[dy] + min(max(w0 + dx - R, 0), W - 1));
+            for (int dx = 0; dx < KS; ++dx) {
+                unsigned word = (unsigned)(dy * KS + dx);
 #pragma unroll
-        for (int i = 0; i < K; ++i) rk[i] = rank_of<K>(v, i, v[i]);
-        float nxt[KS];                                       // right column of the next pixel's window
-#pragma unroll
-        for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + min(w0 + 1 + R, W - 1));
-        const int wend = min(w0 + kRun, W);
-        for (int w = w0; w < wend; ++w) {
-#pragma unroll
-            for (int i = 0; i < K; ++i) {
-                sw[rk[i] * NT] = sp[i];
-                sidx[rk[i] * NT] = (unsigned char)i;
+                for (int a = 0; a < dx; ++a) word |= (unsigned)(dy + 1) << (kRkBits + kCntBits * a);
+                v[dy * KS + dx] = 0.0f;
+                wd[dy * KS + dx] = word;
             }
-            const Crossing c = scan_sorted<K>(sw);
-            int t = -1;
-            float o = v[K / 2];                                  // no crossing: the centre value passes through
-            if (c.rank >= 0) {
-                t = sidx[c.rank * NT];
-                const int dy = t / KS, dx = t % KS - R;
-                o = __ldg(src + rowoff[dy] + min(max(w + dx, 0), W - 1));
-            }
-            const long long idx = img * plane + (long long)h * W + w;
-            out[idx] = o;
-            if (tap) tap[idx] = t;
-            if (alpha) alpha[idx] = c.alpha;
-            if (w + 1 >= wend) break;
-            // --- slide the window one pixel to the right ---
-            // 1. remove column 0: a kept tap loses one rank for every removed tap that was below it
+        float nxt[KS];                                       // the column that enters with the next slide
 #pragma unroll
-            for (int dy = 0; dy < KS; ++dy)
+        for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + max(w0 - R, 0));
+        const long long base = img * plane + (long long)h * W;
+        // step s: the window is centred on pixel w0 - KS + s; the first KS steps only slide the real columns in
+#pragma unroll 1
+        for (int s = 0; s < KS + len; ++s) {
+            const int w = w0 - KS + s;
+            if (s >= KS) {
 #pragma unroll
-                for (int dx = 1; dx < KS; ++dx) {
-                    int drop = 0;
-#pragma unroll
-                    for (int ry = 0; ry < KS; ++ry) drop += (rk[ry * KS] < rk[dy * KS + dx]) ? 1 : 0;
-                    rk[dy * KS + dx] -= drop;
+                for (int i = 0; i < K; ++i) sw[(wd[i] & kRkMask) * NT] = sp[i];
+                int t;
+                const Crossing c = scan_sorted_pairs<K>(sw, t);
+                float o = v[K / 2];                              // no crossing: the centre value passes through
+                if (t >= 0) {
+                    const int dy = t / KS - R, dx = t % KS - R;
+                    o = __ldg(src + min(max(h + dy, 0), H - 1) * W + min(max(w + dx, 0), W - 1));
                 }
-            // 2. shift the columns
+                out[base + w] = o;
+                if (tap) tap[base + w] = t;
+                if (alpha) alpha[base + w] = c.alpha;
+                if (s + 1 >= KS + len) break;
+            }
+            // --- slide the window one pixel to the right ---
+            // 1. the left column leaves, the others move one place to the left
 #pragma unroll
             for (int dy = 0; dy < KS; ++dy)
 #pragma unroll
                 for (int dx = 0; dx + 1 < KS; ++dx) {
+                    const unsigned old = wd[dy * KS + dx + 1];
+                    const unsigned below = (old >> kRkBits) & ((1u << kCntBits) - 1u);   // taps of the leaving column below it
+                    wd[dy * KS + dx] = ((old >> kCntBits) & ~kRkMask) | ((old - below) & kRkMask);
                     v[dy * KS + dx] = v[dy * KS + dx + 1];
-                    rk[dy * KS + dx] = rk[dy * KS + dx + 1];
                 }
-            // 3. insert the new right column
-            int rnew[KS];
+            // 2. the new right column enters
+            unsigned wnew[KS];
 #pragma unroll
-            for (int ny = 0; ny < KS; ++ny) rnew[ny] = 0;
+            for (int ny = 0; ny < KS; ++ny) wnew[ny] = 0u;
 #pragma unroll
             for (int ny = 0; ny < KS; ++ny) {
                 const float x = nxt[ny];
@@ -208,23 +245,23 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
                     for (int dx = 0; dx + 1 < KS; ++dx) {
                         // kept tap first: smaller value, or equal value and not a later window row
                         const bool kept_first = (dy <= ny) ? (v[dy * KS + dx] <= x) : (v[dy * KS + dx] < x);
-                        rnew[ny] += kept_first ? 1 : 0;
-                        rk[dy * KS + dx] += kept_first ? 0 : 1;
+                        if (kept_first) wnew[ny] += (1u << (kRkBits + kCntBits * dx)) + 1u;
+                        else wd[dy * KS + dx] += 1u;
                     }
 #pragma unroll
                 for (int my = 0; my < ny; ++my) {               // among the new taps the smaller row wins ties
-                    const bool other_first = nxt[my] <= x;
-                    rnew[ny] += other_first ? 1 : 0;
-                    rnew[my] += other_first ? 0 : 1;
+                    if (nxt[my] <= x) wnew[ny] += 1u;
+                    else wnew[my] += 1u;
                 }
             }
 #pragma unroll
             for (int ny = 0; ny < KS; ++ny) {
                 v[ny * KS + KS - 1] = nxt[ny];
-                rk[ny * KS + KS - 1] = rnew[ny];
+                wd[ny * KS + KS - 1] = wnew[ny];
             }
+            const int col = min(max(w + 2 + R, 0), W - 1);
 #pragma unroll
-            for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + min(w + 2 + R, W - 1));
+            for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + col);
         }
     }
 }
@@ -277,7 +314,11 @@ wmedian_weight_grad_kernel(const float* __restrict__ flow, const float* __restri
 }
 
 // Sliding-window variant of the weight-gradient kernel: a thread walks along kRun pixels of a row, keeps the window
-// in registers (one new column per pixel instead of K loads) and its per-tap sums in registers too.
+// in registers (one new column per pixel instead of K loads) and its per-tap sums in registers too.  Every tap is
+// first counted as lying before (-half) or after (+half) the selected one, the selected tap itself as "after"; the
+// difference (mid - half) owed to the selected tap goes to a thread-private column of shared memory, because the tap
+// index is only known at run time.  The selected tap's value is read back from the image (the forward pass put
+// exactly that value out) instead of being picked from the registers with K compares.
 template <int KS>
 __global__ void __launch_bounds__(NT, 3)
 wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __restrict__ weights, const int* __restrict__ tap,
@@ -287,10 +328,14 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
     extern __shared__ unsigned char smem_raw[];
     __shared__ float sp[K];
     stage_weights<K>(weights, sp);
+    float* sacc = reinterpret_cast<float*>(smem_raw) + threadIdx.x;            // sacc[i * NT]
     const long long plane = (long long)H * W;
     float acc[K];
 #pragma unroll
-    for (int i = 0; i < K; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < K; ++i) {
+        acc[i] = 0.0f;
+        sacc[i * NT] = 0.0f;
+    }
     for (long long tix = (long long)blockIdx.x * NT + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * NT) {
         const int h = (int)(tix % H);
         const long long q = tix / H;
@@ -308,27 +353,43 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
             for (int dx = 0; dx < KS; ++dx) v[dy * KS + dx] = __ldg(src + rowoff[dy] + min(max(w0 + dx - R, 0), W - 1));
         const int wend = min(w0 + kRun, W);
         const long long base = img * plane + (long long)h * W;
-        // per-pixel operands are fetched one pixel ahead so that no load latency sits between two pixels
+        // value of the tap that the window centred on (h, w) selected; the centre when there was no crossing
+        auto selected_value = [&](int t, int w) {
+            const int tt = t < 0 ? K / 2 : t;
+            return __ldg(src + min(max(h + tt / KS - R, 0), H - 1) * W + min(max(w + tt % KS - R, 0), W - 1));
+        };
+        // per-pixel operands are fetched ahead (the tap two pixels, the rest one) so that no load latency sits between two pixels
         int t_n = tap[base + w0];
-        float g_n = grad[base + w0], a_n = alpha[base + w0];
+        int t_nn = w0 + 1 < wend ? tap[base + w0 + 1] : -1;
+        float g_n = grad[base + w0], a_n = alpha[base + w0], vs_n = selected_value(t_n, w0);
+#pragma unroll 1
         for (int w = w0; w < wend; ++w) {
             const int t = t_n;
-            const float g0 = g_n, al = a_n;
+            const float g0 = g_n, al = a_n, vsel = vs_n;
             float nxt[KS];                                   // right column of the next pixel's window
 #pragma unroll
             for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + min(w + 1 + R, W - 1));
-            if (w + 1 < wend) { t_n = tap[base + w + 1]; g_n = grad[base + w + 1]; a_n = alpha[base + w + 1]; }
-            const float pmid = t >= 0 ? sp[t] : 1.0f;
-            const float half = (float)((double)g0 / (2.0 * (double)pmid));
-            const float mid = __fdiv_rn(__fmul_rn(g0, al), -pmid);
-            float vsel = 0.0f;
+            if (w + 1 < wend) {
+                t_n = t_nn;
+                g_n = grad[base + w + 1];
+                a_n = alpha[base + w + 1];
+                vs_n = selected_value(t_n, w + 1);
+                if (w + 2 < wend) t_nn = tap[base + w + 2];
+            }
+            if (t >= 0) {
+                const float pmid = sp[t];
+                const float half = (float)((double)g0 / (2.0 * (double)pmid));
+                const float mid = __fdiv_rn(__fmul_rn(g0, al), -pmid);
+                sacc[t * NT] += mid - half;
 #pragma unroll
-            for (int i = 0; i < K; ++i) vsel = (i == t) ? v[i] : vsel;
+                for (int i = 0; i < K; ++i) {
+                    const bool before = v[i] < vsel || (v[i] == vsel && i < t);
+                    acc[i] += before ? -half : half;
+                }
+            } else {                                         // no crossing: every bin counts as "before" (weight 1)
+                const float half = (float)((double)g0 / 2.0);
 #pragma unroll
-            for (int i = 0; i < K; ++i) {
-                // no crossing (t < 0): every bin counts as "before"
-                const bool before = t < 0 || v[i] < vsel || (v[i] == vsel && i < t);
-                acc[i] += before ? -half : ((i == t) ? mid : half);
+                for (int i = 0; i < K; ++i) acc[i] -= half;
             }
 #pragma unroll
             for (int dy = 0; dy < KS; ++dy) {
@@ -338,9 +399,8 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
             }
         }
     }
-    float* sacc = reinterpret_cast<float*>(smem_raw) + threadIdx.x;            // sacc[i * NT]
 #pragma unroll
-    for (int i = 0; i < K; ++i) sacc[i * NT] = acc[i];
+    for (int i = 0; i < K; ++i) sacc[i * NT] += acc[i];
     __syncthreads();
     if (threadIdx.x < K) {
         const float* row = reinterpret_cast<float*>(smem_raw) + (size_t)threadIdx.x * NT;
@@ -442,11 +502,17 @@ static int run_forward(const float* flow, const float* wts, float* out, int* tap
     const int smem = K * NT * (int)sizeof(float) + K * NT;
     CNL_TRY(ensure_dynamic_smem(wmedian_forward_kernel<KS>, smem));
     if (slide_enabled()) {
-        CNL_TRY(ensure_dynamic_smem(wmedian_forward_slide_kernel<KS>, smem));
-        const int runs = (W + kRun - 1) / kRun;
-        const long long nthreads = total / W * runs;                 // one thread per (image-channel, row, run)
+        const int smem_slide = K * NT * (int)sizeof(WeightTap);
+        CNL_TRY(ensure_dynamic_smem(wmedian_forward_slide_kernel<KS>, smem_slide));
+        // Long runs amortise the KS start-up slides; short ones keep every SM busy on small inputs.
+        const long long rows = total / W, resident = 148LL * 3;
+        int run_len = 16;
+        if ((rows * ((W + 63) / 64) + NT - 1) / NT >= 4 * resident) run_len = 64;
+        else if ((rows * ((W + 31) / 32) + NT - 1) / NT >= resident) run_len = 32;
+        const int runs = (W + run_len - 1) / run_len;
+        const long long nthreads = rows * runs;                      // one thread per (image-channel, row, run)
         const unsigned sblocks = (unsigned)std::min<long long>((nthreads + NT - 1) / NT, 148LL * 64);
-        wmedian_forward_slide_kernel<KS><<<sblocks, NT, smem, st>>>(flow, wts, out, tap, alpha, nthreads, H, W, runs);
+        wmedian_forward_slide_kernel<KS><<<sblocks, NT, smem_slide, st>>>(flow, wts, out, tap, alpha, nthreads, H, W, runs, run_len);
         return after_launch("wmedian_forward_slide_kernel");
     }
     const unsigned blocks = (unsigned)std::min<long long>((total + NT - 1) / NT, 148LL * 64);
@@ -465,7 +531,16 @@ static int run_backward(const float* flow, const float* wts, const int* tap, con
         CNL_TRY(ensure_dynamic_smem(wmedian_weight_grad_slide_kernel<KS>, smem));
         const int runs = (W + kRun - 1) / kRun;
         const long long nthreads = total / W * runs;
-        blocks = (int)std::min<long long>((nthreads + NT - 1) / NT, kGradBlocks);
+        // every block walks the same number of runs, so the grid is what one wave of the device holds
+        static int wave = 0;                                // the GPUs of one process are alike
+        if (wave == 0) {
+            int per_sm = 0, dev = 0, sms = 0;
+            CNL_TRY(check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, wmedian_weight_grad_slide_kernel<KS>, NT, smem), "occupancy of the weight-gradient kernel"));
+            CNL_TRY(check_cuda(cudaGetDevice(&dev), "cudaGetDevice"));
+            CNL_TRY(check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "SM count"));
+            wave = std::max(1, per_sm * sms);
+        }
+        blocks = (int)std::min<long long>((nthreads + NT - 1) / NT, std::min(kGradBlocks, wave));
         wmedian_weight_grad_slide_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, tap, alpha, grad, scratch, nthreads, H, W, runs);
         CNL_TRY(after_launch("wmedian_weight_grad_slide_kernel"));
     } else {

@@ -68,6 +68,31 @@ def test_cuda_matches_oracle(case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("case", [(1, 1, 20, 45, 3), (1, 2, 33, 130, 5), (2, 1, 70, 300, 7), (4, 2, 384, 1270, 7), (16, 2, 384, 1270, 7)],
+                         ids=lambda c: "n%d_c%d_%dx%d_k%d" % c)
+def test_sliding_kernels_give_the_bits_of_the_per_pixel_kernels(case, monkeypatch):
+    """The sliding-window kernels (runs of 16, 32 or 64 pixels per thread, chosen by the size of the input; the widths
+    here leave a ragged last run) against the one-thread-per-pixel kernels, which the small cases pin to the oracle."""
+    from customnetworklayers_b200 import wmedian as wm
+    n, c, h, w, k = case
+    flow, wts, grad = make_median_filter_inputs(n, c, h, w, k=k, seed=77 + k)
+    flow[0, 0, h // 2, 5:40] = 0.5                 # ties entering and leaving the window
+    flow[0, 0, :, w - 3] = flow[0, 0, :, w - 2]
+    flow, grad = flow.cuda(), grad.cuda()
+    p = (wts / wts.sum()).float().cuda()
+    res = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("CNL_WMEDIAN_NO_SLIDE", mode)
+        out, tap, alpha = wm.forward(flow, p, k)
+        g_flow, g_p = wm.backward(flow, p, tap, alpha, grad, k)
+        torch.cuda.synchronize()
+        res[mode] = (out, tap, alpha, g_flow, g_p)
+    for name, a, b in zip(("out", "tap", "alpha", "g_flow"), res["0"], res["1"]):
+        assert torch.equal(a, b), name
+    assert_close(res["0"][4], res["1"][4], "g_weights")
+
+
+@pytest.mark.gpu
 def test_filter_module_learns_through_normalisation():
     from customnetworklayers_b200.wmedian import WeightedMedianFilter
     flow, wts, grad = make_median_filter_inputs(2, 2, 24, 32, seed=5)
