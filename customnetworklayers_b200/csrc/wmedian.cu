@@ -313,8 +313,9 @@ wmedian_weight_grad_kernel(const float* __restrict__ flow, const float* __restri
     }
 }
 
-// Sliding-window variant of the weight-gradient kernel: a thread walks along kRun pixels of a row, keeps the window
-// in registers (one new column per pixel instead of K loads) and its per-tap sums in registers too.  Every tap is
+// Sliding-window variant of the weight-gradient kernel: a thread walks DOWN kRun pixels of an image column and keeps
+// the window in registers (one new window row per pixel instead of K loads) and its per-tap sums in registers too; the
+// lanes of a warp take consecutive columns, so every load is coalesced.  Every tap is
 // first counted as lying before (-half) or after (+half) the selected one, the selected tap itself as "after"; the
 // difference (mid - half) owed to the selected tap goes to a thread-private column of shared memory, because the tap
 // index is only known at run time.  The selected tap's value is read back from the image (the forward pass put
@@ -337,44 +338,50 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
         sacc[i * NT] = 0.0f;
     }
     for (long long tix = (long long)blockIdx.x * NT + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * NT) {
-        const int h = (int)(tix % H);
-        const long long q = tix / H;
+        const int w = (int)(tix % W);
+        const long long q = tix / W;
         const int run = (int)(q % runs);
         const long long img = q / runs;
         const float* src = flow + img * plane;
-        const int w0 = run * kRun;
-        int rowoff[KS];
+        const int h0 = run * kRun;
+        int coloff[KS];
 #pragma unroll
-        for (int dy = 0; dy < KS; ++dy) rowoff[dy] = min(max(h + dy - R, 0), H - 1) * W;
+        for (int dx = 0; dx < KS; ++dx) coloff[dx] = min(max(w + dx - R, 0), W - 1);
         float v[K];
 #pragma unroll
-        for (int dy = 0; dy < KS; ++dy)
+        for (int dy = 0; dy < KS; ++dy) {
+            const float* row = src + min(max(h0 + dy - R, 0), H - 1) * W;
 #pragma unroll
-            for (int dx = 0; dx < KS; ++dx) v[dy * KS + dx] = __ldg(src + rowoff[dy] + min(max(w0 + dx - R, 0), W - 1));
-        const int wend = min(w0 + kRun, W);
-        const long long base = img * plane + (long long)h * W;
+            for (int dx = 0; dx < KS; ++dx) v[dy * KS + dx] = __ldg(row + coloff[dx]);
+        }
+        const int hend = min(h0 + kRun, H);
+        const long long base = img * plane + w;
         // value of the tap that the window centred on (h, w) selected; the centre when there was no crossing
-        auto selected_value = [&](int t, int w) {
+        auto selected_value = [&](int t, int h) {
             const int tt = t < 0 ? K / 2 : t;
             return __ldg(src + min(max(h + tt / KS - R, 0), H - 1) * W + min(max(w + tt % KS - R, 0), W - 1));
         };
         // per-pixel operands are fetched ahead (the tap two pixels, the rest one) so that no load latency sits between two pixels
-        int t_n = tap[base + w0];
-        int t_nn = w0 + 1 < wend ? tap[base + w0 + 1] : -1;
-        float g_n = grad[base + w0], a_n = alpha[base + w0], vs_n = selected_value(t_n, w0);
+        int t_n = tap[base + (long long)h0 * W];
+        int t_nn = h0 + 1 < hend ? tap[base + (long long)(h0 + 1) * W] : -1;
+        float g_n = grad[base + (long long)h0 * W], a_n = alpha[base + (long long)h0 * W], vs_n = selected_value(t_n, h0);
 #pragma unroll 1
-        for (int w = w0; w < wend; ++w) {
+        for (int h = h0; h < hend; ++h) {
             const int t = t_n;
             const float g0 = g_n, al = a_n, vsel = vs_n;
-            float nxt[KS];                                   // right column of the next pixel's window
+            float nxt[KS];                                   // bottom row of the next pixel's window
+            {
+                const float* row = src + min(h + 1 + R, H - 1) * W;
 #pragma unroll
-            for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + min(w + 1 + R, W - 1));
-            if (w + 1 < wend) {
+                for (int dx = 0; dx < KS; ++dx) nxt[dx] = __ldg(row + coloff[dx]);
+            }
+            if (h + 1 < hend) {
+                const long long at = base + (long long)(h + 1) * W;
                 t_n = t_nn;
-                g_n = grad[base + w + 1];
-                a_n = alpha[base + w + 1];
-                vs_n = selected_value(t_n, w + 1);
-                if (w + 2 < wend) t_nn = tap[base + w + 2];
+                g_n = grad[at];
+                a_n = alpha[at];
+                vs_n = selected_value(t_n, h + 1);
+                if (h + 2 < hend) t_nn = tap[at + W];
             }
             if (t >= 0) {
                 const float pmid = sp[t];
@@ -392,10 +399,10 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
                 for (int i = 0; i < K; ++i) acc[i] -= half;
             }
 #pragma unroll
-            for (int dy = 0; dy < KS; ++dy) {
+            for (int dx = 0; dx < KS; ++dx) {
 #pragma unroll
-                for (int dx = 0; dx + 1 < KS; ++dx) v[dy * KS + dx] = v[dy * KS + dx + 1];
-                v[dy * KS + KS - 1] = nxt[dy];
+                for (int dy = 0; dy + 1 < KS; ++dy) v[dy * KS + dx] = v[(dy + 1) * KS + dx];
+                v[(KS - 1) * KS + dx] = nxt[dx];
             }
         }
     }
@@ -529,8 +536,8 @@ static int run_backward(const float* flow, const float* wts, const int* tap, con
     int blocks;
     if (slide_enabled()) {
         CNL_TRY(ensure_dynamic_smem(wmedian_weight_grad_slide_kernel<KS>, smem));
-        const int runs = (W + kRun - 1) / kRun;
-        const long long nthreads = total / W * runs;
+        const int runs = (H + kRun - 1) / kRun;
+        const long long nthreads = total / H * runs;                 // one thread per (image-channel, column, run of rows)
         // every block walks the same number of runs, so the grid is what one wave of the device holds
         static int wave = 0;                                // the GPUs of one process are alike
         if (wave == 0) {
