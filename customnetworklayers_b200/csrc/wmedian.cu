@@ -115,19 +115,19 @@ wmedian_forward_kernel(const float* __restrict__ flow, const float* __restrict__
     }
 }
 
-// Sliding-window variant of the forward kernel.  A thread walks along a run of consecutive pixels of one image row and
-// keeps, per window tap, its value and ONE packed word: bits 0-5 the tap's rank in the stable ascending order of the
-// window, then one 3-bit field per older window column holding how many taps of that column precede it.  Moving one
-// pixel to the right
-//   * removes the left column: a kept tap's rank drops by its field for that column, and its fields move down one place
+// Sliding-window variant of the forward kernel.  A thread walks DOWN a run of consecutive pixels of one image column
+// (the lanes of a warp take consecutive columns, so every load and store is coalesced) and keeps, per window tap, its
+// value and ONE packed word: bits 0-5 the tap's rank in the stable ascending order of the window, then one 3-bit field
+// per older window row holding how many taps of that row precede it.  Moving one pixel down
+//   * removes the top row: a kept tap's rank drops by its field for that row, and its fields move down one place
 //     (five integer instructions per tap, no compares: the counts were found when the tap entered the window);
-//   * inserts the new right column: one float compare per (kept, new) pair decides which of the two precedes the other
-//     and adds either 1 to the kept tap's rank or (1 + one count in the kept tap's column field) to the new tap's word.
+//   * inserts the new bottom row: one float compare per (kept, new) pair decides which of the two precedes the other
+//     and adds either 1 to the kept tap's rank or (1 + one count in the kept tap's row field) to the new tap's word.
 // The stable order breaks ties by window index (row-major), which is invariant under the shift; a new tap sits in the
-// last column, so it precedes an equal kept tap exactly when its window row is smaller.  A run starts from a window of
-// equal sentinel values, whose ranks and counts are compile-time constants, and slides the k real columns in before the
-// first output: the start-up shares the code of the steady state, which keeps the unrolled body inside the instruction
-// caches.  Lanes of a warp take consecutive image rows, so the column loads of neighbouring lanes share cache lines.
+// last row, so an equal kept tap always precedes it, and among equal new taps the left one comes first.  A run starts
+// from a window of equal sentinel values, whose ranks and counts are compile-time constants, and slides the k real rows
+// in before the first output: the start-up shares the code of the steady state, which keeps the unrolled body inside
+// the instruction caches.
 constexpr int kRun = 32;                  // pixels per thread of the weight-gradient walk
 constexpr int kRkBits = 6, kCntBits = 3;
 constexpr unsigned kRkMask = (1u << kRkBits) - 1u;
@@ -175,16 +175,16 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
     WeightTap* sw = reinterpret_cast<WeightTap*>(smem_raw) + threadIdx.x;             // sw[r * NT]
     const long long plane = (long long)H * W;
     for (long long tix = (long long)blockIdx.x * NT + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * NT) {
-        const int h = (int)(tix % H);
-        const long long q = tix / H;
+        const int w = (int)(tix % W);
+        const long long q = tix / W;
         const int run = (int)(q % runs);
         const long long img = q / runs;
         const float* src = flow + img * plane;
-        const int w0 = run * run_len;
-        const int len = min(run_len, W - w0);
-        int rowoff[KS];
+        const int h0 = run * run_len;
+        const int len = min(run_len, H - h0);
+        int coloff[KS];
 #pragma unroll
-        for (int dy = 0; dy < KS; ++dy) rowoff[dy] = min(max(h + dy - R, 0), H - 1) * W;
+        for (int dx = 0; dx < KS; ++dx) coloff[dx] = min(max(w + dx - R, 0), W - 1);
         // the sentinel window: equal values, so a tap is preceded by the taps of smaller window index
         float v[K];
         unsigned wd[K];
@@ -194,18 +194,21 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
             for (int dx = 0; dx < KS; ++dx) {
                 unsigned word = (unsigned)(dy * KS + dx);
 #pragma unroll
-                for (int a = 0; a < dx; ++a) word |= (unsigned)(dy + 1) << (kRkBits + kCntBits * a);
+                for (int a = 0; a < dy; ++a) word |= (unsigned)KS << (kRkBits + kCntBits * a);
                 v[dy * KS + dx] = 0.0f;
                 wd[dy * KS + dx] = word;
             }
-        float nxt[KS];                                       // the column that enters with the next slide
+        float nxt[KS];                                       // the row that enters with the next slide
+        {
+            const float* row = src + max(h0 - R, 0) * W;
 #pragma unroll
-        for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + max(w0 - R, 0));
-        const long long base = img * plane + (long long)h * W;
-        // step s: the window is centred on pixel w0 - KS + s; the first KS steps only slide the real columns in
+            for (int dx = 0; dx < KS; ++dx) nxt[dx] = __ldg(row + coloff[dx]);
+        }
+        const long long base = img * plane + w;
+        // step s: the window is centred on row h0 - KS + s; the first KS steps only slide the real rows in
 #pragma unroll 1
         for (int s = 0; s < KS + len; ++s) {
-            const int w = w0 - KS + s;
+            const int h = h0 - KS + s;
             if (s >= KS) {
 #pragma unroll
                 for (int i = 0; i < K; ++i) sw[(wd[i] & kRkMask) * NT] = sp[i];
@@ -216,52 +219,54 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
                     const int dy = t / KS - R, dx = t % KS - R;
                     o = __ldg(src + min(max(h + dy, 0), H - 1) * W + min(max(w + dx, 0), W - 1));
                 }
-                out[base + w] = o;
-                if (tap) tap[base + w] = t;
-                if (alpha) alpha[base + w] = c.alpha;
+                const long long at = base + (long long)h * W;
+                out[at] = o;
+                if (tap) tap[at] = t;
+                if (alpha) alpha[at] = c.alpha;
                 if (s + 1 >= KS + len) break;
             }
-            // --- slide the window one pixel to the right ---
-            // 1. the left column leaves, the others move one place to the left
+            // --- slide the window one pixel down ---
+            // 1. the top row leaves, the others move up one place
 #pragma unroll
-            for (int dy = 0; dy < KS; ++dy)
+            for (int dy = 0; dy + 1 < KS; ++dy)
 #pragma unroll
-                for (int dx = 0; dx + 1 < KS; ++dx) {
-                    const unsigned old = wd[dy * KS + dx + 1];
-                    const unsigned below = (old >> kRkBits) & ((1u << kCntBits) - 1u);   // taps of the leaving column below it
+                for (int dx = 0; dx < KS; ++dx) {
+                    const unsigned old = wd[(dy + 1) * KS + dx];
+                    const unsigned below = (old >> kRkBits) & ((1u << kCntBits) - 1u);   // taps of the leaving row below it
                     wd[dy * KS + dx] = ((old >> kCntBits) & ~kRkMask) | ((old - below) & kRkMask);
-                    v[dy * KS + dx] = v[dy * KS + dx + 1];
+                    v[dy * KS + dx] = v[(dy + 1) * KS + dx];
                 }
-            // 2. the new right column enters
+            // 2. the new bottom row enters
             unsigned wnew[KS];
 #pragma unroll
-            for (int ny = 0; ny < KS; ++ny) wnew[ny] = 0u;
+            for (int nx = 0; nx < KS; ++nx) wnew[nx] = 0u;
 #pragma unroll
-            for (int ny = 0; ny < KS; ++ny) {
-                const float x = nxt[ny];
+            for (int nx = 0; nx < KS; ++nx) {
+                const float x = nxt[nx];
 #pragma unroll
-                for (int dy = 0; dy < KS; ++dy)
+                for (int dy = 0; dy + 1 < KS; ++dy)
 #pragma unroll
-                    for (int dx = 0; dx + 1 < KS; ++dx) {
-                        // kept tap first: smaller value, or equal value and not a later window row
-                        const bool kept_first = (dy <= ny) ? (v[dy * KS + dx] <= x) : (v[dy * KS + dx] < x);
-                        if (kept_first) wnew[ny] += (1u << (kRkBits + kCntBits * dx)) + 1u;
+                    for (int dx = 0; dx < KS; ++dx) {
+                        // an equal kept tap has the smaller window index and comes first
+                        if (v[dy * KS + dx] <= x) wnew[nx] += (1u << (kRkBits + kCntBits * dy)) + 1u;
                         else wd[dy * KS + dx] += 1u;
                     }
 #pragma unroll
-                for (int my = 0; my < ny; ++my) {               // among the new taps the smaller row wins ties
-                    if (nxt[my] <= x) wnew[ny] += 1u;
-                    else wnew[my] += 1u;
+                for (int mx = 0; mx < nx; ++mx) {               // among the new taps the left one wins ties
+                    if (nxt[mx] <= x) wnew[nx] += 1u;
+                    else wnew[mx] += 1u;
                 }
             }
 #pragma unroll
-            for (int ny = 0; ny < KS; ++ny) {
-                v[ny * KS + KS - 1] = nxt[ny];
-                wd[ny * KS + KS - 1] = wnew[ny];
+            for (int nx = 0; nx < KS; ++nx) {
+                v[(KS - 1) * KS + nx] = nxt[nx];
+                wd[(KS - 1) * KS + nx] = wnew[nx];
             }
-            const int col = min(max(w + 2 + R, 0), W - 1);
+            {
+                const float* row = src + min(max(h + 2 + R, 0), H - 1) * W;
 #pragma unroll
-            for (int dy = 0; dy < KS; ++dy) nxt[dy] = __ldg(src + rowoff[dy] + col);
+                for (int dx = 0; dx < KS; ++dx) nxt[dx] = __ldg(row + coloff[dx]);
+            }
         }
     }
 }
@@ -512,12 +517,12 @@ static int run_forward(const float* flow, const float* wts, float* out, int* tap
         const int smem_slide = K * NT * (int)sizeof(WeightTap);
         CNL_TRY(ensure_dynamic_smem(wmedian_forward_slide_kernel<KS>, smem_slide));
         // Long runs amortise the KS start-up slides; short ones keep every SM busy on small inputs.
-        const long long rows = total / W, resident = 148LL * 3;
+        const long long cols = total / H, resident = 148LL * 3;
         int run_len = 16;
-        if ((rows * ((W + 63) / 64) + NT - 1) / NT >= 4 * resident) run_len = 64;
-        else if ((rows * ((W + 31) / 32) + NT - 1) / NT >= resident) run_len = 32;
-        const int runs = (W + run_len - 1) / run_len;
-        const long long nthreads = rows * runs;                      // one thread per (image-channel, row, run)
+        if ((cols * ((H + 63) / 64) + NT - 1) / NT >= 4 * resident) run_len = 64;
+        else if ((cols * ((H + 31) / 32) + NT - 1) / NT >= resident) run_len = 32;
+        const int runs = (H + run_len - 1) / run_len;
+        const long long nthreads = cols * runs;                      // one thread per (image-channel, column, run of rows)
         const unsigned sblocks = (unsigned)std::min<long long>((nthreads + NT - 1) / NT, 148LL * 64);
         wmedian_forward_slide_kernel<KS><<<sblocks, NT, smem_slide, st>>>(flow, wts, out, tap, alpha, nthreads, H, W, runs, run_len);
         return after_launch("wmedian_forward_slide_kernel");

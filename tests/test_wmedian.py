@@ -68,16 +68,18 @@ def test_cuda_matches_oracle(case):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("case", [(1, 1, 20, 45, 3), (1, 2, 33, 130, 5), (2, 1, 70, 300, 7), (4, 2, 384, 1270, 7), (16, 2, 384, 1270, 7)],
+@pytest.mark.parametrize("case", [(1, 1, 20, 45, 3), (1, 2, 33, 130, 5), (2, 1, 70, 300, 7), (4, 2, 370, 1270, 7), (16, 2, 370, 1270, 7)],
                          ids=lambda c: "n%d_c%d_%dx%d_k%d" % c)
 def test_sliding_kernels_give_the_bits_of_the_per_pixel_kernels(case, monkeypatch):
-    """The sliding-window kernels (runs of 16, 32 or 64 pixels per thread, chosen by the size of the input; the widths
+    """The sliding-window kernels (runs of 16, 32 or 64 pixels per thread, chosen by the size of the input; the heights
     here leave a ragged last run) against the one-thread-per-pixel kernels, which the small cases pin to the oracle."""
     from customnetworklayers_b200 import wmedian as wm
     n, c, h, w, k = case
     flow, wts, grad = make_median_filter_inputs(n, c, h, w, k=k, seed=77 + k)
     flow[0, 0, h // 2, 5:40] = 0.5                 # ties entering and leaving the window
+    flow[0, 0, 3:18, w // 2] = 0.5
     flow[0, 0, :, w - 3] = flow[0, 0, :, w - 2]
+    flow[0, 0, h - 3, :] = flow[0, 0, h - 2, :]
     flow, grad = flow.cuda(), grad.cuda()
     p = (wts / wts.sum()).float().cuda()
     res = {}
