@@ -137,23 +137,34 @@ struct WeightTap {        // staged per block: the normalised weight of a tap an
     int index;
 };
 
-template <int K>
+// The sequential scan of the selection rule over the weights in rank order, G entries per round: the loads of a round are
+// issued together, the running sum still takes them one by one in rank order.
+template <int K, int G>
 __device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restrict__ sw, int& index) {
+    static_assert(K % G == 0, "the scan takes whole rounds");
     Crossing c;
     c.rank = -1; c.pmid = 1.0f; c.alpha = 0.0f;
     index = -1;
     float score = 0.0f;
-    for (int r = 0; r < K; ++r) {
-        const float p = sw[r * NT].p;
-        const float nxt = score + p;
-        if (score < 0.5f && nxt >= 0.5f) {                       // medimax.cu:30
-            c.rank = r;
-            c.pmid = p;
-            c.alpha = (float)((1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p));     // :33
-            index = sw[r * NT].index;
-            break;
+#pragma unroll 1
+    for (int r0 = 0; r0 < K && c.rank < 0; r0 += G) {
+        float p[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) p[i] = sw[(r0 + i) * NT].p;
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const float nxt = score + p[i];
+            if (c.rank < 0 && score < 0.5f && nxt >= 0.5f) {     // medimax.cu:30
+                c.rank = r0 + i;
+                c.pmid = p[i];
+                c.alpha = score;                                  // the sum before the crossing, turned into alpha below
+            }
+            score = nxt;
         }
-        score = nxt;
+    }
+    if (c.rank >= 0) {
+        c.alpha = (float)((1.0 - 2.0 * (double)c.alpha - (double)c.pmid) / (2.0 * (double)c.pmid));     // :33
+        index = sw[c.rank * NT].index;
     }
     return c;
 }
@@ -213,7 +224,7 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
 #pragma unroll
                 for (int i = 0; i < K; ++i) sw[(wd[i] & kRkMask) * NT] = sp[i];
                 int t;
-                const Crossing c = scan_sorted_pairs<K>(sw, t);
+                const Crossing c = scan_sorted_pairs<K, KS>(sw, t);
                 float o = v[K / 2];                              // no crossing: the centre value passes through
                 if (t >= 0) {
                     const int dy = t / KS - R, dx = t % KS - R;
