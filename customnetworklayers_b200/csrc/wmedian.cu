@@ -129,6 +129,9 @@ wmedian_forward_kernel(const float* __restrict__ flow, const float* __restrict__
 // in before the first output: the start-up shares the code of the steady state, which keeps the unrolled body inside
 // the instruction caches.
 constexpr int kRun = 32;                  // pixels per thread of the weight-gradient walk
+constexpr int kAhead = 4;                 // rows by which that walk prefetches into L2
+
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 constexpr int kRkBits = 6, kCntBits = 3;
 constexpr unsigned kRkMask = (1u << kRkBits) - 1u;
 
@@ -391,6 +394,13 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
 #pragma unroll
                 for (int dx = 0; dx < KS; ++dx) nxt[dx] = __ldg(row + coloff[dx]);
             }
+            {   // rows further down are pulled into L2 ahead of the loads below
+                const long long ahead = base + (long long)min(h + kAhead, H - 1) * W;
+                prefetch_l2(src + (long long)min(h + kAhead + R, H - 1) * W + w);
+                prefetch_l2(tap + ahead);
+                prefetch_l2(grad + ahead);
+                prefetch_l2(alpha + ahead);
+            }
             if (h + 1 < hend) {
                 const long long at = base + (long long)(h + 1) * W;
                 t_n = t_nn;
@@ -401,7 +411,9 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
             }
             if (t >= 0) {
                 const float pmid = sp[t];
-                const float half = (float)((double)g0 / (2.0 * (double)pmid));
+                // g0 / (2 pmid) rounded once; the reference divides in double and rounds the quotient to float, which gives
+                // the same bits (a quotient of two floats rounded to 53 bits and then to 24 rounds like one rounding)
+                const float half = __fdiv_rn(g0, __fmul_rn(2.0f, pmid));
                 const float mid = __fdiv_rn(__fmul_rn(g0, al), -pmid);
                 sacc[t * NT] += mid - half;
 #pragma unroll
@@ -410,7 +422,7 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
                     acc[i] += before ? -half : half;
                 }
             } else {                                         // no crossing: every bin counts as "before" (weight 1)
-                const float half = (float)((double)g0 / 2.0);
+                const float half = 0.5f * g0;
 #pragma unroll
                 for (int i = 0; i < K; ++i) acc[i] -= half;
             }
