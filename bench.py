@@ -736,7 +736,7 @@ def run_wmedian(args, rank, local_rank, world):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"cfg4: learnable 7x7 weighted-median filter fwd+bwd, per-GPU batch {nb}, flow {ch}x{h}x{w}, 5% outliers, 49 weight gradients all-reduced",
                        "global_batch": nb * world, "parallelism": f"dp{world}"},
-            "roofline": {"bound": "hbm", "kernel": "whole step; the kernels are bound by the rank updates of the sliding window (about 2*K*k compares per problem), not by HBM",
+            "roofline": {"bound": "hbm", "kernel": "whole step; the kernels are bound by instruction issue in the rank updates of the sliding window (k*(K-k) compares and twice as many adds per problem), not by HBM",
                          "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_kind": kind,
                          "materialised_layout_equivalent_gbs": 604.0 * problems / world * args.steps / (ms * 1e-3) / 1e9},
             "gpu_launches": int(launches), "clocks": clocks})
