@@ -445,13 +445,21 @@ wmedian_weight_grad_slide_kernel(const float* __restrict__ flow, const float* __
     }
 }
 
-__global__ void __launch_bounds__(64)
+// Sum over the per-block partial sums in a fixed order: sixteen interleaved slices of the blocks, then the slices.
+__global__ void __launch_bounds__(1024)
 wmedian_weight_grad_final_kernel(const double* __restrict__ partial, int nblocks, int K, float* __restrict__ g_p) {
-    const int i = threadIdx.x;
-    if (i >= K) return;
+    __shared__ double slice[16][64];
+    const int i = threadIdx.x & 63, part = threadIdx.x >> 6;
     double s = 0.0;
-    for (int b = 0; b < nblocks; ++b) s += partial[(size_t)b * K + i];
-    g_p[i] = (float)s;
+    if (i < K)
+        for (int b = part; b < nblocks; b += 16) s += partial[(size_t)b * K + i];
+    slice[part][i] = s;
+    __syncthreads();
+    if (part == 0 && i < K) {
+        double t = 0.0;
+        for (int q = 0; q < 16; ++q) t += slice[q][i];
+        g_p[i] = (float)t;
+    }
 }
 
 // Input gradient, gather form: pixel q collects the upstream gradient of every pixel p in its neighbourhood whose
@@ -583,7 +591,7 @@ static int run_backward(const float* flow, const float* wts, const int* tap, con
         wmedian_weight_grad_kernel<KS><<<blocks, NT, smem, st>>>(flow, wts, tap, alpha, grad, scratch, total, H, W);
         CNL_TRY(after_launch("wmedian_weight_grad_kernel"));
     }
-    wmedian_weight_grad_final_kernel<<<1, 64, 0, st>>>(scratch, blocks, K, g_p);
+    wmedian_weight_grad_final_kernel<<<1, 1024, 0, st>>>(scratch, blocks, K, g_p);
     CNL_TRY(after_launch("wmedian_weight_grad_final_kernel"));
     const long long images = total / ((long long)H * W);
     if (images <= 65535) {
