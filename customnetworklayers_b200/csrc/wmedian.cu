@@ -141,32 +141,69 @@ struct WeightTap {        // staged per block: the normalised weight of a tap an
 };
 
 // The sequential scan of the selection rule over the weights in rank order, G entries per round: the loads of a round are
-// issued together, the running sum still takes them one by one in rank order.
+// issued together, the running sum still takes them one by one in rank order.  With weights that are all >= 0
+// (`monotone`) the running sum never falls, so the first crossing lies in the first round that ends at or above 0.5:
+// the rounds then only add, and the round of the crossing is walked a second time to find the entry.
 template <int K, int G>
-__device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restrict__ sw, int& index) {
+__device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restrict__ sw, bool monotone, int& index) {
     static_assert(K % G == 0, "the scan takes whole rounds");
     Crossing c;
     c.rank = -1; c.pmid = 1.0f; c.alpha = 0.0f;
     index = -1;
-    float score = 0.0f;
+    float before = 0.0f;                                          // the sum in front of the crossing
+    if (monotone) {
+        int round = -1;
+        float score = 0.0f;
 #pragma unroll 1
-    for (int r0 = 0; r0 < K && c.rank < 0; r0 += G) {
-        float p[G];
+        for (int r0 = 0; r0 < K; r0 += G) {
+            float p[G];
 #pragma unroll
-        for (int i = 0; i < G; ++i) p[i] = sw[(r0 + i) * NT].p;
+            for (int i = 0; i < G; ++i) p[i] = sw[(r0 + i) * NT].p;
+            float s = score;
 #pragma unroll
-        for (int i = 0; i < G; ++i) {
-            const float nxt = score + p[i];
-            if (c.rank < 0 && score < 0.5f && nxt >= 0.5f) {     // medimax.cu:30
-                c.rank = r0 + i;
-                c.pmid = p[i];
-                c.alpha = score;                                  // the sum before the crossing, turned into alpha below
+            for (int i = 0; i < G; ++i) s += p[i];
+            if (s >= 0.5f) {
+                round = r0;
+                break;
             }
-            score = nxt;
+            score = s;
+        }
+        if (round >= 0) {
+            float p[G];
+#pragma unroll
+            for (int i = 0; i < G; ++i) p[i] = sw[(round + i) * NT].p;
+#pragma unroll
+            for (int i = 0; i < G; ++i) {
+                const float nxt = score + p[i];
+                if (c.rank < 0 && nxt >= 0.5f) {                  // score < 0.5 holds up to the crossing (medimax.cu:30)
+                    c.rank = round + i;
+                    c.pmid = p[i];
+                    before = score;
+                }
+                score = nxt;
+            }
+        }
+    } else {
+        float score = 0.0f;
+#pragma unroll 1
+        for (int r0 = 0; r0 < K && c.rank < 0; r0 += G) {
+            float p[G];
+#pragma unroll
+            for (int i = 0; i < G; ++i) p[i] = sw[(r0 + i) * NT].p;
+#pragma unroll
+            for (int i = 0; i < G; ++i) {
+                const float nxt = score + p[i];
+                if (c.rank < 0 && score < 0.5f && nxt >= 0.5f) {  // medimax.cu:30
+                    c.rank = r0 + i;
+                    c.pmid = p[i];
+                    before = score;
+                }
+                score = nxt;
+            }
         }
     }
     if (c.rank >= 0) {
-        c.alpha = (float)((1.0 - 2.0 * (double)c.alpha - (double)c.pmid) / (2.0 * (double)c.pmid));     // :33
+        c.alpha = (float)((1.0 - 2.0 * (double)before - (double)c.pmid) / (2.0 * (double)c.pmid));      // :33
         index = sw[c.rank * NT].index;
     }
     return c;
@@ -181,11 +218,13 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
     static_assert(K <= (1 << kRkBits) && KS < (1 << kCntBits) && kRkBits + kCntBits * (KS - 1) <= 32, "packed word too small");
     extern __shared__ unsigned char smem_raw[];
     __shared__ WeightTap sp[K];
+    float mine = 0.0f;
     if (threadIdx.x < K) {
-        sp[threadIdx.x].p = weights[threadIdx.x];
+        mine = weights[threadIdx.x];
+        sp[threadIdx.x].p = mine;
         sp[threadIdx.x].index = threadIdx.x;
     }
-    __syncthreads();
+    const bool monotone = __syncthreads_and(mine >= 0.0f) != 0;      // no negative (or NaN) weight: the running sum never falls
     WeightTap* sw = reinterpret_cast<WeightTap*>(smem_raw) + threadIdx.x;             // sw[r * NT]
     const long long plane = (long long)H * W;
     for (long long tix = (long long)blockIdx.x * NT + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * NT) {
@@ -227,7 +266,7 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
 #pragma unroll
                 for (int i = 0; i < K; ++i) sw[(wd[i] & kRkMask) * NT] = sp[i];
                 int t;
-                const Crossing c = scan_sorted_pairs<K, KS>(sw, t);
+                const Crossing c = scan_sorted_pairs<K, KS>(sw, monotone, t);
                 float o = v[K / 2];                              // no crossing: the centre value passes through
                 if (t >= 0) {
                     const int dy = t / KS - R, dx = t % KS - R;

@@ -95,6 +95,27 @@ def test_sliding_kernels_give_the_bits_of_the_per_pixel_kernels(case, monkeypatc
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("k", [3, 7])
+def test_negative_weights_cross_where_the_oracle_crosses(k):
+    """With a negative weight the running sum can fall back below 0.5 and cross again; the first crossing counts.  (The
+    sliding kernel scans weights that are all >= 0 by a shorter route, so this case has a path of its own.)"""
+    from customnetworklayers_b200 import wmedian as wm
+    flow, wts, grad = make_median_filter_inputs(1, 2, 24, 80, k=k, seed=321 + k)
+    wts = wts.clone()
+    wts[1::4] *= -0.6
+    p = (wts / wts.sum()).float()
+    assert float(p.min()) < 0
+    out, tap, alpha = wm.forward(flow.cuda(), p.cuda(), k)
+    g_flow, g_p = wm.backward(flow.cuda(), p.cuda(), tap, alpha, grad.cuda(), k)
+    o_ref, t_ref, _ = W.wmedian_forward(flow.numpy(), p.numpy(), k)
+    gf_ref, gp_ref = W.wmedian_backward(flow.numpy(), p.numpy(), grad.numpy(), k)
+    assert np.array_equal(tap.cpu().numpy(), t_ref), "selected tap must be bit-exact"
+    assert np.array_equal(out.cpu().numpy(), o_ref)
+    assert_close(g_flow, torch.from_numpy(gf_ref), "g_flow", tol=1e-5)
+    assert_close(g_p, torch.from_numpy(gp_ref), "g_weights")
+
+
+@pytest.mark.gpu
 def test_filter_module_learns_through_normalisation():
     from customnetworklayers_b200.wmedian import WeightedMedianFilter
     flow, wts, grad = make_median_filter_inputs(2, 2, 24, 32, seed=5)
