@@ -32,9 +32,10 @@ inline int after_launch(const char* kernel) {
     return check_cuda(cudaGetLastError(), kernel);
 }
 
-// peer_allreduce.cu: final stage of the lambda-gradient reduction fused with its exchange over peer memory
-int launch_tv_dot_final_allreduce(const float* partial, int nblocks, float* out, void* const* peer_bufs, int rank, int world,
-                                  unsigned long long seq, cudaStream_t st);
+// peer_allreduce.cu: the lambda-gradient reduction out = sum a * b in one launch (scratch: nblocks doubles); with
+// peer_bufs non-null the sum over all ranks, exchanged over peer memory inside the same kernel
+int launch_tv_dot(const float* a, const float* b, long long count, float* out, float* scratch, int nblocks,
+                  void* const* peer_bufs, int rank, int world, unsigned long long seq, cudaStream_t st);
 
 #define CNL_TRY(expr)                 \
     do {                              \

@@ -60,15 +60,48 @@ peer_allreduce_kernel(float* __restrict__ values, int count, PeerBufs pb, int ra
     if (i < count) values[i] = peer_sum(values[i], i, pb, rank, world, seq);
 }
 
-// tv_dot_final_kernel with the exchange appended: the local sum never leaves the kernel before it is a global one.
-__global__ void __launch_bounds__(32)
-tv_dot_final_allreduce_kernel(const float* __restrict__ partial, int nblocks, float* __restrict__ out, PeerBufs pb,
-                              int rank, int world, unsigned seq) {
-    const double* p = reinterpret_cast<const double*>(partial);
+// lambda gradient of the TV layer, out = sum a * b, in ONE launch, with the exchange appended where there are peers: the
+// local sum never leaves the kernel before it is a global one.  Every block leaves its partial sum (a double) in the
+// caller's scratch and takes a ticket; the block that draws the last ticket adds the partials in a fixed order, so the
+// result does not depend on which block that was.  Tickets are words of a library-owned table that the last block
+// resets to zero; every call takes the next word (the host counts), so calls that run side by side on different
+// streams do not share one.
+constexpr int kDotTickets = 4096;
+__device__ unsigned int g_dot_tickets[kDotTickets];
+
+template <bool kExchange>
+__global__ void __launch_bounds__(256)
+tv_dot_kernel(const float* __restrict__ a, const float* __restrict__ b, long long count, double* partial, float* __restrict__ out,
+              int ticket, PeerBufs pb, int rank, int world, unsigned seq) {
+    __shared__ double sh[8];
+    __shared__ bool last;
     double s = 0.0;
-    for (int i = threadIdx.x; i < nblocks; i += 32) s += p[i];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+        s += (double)a[i] * (double)b[i];
     for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
-    if (threadIdx.x == 0) out[0] = peer_sum((float)s, 0, pb, rank, world, seq);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double ts = 0.0;
+        for (int i = 0; i < 8; ++i) ts += sh[i];
+        partial[blockIdx.x] = ts;
+        __threadfence();                                        // the partial is visible before the ticket is
+        last = atomicAdd(&g_dot_tickets[ticket], 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    double v = 0.0;
+    for (int i = threadIdx.x; i < (int)gridDim.x; i += 256) v += __ldcg(partial + i);
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double ts = 0.0;
+        for (int i = 0; i < 8; ++i) ts += sh[i];
+        g_dot_tickets[ticket] = 0u;                             // ready for the call that takes this word next
+        out[0] = kExchange ? peer_sum((float)ts, 0, pb, rank, world, seq) : (float)ts;
+    }
 }
 
 static int fill_bufs(PeerBufs& pb, void* const* peer_bufs, int rank, int world) {
@@ -84,13 +117,21 @@ static int fill_bufs(PeerBufs& pb, void* const* peer_bufs, int rank, int world) 
     return CNL_OK;
 }
 
-int launch_tv_dot_final_allreduce(const float* partial, int nblocks, float* out, void* const* peer_bufs, int rank, int world,
-                                  unsigned long long seq, cudaStream_t st) {
+int launch_tv_dot(const float* a, const float* b, long long count, float* out, float* scratch, int nblocks,
+                  void* const* peer_bufs, int rank, int world, unsigned long long seq, cudaStream_t st) {
+    static std::atomic<unsigned> next_ticket{0};
+    const int ticket = (int)(next_ticket.fetch_add(1, std::memory_order_relaxed) % kDotTickets);
+    double* partial = reinterpret_cast<double*>(scratch);
     PeerBufs pb;
+    if (!peer_bufs) {
+        for (int r = 0; r < kPeerMaxWorld; ++r) pb.buf[r] = nullptr;
+        tv_dot_kernel<false><<<nblocks, 256, 0, st>>>(a, b, count, partial, out, ticket, pb, 0, 1, 0u);
+        return after_launch("tv_dot_kernel");
+    }
     CNL_TRY(fill_bufs(pb, peer_bufs, rank, world));
     if (seq == 0) return fail(CNL_ERR_BAD_SHAPE, "call numbers start at 1 (the buffers start zeroed)");
-    tv_dot_final_allreduce_kernel<<<1, 32, 0, st>>>(partial, nblocks, out, pb, rank, world, (unsigned)seq);
-    return after_launch("tv_dot_final_allreduce_kernel");
+    tv_dot_kernel<true><<<nblocks, 256, 0, st>>>(a, b, count, partial, out, ticket, pb, rank, world, (unsigned)seq);
+    return after_launch("tv_dot_kernel");
 }
 
 }  // namespace cnl

@@ -338,36 +338,9 @@ tv_finalize_kernel(FinalizeArgs a, double* __restrict__ partial, const double* _
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// lambda gradient: out = sum g_c * c_raw, deterministic two-stage reduction
+// lambda gradient: out = sum g_c * c_raw, one launch (launch_tv_dot); its grid and the doubles of scratch it needs
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kDotBlocks = 592;      // 4 x 148 SMs
-
-__global__ void __launch_bounds__(256)
-tv_dot_partial_kernel(const float* __restrict__ a, const float* __restrict__ b, long long count,
-                      float* __restrict__ partial) {
-    double s = 0.0;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
-        s += (double)a[i] * (double)b[i];
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
-    __shared__ double sh[8];
-    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        double ts = 0.0;
-        for (int i = 0; i < 8; ++i) ts += sh[i];
-        // a double partial is stored in two float slots so the scratch stays a float array for the caller
-        reinterpret_cast<double*>(partial)[blockIdx.x] = ts;
-    }
-}
-
-__global__ void __launch_bounds__(32)
-tv_dot_final_kernel(const float* __restrict__ partial, int nblocks, float* __restrict__ out) {
-    const double* p = reinterpret_cast<const double*>(partial);
-    double s = 0.0;
-    for (int i = threadIdx.x; i < nblocks; i += 32) s += p[i];
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
-    if (threadIdx.x == 0) out[0] = (float)s;
-}
 
 // ---------------------------------------------------------------------------------------------------------------
 // per-id slots
@@ -1178,10 +1151,7 @@ extern "C" int cnl_tv_lambda_grad(const float* g_c, const float* c_raw, long lon
     if (count < 0) return fail(CNL_ERR_BAD_SHAPE, "negative element count");
     if ((reinterpret_cast<size_t>(scratch) & 7) != 0) return fail(CNL_ERR_BAD_SHAPE, "scratch must be 8-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    tv_dot_partial_kernel<<<kDotBlocks, 256, 0, st>>>(g_c, c_raw, count, scratch);
-    CNL_TRY(after_launch("tv_dot_partial_kernel"));
-    tv_dot_final_kernel<<<1, 32, 0, st>>>(scratch, kDotBlocks, out);
-    return after_launch("tv_dot_final_kernel");
+    return launch_tv_dot(g_c, c_raw, count, out, scratch, kDotBlocks, nullptr, 0, 1, 0, st);
 }
 
 extern "C" int cnl_tv_lambda_grad_allreduce(const float* g_c, const float* c_raw, long long count, float* out, float* scratch,
@@ -1190,7 +1160,6 @@ extern "C" int cnl_tv_lambda_grad_allreduce(const float* g_c, const float* c_raw
     if (count < 0) return fail(CNL_ERR_BAD_SHAPE, "negative element count");
     if ((reinterpret_cast<size_t>(scratch) & 7) != 0) return fail(CNL_ERR_BAD_SHAPE, "scratch must be 8-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    tv_dot_partial_kernel<<<kDotBlocks, 256, 0, st>>>(g_c, c_raw, count, scratch);
-    CNL_TRY(after_launch("tv_dot_partial_kernel"));
-    return launch_tv_dot_final_allreduce(scratch, kDotBlocks, out, peer_bufs, rank, world, seq, st);
+    if (!peer_bufs) return fail(CNL_ERR_NULL, "null pointer argument");
+    return launch_tv_dot(g_c, c_raw, count, out, scratch, kDotBlocks, peer_bufs, rank, world, seq, st);
 }

@@ -96,7 +96,7 @@ class PeerAllReduce:
         return values
 
     def lambda_grad(self, g_c: torch.Tensor, c_raw: torch.Tensor, out=None, scratch=None) -> torch.Tensor:
-        """sum over all ranks of sum(g_c * c_raw): the local reduction and the exchange in one pair of kernels."""
+        """sum over all ranks of sum(g_c * c_raw): the local reduction and the exchange in one kernel."""
         from . import _lib
         if out is None:
             out = torch.empty(1, dtype=torch.float32, device=g_c.device)

@@ -125,7 +125,8 @@ unsigned long long cnl_launch_count(void);
 
 /*
  * Gradient of the loss w.r.t. a scalar lambda that multiplies a raw confidence map (c = lambda * c_raw):
- * out[0] = sum_i g_c[i] * c_raw[i], a deterministic two-stage shuffle reduction.  This is the one value the
+ * out[0] = sum_i g_c[i] * c_raw[i], a deterministic reduction in one launch (per-block partial sums in
+ * double; the block that finishes last adds them in a fixed order).  This is the one value the
  * data-parallel layer all-reduces.  The reference has no learned scalar; its per-pixel confidence gradient is
  * d_outGradC (cudaTV/cudaCode/TVInpaintFista.cu:1795-1798).
  * `scratch` must hold at least cnl_dot_scratch_floats() floats of device memory.
@@ -145,7 +146,7 @@ int cnl_dot_scratch_floats(void);
  *   seq:       call number, 1, 2, 3, ... and the same on every rank for the same call.
  * Every rank must make the same calls in the same order.  Waits are bounded (about a second): a rank whose peers do not
  * answer gets NaN, and cnl_peer_allreduce_status() then returns that call's number (0: none gave up).
- * cnl_tv_lambda_grad_allreduce is cnl_tv_lambda_grad with this exchange fused into its final kernel: out[0] is the sum
+ * cnl_tv_lambda_grad_allreduce is cnl_tv_lambda_grad with this exchange appended inside the same kernel: out[0] is the sum
  * over all ranks.
  */
 long long cnl_peer_allreduce_bytes(void);
