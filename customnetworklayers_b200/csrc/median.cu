@@ -3,8 +3,11 @@
 //
 // Both kernels are HBM bound (K floats in, 2 out / K floats in, K out per pixel).  A warp stages the K weights of
 // its 32 pixels, which are contiguous in memory, with coalesced loads into shared memory (row stride K|1, odd, so
-// the per-thread sequential scans are bank-conflict free), then every thread scans its own row.  The running sum
-// is the same sequential fp32 sum in bin order as the reference's, so the crossing index is bit-identical.
+// the per-thread sequential scans are bank-conflict free), then every thread scans its own row.  With an odd K the
+// staged rows have the layout they have in memory, so staging is a straight 16-byte asynchronous copy and the
+// write-back a straight 16-byte copy out; an even K goes through a scatter that pads every row by one float.  The
+// running sum is the same sequential fp32 sum in bin order as the reference's (the loads of eight bins are issued
+// together, the sum still takes them one by one), so the crossing index is bit-identical.
 #include "common.h"
 
 namespace cnl {
@@ -30,6 +33,15 @@ __device__ __forceinline__ void stage_rows(const float* __restrict__ src, float*
     const int count = (int)(left > 32 ? 32 : left) * k;
     const float* base = src + first_pixel * k;
     const int nvec = (reinterpret_cast<size_t>(base) & 15) == 0 ? count >> 2 : 0;
+    if (stride == k) {                                       // odd k: same layout on both sides
+        for (int v = lane; v < nvec; v += 32) {
+            const unsigned to = (unsigned)__cvta_generic_to_shared(reinterpret_cast<float4*>(dst) + v);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to), "l"(reinterpret_cast<const float4*>(base) + v) : "memory");
+        }
+        for (int i = 4 * nvec + lane; i < count; i += 32) dst[i] = __ldg(base + i);
+        asm volatile("cp.async.commit_group;\ncp.async.wait_all;" ::: "memory");
+        return;
+    }
     for (int v = lane; v < nvec; v += 32) {
         const float4 q = __ldg(reinterpret_cast<const float4*>(base) + v);
         int p = med_div(4 * v, magic), c = 4 * v - p * k;
@@ -53,6 +65,11 @@ __device__ __forceinline__ void unstage_rows(const float* __restrict__ rows, flo
     const int count = (int)(left > 32 ? 32 : left) * k;
     float* base = dst + first_pixel * k;
     const int nvec = (reinterpret_cast<size_t>(base) & 15) == 0 ? count >> 2 : 0;
+    if (stride == k) {                                       // odd k: same layout on both sides
+        for (int v = lane; v < nvec; v += 32) reinterpret_cast<float4*>(base)[v] = reinterpret_cast<const float4*>(rows)[v];
+        for (int i = 4 * nvec + lane; i < count; i += 32) base[i] = rows[i];
+        return;
+    }
     for (int v = lane; v < nvec; v += 32) {
         int p = med_div(4 * v, magic), c = 4 * v - p * k;
         float4 q;
@@ -66,6 +83,32 @@ __device__ __forceinline__ void unstage_rows(const float* __restrict__ rows, flo
         const int p = med_div(i, magic);
         base[i] = rows[p * stride + (i - p * k)];
     }
+}
+
+// First bin c with score < 0.5 <= score + p[c] (medimax.cu:30) for the sequential fp32 running sum over the row;
+// returns -1 if there is none.  Eight loads per round are issued together.
+__device__ __forceinline__ int med_crossing(const float* __restrict__ row, int k, float& p_at, float& score_before) {
+    constexpr int G = 8;
+    int hit = -1;
+    float score = 0.0f;
+    p_at = 1.0f;
+    score_before = 0.0f;
+    for (int c0 = 0; c0 < k && hit < 0; c0 += G) {
+        float p[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) p[i] = c0 + i < k ? row[c0 + i] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const float nxt = score + p[i];
+            if (hit < 0 && c0 + i < k && score < 0.5f && nxt >= 0.5f) {
+                hit = c0 + i;
+                p_at = p[i];
+                score_before = score;
+            }
+            score = nxt;
+        }
+    }
+    return hit;
 }
 
 __global__ void __launch_bounds__(kMedThreads)
@@ -82,19 +125,12 @@ median_forward_kernel(const float* __restrict__ vol, float* __restrict__ out, in
     const long long pix = first + lane;
     if (pix >= total) return;
     const float* row = rows + lane * med_stride(k);
-    float score = 0.0f, o0 = 0.0f, o1 = 0.0f;
-    int hit = -1;
-    for (int c = 0; c < k; ++c) {
-        const float p = row[c];
-        const float nxt = score + p;
-        if (score < 0.5f && nxt >= 0.5f) {                           // medimax.cu:30
-            const double alpha = (1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p);     // :33
-            o0 = (float)((double)c + alpha);                         // :34
-            o1 = p;                                                  // :35
-            hit = c;
-            break;
-        }
-        score = nxt;
+    float o0 = 0.0f, o1 = 0.0f, p, score;
+    const int hit = med_crossing(row, k, p, score);
+    if (hit >= 0) {
+        const double alpha = (1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p);         // :33
+        o0 = (float)((double)hit + alpha);                           // :34
+        o1 = p;                                                      // :35
     }
     const long long img = pix / plane, off = pix - img * plane;
     out[(img * 2 + 0) * plane + off] = o0;
@@ -121,32 +157,29 @@ median_backward_kernel(const float* __restrict__ vol, const float* __restrict__ 
         const float g0 = grad[(img * 2 + 0) * plane + off];
         const float g1 = grad[(img * 2 + 1) * plane + off];
         // pass 1: crossing bin (medimax.cu:55-80)
-        float score = 0.0f, pmid = 1.0f, gmid = 0.0f;
-        int hit = -1;
-        for (int c = 0; c < k; ++c) {
-            const float p = row[c];
-            const float nxt = score + p;
-            if (score < 0.5f && nxt >= 0.5f) {
-                const float alpha = (float)((1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p));
-                gmid = __fadd_rn(__fdiv_rn(__fmul_rn(g0, alpha), -p), g1);       // :73, fp32, no contraction
-                pmid = p;
-                hit = c;
-                break;
-            }
-            score = nxt;
+        float score, pmid, gmid = 0.0f;
+        const int hit = med_crossing(row, k, pmid, score);
+        if (hit >= 0) {
+            const float alpha = (float)((1.0 - 2.0 * (double)score - (double)pmid) / (2.0 * (double)pmid));
+            gmid = __fadd_rn(__fdiv_rn(__fmul_rn(g0, alpha), -pmid), g1);        // :73, fp32, no contraction
         }
         // pass 2: bins before / after the crossing (:82-99); the row in shared memory is overwritten by its gradient
         const float half = (float)((double)g0 / (2.0 * (double)pmid));
         score = 0.0f;
-        for (int c = 0; c < k; ++c) {
-            const float p = row[c];
-            const float nxt = score + p;
-            float g = 0.0f;
-            if (nxt < 0.5f) g = -half;
-            else if (score >= 0.5f) g = half;
-            if (c == hit) g = gmid;
-            row[c] = g;
-            score = nxt;
+        for (int c0 = 0; c0 < k; c0 += 8) {
+            float p[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) p[i] = c0 + i < k ? row[c0 + i] : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float nxt = score + p[i];
+                float g = 0.0f;
+                if (nxt < 0.5f) g = -half;
+                else if (score >= 0.5f) g = half;
+                if (c0 + i == hit) g = gmid;
+                if (c0 + i < k) row[c0 + i] = g;
+                score = nxt;
+            }
         }
     }
     __syncwarp();
