@@ -526,47 +526,81 @@ wmedian_input_grad_kernel(const int* __restrict__ tap, const float* __restrict__
     g_flow[idx] = s;
 }
 
-// The same sum from a shared-memory tile: a block of 32 x 8 pixels first resolves, for every window centre of its tile
-// and halo, which pixel that window selected (one division per centre instead of one per centre and neighbour), then
-// every pixel scans the K centres around it in the order of the kernel above, so the two give the same bits.
+// The same sum from a shared-memory tile of 32 x 32 pixels.  Every window centre of the tile and its halo first marks,
+// in a 49-bit mask of the pixel it selected, which of that pixel's K surrounding centres it is (an integer atomic OR, so
+// the marks do not depend on timing); every pixel then walks the set bits of its own mask in rising order, which is the
+// order in which the kernel above scans the K centres, so the two give the same bits.  A pixel is selected by one
+// centre on average, so it adds about one value instead of comparing K; a thread serves four pixels, so that a block
+// has enough loads in flight to cover their latency.
 template <int KS>
 __global__ void __launch_bounds__(256)
 wmedian_input_grad_tiled_kernel(const int* __restrict__ tap, const float* __restrict__ grad, float* __restrict__ g_flow,
                                 int H, int W) {
-    constexpr int R = KS / 2, BW = 32, BH = 8, TW = BW + 2 * R, TH = BH + 2 * R;
-    __shared__ int s_target[TH][TW];          // linear index of the pixel the window centred here selected, -1 outside the image
+    constexpr int R = KS / 2, BW = 32, BH = 32, TW = BW + 2 * R, TH = BH + 2 * R;
+    __shared__ unsigned int s_mask[BH][BW][2];
     __shared__ float s_grad[TH][TW];
     const size_t plane = (size_t)H * W;
     const int* tp = tap + (size_t)blockIdx.z * plane;
     const float* gp = grad + (size_t)blockIdx.z * plane;
-    const int h0 = blockIdx.y * BH - R, w0 = blockIdx.x * BW - R;
-    for (int i = threadIdx.x; i < TH * TW; i += 256) {
-        const int r = i / TW, c = i - r * TW;
-        const int ph = h0 + r, pw = w0 + c;
-        int target = -1;
-        float g = 0.0f;
-        if (ph >= 0 && ph < H && pw >= 0 && pw < W) {
-            int t = __ldg(tp + (size_t)ph * W + pw);
-            if (t < 0) t = (KS * KS - 1) / 2;                       // no crossing: the centre passed through
-            const int th = min(max(ph + t / KS - R, 0), H - 1), tw = min(max(pw + t % KS - R, 0), W - 1);
-            target = th * W + tw;
-            g = __ldg(gp + (size_t)ph * W + pw);
-        }
-        s_target[r][c] = target;
-        s_grad[r][c] = g;
+    const int h0 = blockIdx.y * BH, w0 = blockIdx.x * BW;
+    const int tx = threadIdx.x & (BW - 1), ty0 = threadIdx.x / BW;
+#pragma unroll
+    for (int ty = ty0; ty < BH; ty += 256 / BW) {
+        s_mask[ty][tx][0] = 0u;
+        s_mask[ty][tx][1] = 0u;
     }
     __syncthreads();
-    const int tx = threadIdx.x & (BW - 1), ty = threadIdx.x / BW;
-    const int qh = blockIdx.y * BH + ty, qw = blockIdx.x * BW + tx;
-    if (qh >= H || qw >= W) return;
-    const int me = qh * W + qw;
-    float s = 0.0f;
+    // all of a thread's centres are fetched before the first is worked on, so that a block waits for memory once
+    constexpr int kPer = (TH * TW + 255) / 256;
+    int taps[kPer];
+    float grads[kPer];
 #pragma unroll
-    for (int dy = 0; dy < KS; ++dy)
+    for (int j = 0; j < kPer; ++j) {
+        const int i = threadIdx.x + j * 256;
+        const int r = i / TW, c = i - r * TW;
+        const int ph = h0 - R + r, pw = w0 - R + c;
+        const bool inside = i < TH * TW && ph >= 0 && ph < H && pw >= 0 && pw < W;
+        taps[j] = inside ? __ldg(tp + (size_t)ph * W + pw) : 0;
+        grads[j] = inside ? __ldg(gp + (size_t)ph * W + pw) : 0.0f;
+    }
 #pragma unroll
-        for (int dx = 0; dx < KS; ++dx)
-            if (s_target[ty + dy][tx + dx] == me) s += s_grad[ty + dy][tx + dx];
-    g_flow[(size_t)blockIdx.z * plane + me] = s;
+    for (int j = 0; j < kPer; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i >= TH * TW) break;
+        const int r = i / TW, c = i - r * TW;
+        const int ph = h0 - R + r, pw = w0 - R + c;
+        if (ph >= 0 && ph < H && pw >= 0 && pw < W) {
+            int t = taps[j];
+            if (t < 0) t = (KS * KS - 1) / 2;                       // no crossing: the centre passed through
+            const int th = min(max(ph + t / KS - R, 0), H - 1), tw = min(max(pw + t % KS - R, 0), W - 1);
+            const int qy = th - h0, qx = tw - w0;
+            if (qy >= 0 && qy < BH && qx >= 0 && qx < BW) {
+                const int bit = (ph - th + R) * KS + (pw - tw + R);     // this centre's place among the K around (th, tw)
+                atomicOr(&s_mask[qy][qx][bit >> 5], 1u << (bit & 31));
+            }
+        }
+        s_grad[r][c] = grads[j];
+    }
+    __syncthreads();
+    const int qw = w0 + tx;
+    if (qw >= W) return;
+#pragma unroll
+    for (int ty = ty0; ty < BH; ty += 256 / BW) {
+        const int qh = h0 + ty;
+        if (qh >= H) break;
+        float s = 0.0f;
+#pragma unroll
+        for (int word = 0; word < 2; ++word) {
+            unsigned int m = s_mask[ty][tx][word];
+            while (m) {
+                const int bit = word * 32 + __ffs(m) - 1;
+                m &= m - 1u;
+                const int dy = bit / KS, dx = bit - dy * KS;
+                s += s_grad[ty + dy][tx + dx];
+            }
+        }
+        g_flow[(size_t)blockIdx.z * plane + (size_t)qh * W + qw] = s;
+    }
 }
 
 constexpr int kGradBlocks = 592;
@@ -634,7 +668,7 @@ static int run_backward(const float* flow, const float* wts, const int* tap, con
     CNL_TRY(after_launch("wmedian_weight_grad_final_kernel"));
     const long long images = total / ((long long)H * W);
     if (images <= 65535) {
-        const dim3 grid((W + 31) / 32, (H + 7) / 8, (unsigned)images);
+        const dim3 grid((W + 31) / 32, (H + 31) / 32, (unsigned)images);
         wmedian_input_grad_tiled_kernel<KS><<<grid, 256, 0, st>>>(tap, grad, g_flow, H, W);
         return after_launch("wmedian_input_grad_tiled_kernel");
     }
