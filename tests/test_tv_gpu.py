@@ -382,6 +382,29 @@ def test_a_wait_that_cannot_end_stops_the_sweep_and_is_reported(ext):
     ext.release(3)
 
 
+def test_lambda_gradients_on_two_streams_at_once_do_not_disturb_each_other(ext):
+    """The reduction runs in one launch whose last block adds the block partials; which block is last is decided by a
+    ticket word that the library hands out per call.  Many calls in flight on two streams, with inputs of different
+    sizes, must each give the sum of their own inputs, the same bits every time."""
+    gen = torch.Generator().manual_seed(77)
+    sizes = [2 * 384 * 1280, 8 * 384 * 1280]
+    a = [torch.randn(n, generator=gen).cuda() for n in sizes]
+    b = [torch.rand(n, generator=gen).cuda() for n in sizes]
+    exact = [float((x.double() * y.double()).sum()) for x, y in zip(a, b)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    results = [[], []]
+    for _ in range(40):
+        for k, st in enumerate(streams):
+            with torch.cuda.stream(st):
+                results[k].append(ext.lambda_grad(a[k], b[k]))
+    torch.cuda.synchronize()
+    for k in range(2):
+        vals = torch.cat(results[k]).cpu()
+        assert bool((vals == vals[0]).all()), "the same inputs must give the same bits on every call"
+        assert abs(float(vals[0]) - exact[k]) <= 1e-4 * max(1.0, abs(exact[k]))
+
+
 def test_host_pipeline_matches_direct_calls(ext):
     """The chunked host-buffer API (copies overlapped with kernels) must give exactly the per-image results of the
     direct device API, for chunk sizes that do and do not divide the batch."""
