@@ -133,6 +133,7 @@ constexpr int kAhead = 4;                 // rows by which that walk prefetches 
 
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 constexpr int kRkBits = 6, kCntBits = 3;
+constexpr int kFwdThreads = 64, kFwdBlocksPerSm = 8;     // sliding forward kernel: 128 registers, 16 warps per SM
 constexpr unsigned kRkMask = (1u << kRkBits) - 1u;
 
 struct WeightTap {        // staged per block: the normalised weight of a tap and the tap's window index
@@ -144,7 +145,7 @@ struct WeightTap {        // staged per block: the normalised weight of a tap an
 // issued together, the running sum still takes them one by one in rank order.  With weights that are all >= 0
 // (`monotone`) the running sum never falls, so the first crossing lies in the first round that ends at or above 0.5:
 // the rounds then only add, and the round of the crossing is walked a second time to find the entry.
-template <int K, int G>
+template <int K, int G, int TPB>
 __device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restrict__ sw, bool monotone, int& index) {
     static_assert(K % G == 0, "the scan takes whole rounds");
     Crossing c;
@@ -158,7 +159,7 @@ __device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restric
         for (int r0 = 0; r0 < K; r0 += G) {
             float p[G];
 #pragma unroll
-            for (int i = 0; i < G; ++i) p[i] = sw[(r0 + i) * NT].p;
+            for (int i = 0; i < G; ++i) p[i] = sw[(r0 + i) * TPB].p;
             float s = score;
 #pragma unroll
             for (int i = 0; i < G; ++i) s += p[i];
@@ -171,7 +172,7 @@ __device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restric
         if (round >= 0) {
             float p[G];
 #pragma unroll
-            for (int i = 0; i < G; ++i) p[i] = sw[(round + i) * NT].p;
+            for (int i = 0; i < G; ++i) p[i] = sw[(round + i) * TPB].p;
 #pragma unroll
             for (int i = 0; i < G; ++i) {
                 const float nxt = score + p[i];
@@ -189,7 +190,7 @@ __device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restric
         for (int r0 = 0; r0 < K && c.rank < 0; r0 += G) {
             float p[G];
 #pragma unroll
-            for (int i = 0; i < G; ++i) p[i] = sw[(r0 + i) * NT].p;
+            for (int i = 0; i < G; ++i) p[i] = sw[(r0 + i) * TPB].p;
 #pragma unroll
             for (int i = 0; i < G; ++i) {
                 const float nxt = score + p[i];
@@ -204,13 +205,13 @@ __device__ __forceinline__ Crossing scan_sorted_pairs(const WeightTap* __restric
     }
     if (c.rank >= 0) {
         c.alpha = (float)((1.0 - 2.0 * (double)before - (double)c.pmid) / (2.0 * (double)c.pmid));      // :33
-        index = sw[c.rank * NT].index;
+        index = sw[c.rank * TPB].index;
     }
     return c;
 }
 
 template <int KS>
-__global__ void __launch_bounds__(NT, 3)
+__global__ void __launch_bounds__(kFwdThreads, kFwdBlocksPerSm)
 wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __restrict__ weights, float* __restrict__ out,
                              int* __restrict__ tap, float* __restrict__ alpha, long long nthreads, int H, int W, int runs,
                              int run_len) {
@@ -225,9 +226,9 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
         sp[threadIdx.x].index = threadIdx.x;
     }
     const bool monotone = __syncthreads_and(mine >= 0.0f) != 0;      // no negative (or NaN) weight: the running sum never falls
-    WeightTap* sw = reinterpret_cast<WeightTap*>(smem_raw) + threadIdx.x;             // sw[r * NT]
+    WeightTap* sw = reinterpret_cast<WeightTap*>(smem_raw) + threadIdx.x;             // sw[r * kFwdThreads]
     const long long plane = (long long)H * W;
-    for (long long tix = (long long)blockIdx.x * NT + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * NT) {
+    for (long long tix = (long long)blockIdx.x * kFwdThreads + threadIdx.x; tix < nthreads; tix += (long long)gridDim.x * kFwdThreads) {
         const int w = (int)(tix % W);
         const long long q = tix / W;
         const int run = (int)(q % runs);
@@ -264,9 +265,9 @@ wmedian_forward_slide_kernel(const float* __restrict__ flow, const float* __rest
             const int h = h0 - KS + s;
             if (s >= KS) {
 #pragma unroll
-                for (int i = 0; i < K; ++i) sw[(wd[i] & kRkMask) * NT] = sp[i];
+                for (int i = 0; i < K; ++i) sw[(wd[i] & kRkMask) * kFwdThreads] = sp[i];
                 int t;
-                const Crossing c = scan_sorted_pairs<K, KS>(sw, monotone, t);
+                const Crossing c = scan_sorted_pairs<K, KS, kFwdThreads>(sw, monotone, t);
                 float o = v[K / 2];                              // no crossing: the centre value passes through
                 if (t >= 0) {
                     const int dy = t / KS - R, dx = t % KS - R;
@@ -618,17 +619,17 @@ static int run_forward(const float* flow, const float* wts, float* out, int* tap
     const int smem = K * NT * (int)sizeof(float) + K * NT;
     CNL_TRY(ensure_dynamic_smem(wmedian_forward_kernel<KS>, smem));
     if (slide_enabled()) {
-        const int smem_slide = K * NT * (int)sizeof(WeightTap);
+        const int smem_slide = K * kFwdThreads * (int)sizeof(WeightTap);
         CNL_TRY(ensure_dynamic_smem(wmedian_forward_slide_kernel<KS>, smem_slide));
         // Long runs amortise the KS start-up slides; short ones keep every SM busy on small inputs.
-        const long long cols = total / H, resident = 148LL * 3;
+        const long long cols = total / H, resident = 148LL * kFwdBlocksPerSm;
         int run_len = 16;
-        if ((cols * ((H + 63) / 64) + NT - 1) / NT >= 4 * resident) run_len = 64;
-        else if ((cols * ((H + 31) / 32) + NT - 1) / NT >= resident) run_len = 32;
+        if ((cols * ((H + 63) / 64) + kFwdThreads - 1) / kFwdThreads >= 4 * resident) run_len = 64;
+        else if ((cols * ((H + 31) / 32) + kFwdThreads - 1) / kFwdThreads >= resident) run_len = 32;
         const int runs = (H + run_len - 1) / run_len;
         const long long nthreads = cols * runs;                      // one thread per (image-channel, column, run of rows)
-        const unsigned sblocks = (unsigned)std::min<long long>((nthreads + NT - 1) / NT, 148LL * 64);
-        wmedian_forward_slide_kernel<KS><<<sblocks, NT, smem_slide, st>>>(flow, wts, out, tap, alpha, nthreads, H, W, runs, run_len);
+        const unsigned sblocks = (unsigned)std::min<long long>((nthreads + kFwdThreads - 1) / kFwdThreads, 148LL * 128);
+        wmedian_forward_slide_kernel<KS><<<sblocks, kFwdThreads, smem_slide, st>>>(flow, wts, out, tap, alpha, nthreads, H, W, runs, run_len);
         return after_launch("wmedian_forward_slide_kernel");
     }
     const unsigned blocks = (unsigned)std::min<long long>((total + NT - 1) / NT, 148LL * 64);
