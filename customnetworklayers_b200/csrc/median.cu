@@ -111,6 +111,50 @@ __device__ __forceinline__ int med_crossing(const float* __restrict__ row, int k
     return hit;
 }
 
+// The same for a row without negative weights, whose running sum never falls: the rounds only add (and look at the
+// signs), the first round that ends at or above 0.5 holds the crossing and is walked again for the bin.  `negative`
+// reports a weight below zero (or NaN) anywhere in the row; the result is then not to be used.
+__device__ __forceinline__ int med_crossing_rising(const float* __restrict__ row, int k, float& p_at, float& score_before,
+                                                   bool& negative) {
+    constexpr int G = 8;
+    int round = -1;
+    float score = 0.0f, at_round = 0.0f;
+    negative = false;
+    for (int c0 = 0; c0 < k; c0 += G) {
+        float p[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) p[i] = c0 + i < k ? row[c0 + i] : 0.0f;
+        float s = score;
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            negative |= !(p[i] >= 0.0f);
+            s += p[i];
+        }
+        if (round < 0 && s >= 0.5f) {
+            round = c0;
+            at_round = score;
+        }
+        score = s;
+    }
+    p_at = 1.0f;
+    score_before = 0.0f;
+    if (round < 0) return -1;
+    int hit = -1;
+    score = at_round;
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+        const float p = round + i < k ? row[round + i] : 0.0f;
+        const float nxt = score + p;
+        if (hit < 0 && round + i < k && nxt >= 0.5f) {          // score < 0.5 holds up to the crossing
+            hit = round + i;
+            p_at = p;
+            score_before = score;
+        }
+        score = nxt;
+    }
+    return hit;
+}
+
 __global__ void __launch_bounds__(kMedThreads)
 median_forward_kernel(const float* __restrict__ vol, float* __restrict__ out, int* __restrict__ index,
                       long long plane, int n_images, int k) {
@@ -126,7 +170,9 @@ median_forward_kernel(const float* __restrict__ vol, float* __restrict__ out, in
     if (pix >= total) return;
     const float* row = rows + lane * med_stride(k);
     float o0 = 0.0f, o1 = 0.0f, p, score;
-    const int hit = med_crossing(row, k, p, score);
+    bool negative;
+    int hit = med_crossing_rising(row, k, p, score, negative);
+    if (negative) hit = med_crossing(row, k, p, score);
     if (hit >= 0) {
         const double alpha = (1.0 - 2.0 * (double)score - (double)p) / (2.0 * (double)p);         // :33
         o0 = (float)((double)hit + alpha);                           // :34
@@ -158,27 +204,36 @@ median_backward_kernel(const float* __restrict__ vol, const float* __restrict__ 
         const float g1 = grad[(img * 2 + 1) * plane + off];
         // pass 1: crossing bin (medimax.cu:55-80)
         float score, pmid, gmid = 0.0f;
-        const int hit = med_crossing(row, k, pmid, score);
+        bool negative;
+        int hit = med_crossing_rising(row, k, pmid, score, negative);
+        if (negative) hit = med_crossing(row, k, pmid, score);
         if (hit >= 0) {
             const float alpha = (float)((1.0 - 2.0 * (double)score - (double)pmid) / (2.0 * (double)pmid));
             gmid = __fadd_rn(__fdiv_rn(__fmul_rn(g0, alpha), -pmid), g1);        // :73, fp32, no contraction
         }
         // pass 2: bins before / after the crossing (:82-99); the row in shared memory is overwritten by its gradient
         const float half = (float)((double)g0 / (2.0 * (double)pmid));
-        score = 0.0f;
-        for (int c0 = 0; c0 < k; c0 += 8) {
-            float p[8];
+        if (!negative) {
+            // the running sum never falls: bins in front of the crossing are the ones the tests below call "before"
+            // (nxt < 0.5), bins behind it the ones they call "after" (score >= 0.5); no crossing: all "before"
+            const int at = hit < 0 ? k : hit;
+            for (int c = 0; c < k; ++c) row[c] = c < at ? -half : (c == at ? gmid : half);
+        } else {
+            score = 0.0f;
+            for (int c0 = 0; c0 < k; c0 += 8) {
+                float p[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) p[i] = c0 + i < k ? row[c0 + i] : 0.0f;
+                for (int i = 0; i < 8; ++i) p[i] = c0 + i < k ? row[c0 + i] : 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float nxt = score + p[i];
-                float g = 0.0f;
-                if (nxt < 0.5f) g = -half;
-                else if (score >= 0.5f) g = half;
-                if (c0 + i == hit) g = gmid;
-                if (c0 + i < k) row[c0 + i] = g;
-                score = nxt;
+                for (int i = 0; i < 8; ++i) {
+                    const float nxt = score + p[i];
+                    float g = 0.0f;
+                    if (nxt < 0.5f) g = -half;
+                    else if (score >= 0.5f) g = half;
+                    if (c0 + i == hit) g = gmid;
+                    if (c0 + i < k) row[c0 + i] = g;
+                    score = nxt;
+                }
             }
         }
     }

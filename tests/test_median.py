@@ -84,6 +84,27 @@ def test_cuda_matches_oracle_bit_exact_index(case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("k", [7, 49, 64])
+def test_rows_with_negative_weights_take_the_general_scan(k):
+    """Rows without negative weights are scanned by a shorter route (their running sum never falls); a negative weight
+    anywhere in a row must send that row through the general rule, where the sum can cross 0.5 more than once."""
+    from customnetworklayers_b200 import median_cuda_ext as ext
+    vol, grad = make_median_volume(2, 9, 37, k, seed=90 + k)
+    vol = vol.clone()
+    vol[0, :, ::3, 1::5] *= -0.7                   # some rows only; the others stay on the short route
+    vol[1, 2, 3, :] = 0.0
+    vol[1, 2, 3, 0], vol[1, 2, 3, 1], vol[1, 2, 3, 2] = 0.6, -0.3, 0.4      # crosses, falls back, crosses again
+    out, idx = ext.forward_with_index(vol.cuda())
+    g = ext.backward(grad.cuda(), vol.cuda())[0]
+    o_ref, i_ref = M.median_forward(vol.numpy())
+    g_ref = M.median_backward(vol.numpy(), grad.numpy())
+    assert int(i_ref[1, 2, 3]) == 0
+    assert np.array_equal(idx.cpu().numpy(), i_ref), "crossing index must be bit-exact"
+    assert np.array_equal(out.cpu().numpy(), o_ref), "position and crossing weight must be bit-exact"
+    assert np.array_equal(g.cpu().numpy(), g_ref), "gradient must be bit-exact"
+
+
+@pytest.mark.gpu
 def test_cuda_matches_reference_kernels_live():
     from oracle import ref_cuda
     if not ref_cuda.median_available():
